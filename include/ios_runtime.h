@@ -1,0 +1,116 @@
+/*
+ * C-ABI of libios_runtime.so, the B200-native execution engine for IOS schedules.
+ *
+ * The first four symbols are exactly what the reference's ctypes front-end binds
+ * (python/ios/contrib/ios_runtime.py:18-23 loads the library, :33, :63, :101, :124 call them) and
+ * keep the reference's signatures (src/ios/ios_runtime.cu:1480-1502).  They return nothing; on an
+ * error they fill their float outputs with NaN and record a message readable through
+ * ios_last_error().  Every other entry point returns an int status (0 = IOS_OK).
+ *
+ * All pointers are owned by the caller and only have to stay valid for the duration of the call.
+ * Tensors at this boundary are float32, NCHW, batch-major, C-contiguous; convolution weights are
+ * OIHW (Cout, Cin/groups, kh, kw) and biases (Cout).  JSON arguments follow the wire format of
+ * python/ios/ir.py (Graph.export_config, Block.export_config, Node.export_config).
+ */
+#ifndef IOS_RUNTIME_H_
+#define IOS_RUNTIME_H_
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define IOS_API __attribute__((visibility("default")))
+
+enum {
+    IOS_OK = 0,
+    IOS_ERR_JSON = 1,       /* malformed JSON text */
+    IOS_ERR_GRAPH = 2,      /* well-formed JSON that is not a valid graph / block / stage */
+    IOS_ERR_ARGUMENT = 3,   /* bad argument (NULL pointer, non-positive count, unknown option) */
+    IOS_ERR_CUDA = 4,       /* a CUDA runtime or driver call failed */
+    IOS_ERR_TIMEOUT = 5,    /* a bounded device-side wait ran out */
+    IOS_ERR_LIMIT = 6,      /* a stated size limit was exceeded */
+    IOS_ERR_MISSING = 7     /* a convolution was given no weights */
+};
+
+/* ---- drop-in symbols (reference src/ios/ios_runtime.cu:1480, :1486, :1492, :1500) ---------- */
+
+/* Time a whole graph: results[repeat] (ms, each the mean of `number` forwards) and, when
+ * profile_stage_latency != 0, stage_results[repeat * num_stages] row-major. */
+IOS_API void graph_latency(const char *graph_json, int batch_size, int warmup, int number, int repeat,
+                           int profile_stage_latency, float *results, float *stage_results);
+/* Same for one block; its enter node becomes the input. */
+IOS_API void block_latency(const char *block_json, int batch_size, int warmup, int number, int repeat,
+                           int profile_stage_latency, float *results, float *stage_results);
+/* Time one candidate stage: stage_json = [[node config, ...], ...] (groups x operators),
+ * input_json = {producer name: [C, H, W]}.  results[repeat]; stage_results is not written. */
+IOS_API void stage_latency(const char *stage_json, const char *input_json, int batch_size, int warmup,
+                           int number, int repeat, int profile_stage_latency, float *results,
+                           float *stage_results);
+/* Run a graph once on host data: uploads input and weights, executes the schedule, downloads the
+ * exit node of the last block into output[batch, C, H, W]. */
+IOS_API void graph_inference(const char *graph_json, int batch_size, float *input, int num_convs,
+                             char **conv_names, float **filter_data, float **bias_data, float *output);
+
+/* ---- status-returning twins of the four symbols above (same arguments) --------------------- */
+IOS_API int ios_graph_latency(const char *graph_json, int batch_size, int warmup, int number, int repeat,
+                              int profile_stage_latency, float *results, float *stage_results);
+IOS_API int ios_block_latency(const char *block_json, int batch_size, int warmup, int number, int repeat,
+                              int profile_stage_latency, float *results, float *stage_results);
+IOS_API int ios_stage_latency(const char *stage_json, const char *input_json, int batch_size, int warmup,
+                              int number, int repeat, int profile_stage_latency, float *results,
+                              float *stage_results);
+IOS_API int ios_graph_inference(const char *graph_json, int batch_size, const float *input, int num_convs,
+                                char **conv_names, float **filter_data, float **bias_data, float *output);
+
+/* Message of the calling thread's most recent failure ("" if none).  Replaces the reference's
+ * FatalError -> exit(1) (include/utils/utils.h:8-14): the library never terminates the process. */
+IOS_API const char *ios_last_error(void);
+
+/* ---- run-time options (replace the reference's compile-time switches, config.cmake:8-17) ----
+ * key "precision": "tf32" (default; fp32 storage, TF32 tensor-core products, fp32 accumulate),
+ *                  "fp32" (CUDA-core fp32 products, the slow exact path)
+ * key "executor":  "graph" (default; a schedule is captured once into a CUDA graph),
+ *                  "streams" (group j of every stage is launched on stream j, events between stages)
+ * key "conv":      "auto" (default), "direct" (never use the tensor-core kernel)
+ * Options apply to plans built afterwards on the calling process. */
+IOS_API int ios_set_option(const char *key, const char *value);
+IOS_API int ios_get_option(const char *key, char *value, int capacity);
+
+/* Select the CUDA device used by subsequent calls of this process (reference: device 0 only,
+ * src/ios/profile.cu:40-46). */
+IOS_API int ios_set_device(int device);
+IOS_API int ios_device_count(int *count);
+
+/* ---- engine: build once, run many (replaces the per-call map()/unmap() of the reference,
+ *      src/ios/ios_runtime.cu:1273-1285, 1318-1327, for serving and for benchmarking) ---------- */
+typedef struct ios_engine ios_engine;
+
+/* Build a resident plan for (graph, batch size): parses, plans memory, packs and uploads the
+ * weights (filter_data / bias_data may be NULL as a whole: synthetic weights are generated). */
+IOS_API int ios_engine_create(const char *graph_json, int batch_size, int num_convs, char **conv_names,
+                              float **filter_data, float **bias_data, ios_engine **engine);
+IOS_API int ios_engine_destroy(ios_engine *engine);
+/* Host in -> host out.  input[batch, C, H, W], output[batch, Cexit, Hexit, Wexit]. */
+IOS_API int ios_engine_run(ios_engine *engine, const float *input, float *output);
+/* Execute `iters` forwards on the resident input; *ms_per_iter receives the CUDA-event time. */
+IOS_API int ios_engine_time(ios_engine *engine, int iters, float *ms_per_iter);
+/* Describe the plan: writes a JSON text (kernel launches per forward, arena bytes, workspace bytes,
+ * algorithmic FLOPs, output shape) into text[capacity]. */
+IOS_API int ios_engine_describe(ios_engine *engine, char *text, int capacity);
+/* Upload the input once (for ios_engine_time) / read back the last output. */
+IOS_API int ios_engine_set_input(ios_engine *engine, const float *input);
+IOS_API int ios_engine_get_output(ios_engine *engine, float *output);
+
+/* ---- single-operator entry points used by the parity tests (no reference counterpart: the
+ *      reference reaches its operators only through a graph; ConvOP::forward is
+ *      src/ios/ios_runtime.cu:309-332, PoolOP::forward :563-566) ------------------------------ */
+/* y[n, cout, oh, ow] = act(conv(x[n, cin, h, w], w[cout, cin/groups, kh, kw]) + bias).
+ * act: 0 identity, 1 relu, 2 sigmoid, 3 tanh.  impl: 0 auto, 1 direct (CUDA cores), 2 tensor core. */
+IOS_API int ios_conv2d(const float *x, const float *w, const float *bias, float *y, int n, int cin, int h,
+                       int wdt, int cout, int kh, int kw, int sh, int sw, int ph, int pw, int groups,
+                       int act, int impl);
+
+#ifdef __cplusplus
+}
+#endif
+#endif  /* IOS_RUNTIME_H_ */

@@ -1,0 +1,530 @@
+// Implicit-GEMM convolution on the 5th-generation tensor cores (sm_100a): tcgen05.mma with the
+// accumulator in tensor memory, both operands staged in shared memory by TMA, one CTA per
+// (pixel tile, output-channel tile, K split).
+//
+// GEMM view of y = act(conv(x, w) + b), groups == 1:
+//     D[pixel, cout] = sum over taps (r, s) and input channels c of  X[pixel @ tap, c] * Wp[cout, tap, c]
+// * M (128 TMEM lanes) = a tile of output pixels: box_w x box_h x box_n pixels of the output,
+//   fetched for tap (r, s) by ONE tiled TMA load over the NHWC input whose box starts at
+//   (ow0*sw - pw + s, oh0*sh - ph + r) and walks with element strides (sw, sh).  Coordinates
+//   outside the image are filled with zeros by the TMA unit, which is the convolution's padding;
+//   channels beyond Cin are out of range too, so K needs no padded activation copy.
+// * N = bn output channels (16..256), K advances 32 floats (one 128-byte swizzle row) per step,
+//   four tcgen05.mma.kind::tf32 (K = 8) per step.
+// * split_k CTAs share an output tile when the layer is too small to fill 148 SMs (batch 1):
+//   each writes its fp32 partial tile to a workspace, the last to arrive (one atomic ticket per
+//   tile) adds the partials in split order -- so results do not depend on arrival order -- and
+//   runs the epilogue.
+// * Epilogue: tcgen05.ld (one thread per pixel row), + bias, activation, optional rounding to TF32
+//   for a consumer convolution, store into a channel window of the destination (NHWC, pitch), which
+//   is how concat-by-placement and merged convolutions are written without a copy.
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM allocator + MMA issuer,
+// warps 2..5 = epilogue.  Every wait on an mbarrier is bounded: when the bound is hit the kernel
+// records a code in *error_flag, drains its own loads, frees its tensor memory and returns.
+//
+// Replaces cudnnConvolutionBiasActivationForward / cudnnConvolutionForward + cudnnAddTensor
+// (reference src/ios/ios_runtime.cu:313-331) and the algorithm search of :150-205.
+#include "kernels.h"
+
+#include <cuda.h>
+#include <cstdio>
+#include <cstring>
+#include <cmath>
+#include <algorithm>
+
+namespace ios {
+namespace {
+
+constexpr int kTileM = 128;          // TMEM lanes = pixel rows per CTA
+constexpr int kChunk = 32;           // floats of K per pipeline step = one 128-byte swizzle row
+constexpr int kATileBytes = kTileM * kChunk * 4;   // 16 KiB
+constexpr int kThreads = 192;
+constexpr uint64_t kWaitBudgetNs = 2000000000ull;  // 2 s per wait
+
+struct TileGeom {
+    int box_w, box_h, box_n;
+    int tiles_w, tiles_h;
+    int bn, cchunks, k_iters, split_k, stages, flat;
+    int a_bytes;      // bytes one A load delivers
+    int tmem_cols;
+    int round_tf32;   // round the stored result to TF32 (the consumer is a tensor-core convolution)
+};
+
+// ---- PTX wrappers ----------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+__device__ __forceinline__ uint64_t global_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: false when the budget ran out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_ns();
+    for (uint32_t spin = 1;; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 255u) == 0 && global_ns() - t0 > kWaitBudgetNs) return false;
+    }
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void *tmap, uint32_t bar, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void *tmap, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float *v) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+// K-major operand tile with 128-byte swizzle: rows are 128 bytes, groups of 8 rows are 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    uint64_t d = 0;
+    d |= uint64_t((addr & 0x3FFFF) >> 4);    // start address, 16-byte units
+    d |= uint64_t(1) << 16;                  // leading-dimension byte offset (unused for swizzled K-major)
+    d |= uint64_t(1024 >> 4) << 32;          // stride-dimension byte offset: 8 rows * 128 B
+    d |= uint64_t(1) << 46;                  // descriptor version for sm_100
+    d |= uint64_t(2) << 61;                  // SWIZZLE_128B
+    return d;
+}
+__device__ __forceinline__ float act_apply(float v, int act) {
+    switch (act) {
+        case 1: return fmaxf(v, 0.0f);
+        case 2: return 1.0f / (1.0f + __expf(-v));
+        case 3: return tanhf(v);
+        default: return v;
+    }
+}
+__device__ __forceinline__ float round_tf32(float v) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+    return __uint_as_float(r);
+}
+
+// ---- the kernel ------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads, 1)
+conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const ConvTcParams p, const TileGeom t) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int b_bytes = t.bn * kChunk * 4;
+    const int stage_bytes = kATileBytes + b_bytes;
+    const uint32_t bars = smem_base + uint32_t(t.stages) * stage_bytes;   // full[stages], empty[stages], accum
+    const uint32_t full0 = bars, empty0 = bars + 8u * t.stages, accum_bar = bars + 16u * t.stages;
+    uint8_t *generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(generic_base + size_t(t.stages) * stage_bytes + 16 * t.stages + 8);
+    volatile int *ticket_slot = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const ConvGeom &g = p.g;
+
+    // a wait that ran out in an earlier CTA of this launch makes the rest of the grid return at once
+    __shared__ int abort_launch;
+    if (threadIdx.x == 0) abort_launch = *reinterpret_cast<volatile int *>(p.error_flag);
+    __syncthreads();
+    if (abort_launch != 0) return;
+
+    // tile coordinates
+    const int m_tile = blockIdx.x, n_tile = blockIdx.y, split = blockIdx.z;
+    int ow0 = 0, oh0 = 0, n0 = 0;
+    if (t.flat) {
+        ow0 = m_tile * t.box_w;
+    } else {
+        const int tw = m_tile % t.tiles_w;
+        const int rest = m_tile / t.tiles_w;
+        ow0 = tw * t.box_w;
+        oh0 = (rest % t.tiles_h) * t.box_h;
+        n0 = (rest / t.tiles_h) * t.box_n;
+    }
+    const int cout0 = n_tile * t.bn;
+    const int it_begin = int(long(split) * t.k_iters / t.split_k);
+    const int it_end = int(long(split + 1) * t.k_iters / t.split_k);
+    const int n_it = it_end - it_begin;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < t.stages; ++s) {
+            mbar_init(full0 + 8u * s, 1);
+            mbar_init(empty0 + 8u * s, 1);
+        }
+        mbar_init(accum_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), uint32_t(t.tmem_cols));
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---------------- TMA producer ----------------
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
+            bool ok = true;
+            int issued = 0;
+            for (int i = 0; i < n_it && ok; ++i) {
+                const int s = i % t.stages;
+                if (i >= t.stages) ok = mbar_wait(empty0 + 8u * s, uint32_t((i / t.stages - 1) & 1));
+                if (!ok) break;
+                const int it = it_begin + i;
+                const int tap = it / t.cchunks, cc = it - tap * t.cchunks;
+                const int r = tap / g.kw, sx = tap - r * g.kw;
+                const uint32_t a_dst = smem_base + uint32_t(s) * stage_bytes;
+                const uint32_t bar = full0 + 8u * s;
+                mbar_expect_tx(bar, uint32_t(t.a_bytes + b_bytes));
+                if (t.flat) tma_load_4d(a_dst, &tmap_a, bar, cc * kChunk, ow0, 0, 0);
+                else tma_load_4d(a_dst, &tmap_a, bar, cc * kChunk, ow0 * g.sw - g.pw + sx, oh0 * g.sh - g.ph + r, n0);
+                tma_load_2d(a_dst + kATileBytes, &tmap_b, bar, it * kChunk, cout0);
+                issued = i + 1;
+            }
+            if (!ok) {
+                atomicExch(p.error_flag, 1);
+                // drain: the loads already issued still land in this CTA's shared memory
+                for (int i = max(0, issued - t.stages); i < issued; ++i)
+                    mbar_wait(full0 + 8u * (i % t.stages), uint32_t((i / t.stages) & 1));
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---------------- MMA issuer ----------------
+            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(t.bn >> 3) << 17) | (uint32_t(kTileM >> 4) << 24);
+            bool ok = true;
+            for (int i = 0; i < n_it; ++i) {
+                const int s = i % t.stages;
+                ok = mbar_wait(full0 + 8u * s, uint32_t((i / t.stages) & 1));
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_addr = smem_base + uint32_t(s) * stage_bytes;
+                const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + kATileBytes);
+#pragma unroll
+                for (int k = 0; k < kChunk / 8; ++k)
+                    umma_tf32(tmem_base, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+                umma_commit(empty0 + 8u * s);   // frees the stage once these MMAs have read it
+            }
+            if (ok) umma_commit(accum_bar);
+            else atomicExch(p.error_flag, 2);
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5, one thread per TMEM lane ----------------
+        const int quad = warp & 3;                  // TMEM lane group this warp may read
+        const int row = quad * 32 + lane;
+        bool ok = mbar_wait(accum_bar, 0);
+        if (!ok && lane == 0) atomicExch(p.error_flag, 3);
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16);
+        const int tile_id = m_tile * gridDim.y + n_tile;
+        bool finisher = true;
+        if (ok && t.split_k > 1) {
+            // publish this CTA's partial tile: ws[tile][split][col][row], rows contiguous
+            float *ws = p.workspace + (size_t(tile_id) * t.split_k + split) * size_t(t.bn) * kTileM;
+            for (int c = 0; c < t.bn; c += 16) {
+                float v[16];
+                tmem_ld16(taddr + c, v);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) ws[size_t(c + j) * kTileM + row] = v[j];
+            }
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (threadIdx.x == 64) {
+                const unsigned int prev = atomicAdd(p.counters + tile_id, 1u);
+                *ticket_slot = int(prev);
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            finisher = (*ticket_slot == t.split_k - 1);
+            if (finisher) __threadfence();
+        }
+        if (ok && finisher) {
+            // which output pixel does this row hold?
+            long pix_off = -1;
+            if (t.flat) {
+                const long pix = long(ow0) + row;
+                if (row < t.box_w && pix < long(g.N) * g.OH * g.OW) pix_off = pix * p.out.pitch;
+            } else {
+                const int ww = row % t.box_w;
+                const int hh = (row / t.box_w) % t.box_h;
+                const int im = row / (t.box_w * t.box_h);
+                const int ow = ow0 + ww, oh = oh0 + hh, n = n0 + im;
+                if (im < t.box_n && ow < g.OW && oh < g.OH && n < g.N)
+                    pix_off = ((long(n) * g.OH + oh) * g.OW + ow) * p.out.pitch;
+            }
+            const int valid = min(t.bn, g.Cout - cout0);
+            float *dst = p.out.ptr + (pix_off < 0 ? 0 : pix_off) + cout0;
+            const bool vec_ok = ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+            const float *ws_tile = p.workspace + size_t(tile_id) * t.split_k * size_t(t.bn) * kTileM;
+            for (int c = 0; c < t.bn; c += 16) {
+                float v[16];
+                if (t.split_k == 1) {
+                    tmem_ld16(taddr + c, v);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+                    for (int s = 0; s < t.split_k; ++s) {
+                        const float *src = ws_tile + size_t(s) * t.bn * kTileM + size_t(c) * kTileM + row;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] += __ldcg(src + size_t(j) * kTileM);
+                    }
+                }
+                if (pix_off < 0 || c >= valid) continue;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int co = cout0 + c + j;
+                    float o = v[j] + ((p.bias && co < g.Cout) ? p.bias[co] : 0.0f);
+                    o = act_apply(o, g.act);
+                    v[j] = t.round_tf32 ? round_tf32(o) : o;
+                }
+                if (vec_ok && c + 16 <= valid) {
+#pragma unroll
+                    for (int j = 0; j < 16; j += 4)
+                        *reinterpret_cast<float4 *>(dst + c + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (c + j < valid) dst[c + j] = v[j];
+                }
+            }
+            if (t.split_k > 1 && threadIdx.x == 64) p.counters[tile_id] = 0;   // ready for the next launch
+        }
+        tc_fence_before();
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, uint32_t(t.tmem_cols));
+    }
+}
+
+// ---- host side -------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn) return fn;
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+        return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(sym);
+    return fn;
+}
+
+int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+float tf32_round_host(float v) {
+    uint32_t u;
+    std::memcpy(&u, &v, 4);
+    if ((u & 0x7F800000u) == 0x7F800000u) return v;   // inf / nan
+    u += 0x00000FFFu + ((u >> 13) & 1u);              // round to nearest even on the 13 dropped bits
+    u &= 0xFFFFE000u;
+    float r;
+    std::memcpy(&r, &u, 4);
+    return r;
+}
+
+}  // namespace
+
+bool conv_tc_supported(const TensorRef &in, const ConvGeom &g) {
+    if (g.groups != 1 || g.pre_relu) return false;
+    if ((reinterpret_cast<uintptr_t>(in.ptr) & 15) != 0 || in.pitch % 4 != 0) return false;
+    if (g.sw > 8 || g.sh > 8) return false;            // TMA element strides are at most 8
+    if (g.kh * g.kw > 4096) return false;
+    return true;
+}
+
+void conv_tc_choose(const ConvGeom &g, int sm_count, int concurrency_hint, ConvTcPlan *plan) {
+    ConvTcPlan &q = *plan;
+    const bool flat = g.kh == 1 && g.kw == 1 && g.sh == 1 && g.sw == 1 && g.ph == 0 && g.pw == 0;
+    q.flat_1x1 = flat ? 1 : 0;
+    if (flat) {
+        const long pixels = long(g.N) * g.OH * g.OW;
+        const long tiles = (pixels + kTileM - 1) / kTileM;
+        q.box_w = int((pixels + tiles - 1) / tiles);
+        q.box_h = q.box_n = 1;
+        q.tiles_w = int((pixels + q.box_w - 1) / q.box_w);
+        q.tiles_h = q.tiles_n = 1;
+    } else if (g.OW <= std::min(kTileM, 256 / g.sw)) {
+        q.box_w = g.OW;
+        q.box_h = std::min(g.OH, std::max(1, kTileM / g.OW));
+        if (q.box_h * g.sh > 256) q.box_h = 256 / g.sh;
+        q.box_n = (q.box_h == g.OH) ? std::min(g.N, std::max(1, kTileM / (g.OH * g.OW))) : 1;
+        q.tiles_w = 1;
+        q.tiles_h = ceil_div(g.OH, q.box_h);
+        q.tiles_n = ceil_div(g.N, q.box_n);
+    } else {
+        const int max_w = std::min(kTileM, 256 / g.sw);
+        const int parts = ceil_div(g.OW, max_w);
+        q.box_w = ceil_div(g.OW, parts);
+        q.box_h = q.box_n = 1;
+        q.tiles_w = ceil_div(g.OW, q.box_w);
+        q.tiles_h = g.OH;
+        q.tiles_n = g.N;
+    }
+    const int m_tiles = q.tiles_w * q.tiles_h * q.tiles_n;
+    const int target = std::max(1, sm_count / std::max(1, concurrency_hint));
+    // output-channel tiling: wide tiles when the pixel tiles alone fill the machine, else narrow
+    int n_tiles = ceil_div(g.Cout, m_tiles * ceil_div(g.Cout, 128) >= target ? 128 : 64);
+    q.bn = std::min(256, ceil_div(ceil_div(g.Cout, n_tiles), 16) * 16);
+    q.n_tiles = ceil_div(g.Cout, q.bn);
+    q.cout_pad = q.n_tiles * q.bn;
+    q.cchunks = ceil_div(g.Cin, kChunk);
+    q.k_iters = g.kh * g.kw * q.cchunks;
+    const int base = m_tiles * q.n_tiles;
+    int split = 1;
+    if (base < target) {
+        split = std::min(target / base, q.k_iters / 3);
+        split = std::max(1, std::min(split, 32));
+    }
+    q.split_k = split;
+    const int stage_bytes = kATileBytes + q.bn * kChunk * 4;
+    const int per_split = ceil_div(q.k_iters, split);
+    q.stages = std::max(2, std::min({6, per_split, (200 * 1024) / stage_bytes}));
+    q.smem_bytes = size_t(q.stages) * stage_bytes + 16 * q.stages + 64 + 1024;
+    q.workspace_bytes = split > 1 ? size_t(base) * split * q.bn * kTileM * sizeof(float) : 0;
+    q.counter_bytes = split > 1 ? size_t(base) * sizeof(unsigned int) : 0;
+}
+
+size_t conv_tc_packed_floats(const ConvGeom &g, const ConvTcPlan &plan) {
+    return size_t(plan.cout_pad) * g.kh * g.kw * plan.cchunks * kChunk;
+}
+
+void conv_tc_pack_weights(const float *oihw, const ConvGeom &g, const ConvTcPlan &plan, float *packed) {
+    const int taps = g.kh * g.kw;
+    const size_t row = size_t(taps) * plan.cchunks * kChunk;
+    std::memset(packed, 0, size_t(plan.cout_pad) * row * sizeof(float));
+    for (int o = 0; o < g.Cout; ++o)
+        for (int c = 0; c < g.Cin; ++c)
+            for (int tp = 0; tp < taps; ++tp)
+                packed[size_t(o) * row + size_t(tp) * plan.cchunks * kChunk + c] =
+                    tf32_round_host(oihw[(size_t(o) * g.Cin + c) * taps + tp]);
+}
+
+const char *conv_tc_encode(const ConvTcParams &p, ConvTcPlan *plan) {
+    EncodeTiledFn encode = encode_fn();
+    if (!encode) return "cuTensorMapEncodeTiled is not available from the driver";
+    const ConvGeom &g = p.g;
+    ConvTcPlan &q = *plan;
+    static char msg[160];
+    {
+        cuuint64_t dims[4];
+        cuuint64_t strides[3];
+        cuuint32_t box[4], estr[4];
+        const cuuint64_t pix_bytes = cuuint64_t(p.in.pitch) * 4;
+        if (q.flat_1x1) {
+            dims[0] = cuuint64_t(g.Cin); dims[1] = cuuint64_t(g.N) * g.H * g.W; dims[2] = 1; dims[3] = 1;
+            strides[0] = pix_bytes; strides[1] = pix_bytes * dims[1]; strides[2] = strides[1];
+            box[0] = kChunk; box[1] = cuuint32_t(q.box_w); box[2] = 1; box[3] = 1;
+            estr[0] = estr[1] = estr[2] = estr[3] = 1;
+        } else {
+            dims[0] = cuuint64_t(g.Cin); dims[1] = cuuint64_t(g.W); dims[2] = cuuint64_t(g.H); dims[3] = cuuint64_t(g.N);
+            strides[0] = pix_bytes; strides[1] = pix_bytes * g.W; strides[2] = pix_bytes * g.W * g.H;
+            box[0] = kChunk; box[1] = cuuint32_t(q.box_w * g.sw); box[2] = cuuint32_t(q.box_h * g.sh); box[3] = cuuint32_t(q.box_n);
+            estr[0] = 1; estr[1] = cuuint32_t(g.sw); estr[2] = cuuint32_t(g.sh); estr[3] = 1;
+        }
+        CUresult r = encode(reinterpret_cast<CUtensorMap *>(q.tmap_a), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.in.ptr, dims,
+                            strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) {
+            std::snprintf(msg, sizeof msg, "cuTensorMapEncodeTiled(activations) failed with CUresult %d", int(r));
+            return msg;
+        }
+    }
+    {
+        const cuuint64_t krow = cuuint64_t(g.kh) * g.kw * q.cchunks * kChunk;
+        cuuint64_t dims[2] = {krow, cuuint64_t(q.cout_pad)};
+        cuuint64_t strides[1] = {krow * 4};
+        cuuint32_t box[2] = {kChunk, cuuint32_t(q.bn)};
+        cuuint32_t estr[2] = {1, 1};
+        CUresult r = encode(reinterpret_cast<CUtensorMap *>(q.tmap_b), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+                            const_cast<float *>(p.weight_packed), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) {
+            std::snprintf(msg, sizeof msg, "cuTensorMapEncodeTiled(weights) failed with CUresult %d", int(r));
+            return msg;
+        }
+    }
+    return nullptr;
+}
+
+cudaError_t conv_tc_prepare() {
+    return cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+}
+
+void launch_conv_tc(const ConvTcParams &p, const ConvTcPlan &q, cudaStream_t stream) {
+    TileGeom t;
+    t.box_w = q.box_w; t.box_h = q.box_h; t.box_n = q.box_n;
+    t.tiles_w = q.tiles_w; t.tiles_h = q.tiles_h;
+    t.bn = q.bn; t.cchunks = q.cchunks; t.k_iters = q.k_iters; t.split_k = q.split_k; t.stages = q.stages;
+    t.flat = q.flat_1x1;
+    t.a_bytes = q.box_w * q.box_h * q.box_n * kChunk * 4;
+    int cols = 32;
+    while (cols < q.bn) cols *= 2;
+    t.tmem_cols = cols;
+    t.round_tf32 = p.g.round_out;
+    dim3 grid(q.tiles_w * q.tiles_h * q.tiles_n, q.n_tiles, q.split_k);
+    conv_tc_kernel<<<grid, kThreads, q.smem_bytes, stream>>>(*reinterpret_cast<const CUtensorMap *>(q.tmap_a),
+                                                             *reinterpret_cast<const CUtensorMap *>(q.tmap_b), p, t);
+}
+
+}  // namespace ios

@@ -1,0 +1,123 @@
+// Device-side operator library: parameter blocks and host launchers.
+//
+// Activations live in HBM as NHWC float32 with a per-pixel pitch (floats) that is a multiple of 4,
+// so that a pixel row starts on a 16-byte boundary.  A TensorRef addresses a channel window of such
+// a buffer: element (n, h, w, c) is ptr[((n*H + h)*W + w)*pitch + c].  Channel slices, concat
+// members and whole tensors are all TensorRefs, which is what lets a producer write straight into
+// its slot of a consumer's concat buffer and a consumer read a slice of a merged convolution
+// without the copy kernels of the reference (src/ios/ops.cu:6-24).
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace ios {
+
+struct TensorRef {
+    float *ptr = nullptr;
+    int N = 0, H = 0, W = 0, C = 0;
+    int pitch = 0;   // floats between consecutive pixels
+
+    __host__ __device__ long pixels() const { return long(N) * H * W; }
+    bool vec4() const { return (C % 4 == 0) && (pitch % 4 == 0) && ((reinterpret_cast<uintptr_t>(ptr) & 15) == 0); }
+};
+
+constexpr int kMaxSumInputs = 8;
+
+// out = act(in_0 (+|*) in_1 ... in_{k-1}); k = 1 with act = identity is a strided copy.
+struct SumActParams {
+    const float *in[kMaxSumInputs];
+    int in_pitch[kMaxSumInputs];
+    float *out;
+    int out_pitch;
+    int k;
+    int C;
+    long pixels;
+    int act;   // Act
+    int mul;   // 1: product instead of sum
+    int round_out;   // 1: round the stored result to TF32
+};
+void launch_sum_act(const SumActParams &p, bool vec4, cudaStream_t stream);
+
+struct PoolParams {
+    TensorRef in, out;
+    int kh, kw, sh, sw, ph, pw;
+    int is_max;
+    int round_out;   // 1: round the stored result to TF32
+};
+void launch_pool(const PoolParams &p, cudaStream_t stream);
+
+// NCHW dense <-> NHWC TensorRef
+void launch_nchw_to_nhwc(const float *src, TensorRef dst, bool round_tf32, cudaStream_t stream);
+void launch_nhwc_to_nchw(TensorRef src, float *dst, cudaStream_t stream);
+
+// Deterministic pseudo-random fill in [-scale, scale] (synthetic weights / inputs for timing runs).
+void launch_fill(float *dst, long count, uint32_t seed, float scale, cudaStream_t stream);
+
+// ---- convolution ---------------------------------------------------------------------------
+struct ConvGeom {
+    int N, Cin, H, W;      // input
+    int Cout, OH, OW;      // output
+    int kh, kw, sh, sw, ph, pw, groups;
+    int act;
+    int pre_relu;          // apply ReLU to the input while reading it (fused ReLU -> conv)
+    int round_out;         // round the stored result to TF32: every consumer is a tensor-core convolution
+};
+
+// CUDA-core convolution for every shape the tensor-core kernel does not take (grouped, unaligned
+// views, precision "fp32").  Weights: [tap][Cin/groups][Cout] float32.
+struct ConvDirectParams {
+    TensorRef in, out;
+    const float *weight;
+    const float *bias;
+    ConvGeom g;
+};
+void launch_conv_direct(const ConvDirectParams &p, cudaStream_t stream);
+// Depthwise (groups == Cin == Cout).  Weights: [tap][C] float32.
+void launch_conv_depthwise(const ConvDirectParams &p, cudaStream_t stream);
+
+// Tensor-core implicit-GEMM convolution (tcgen05 + TMEM + TMA), groups == 1.
+// Packed weights: [Cout_pad][taps][cchunks*32] float32 (TF32-rounded), zero padded.
+struct ConvTcPlan {
+    // tile geometry chosen by conv_tc_plan()
+    int box_w, box_h, box_n;       // output pixels covered by one M tile along W, H, batch
+    int tiles_w, tiles_h, tiles_n; // number of M tiles along each
+    int bn;                        // output channels per CTA (UMMA N)
+    int n_tiles;                   // ceil(Cout / bn)
+    int cchunks;                   // ceil(Cin / 32)
+    int k_iters;                   // taps * cchunks
+    int split_k;                   // CTAs sharing one output tile
+    int stages;                    // smem pipeline depth
+    int flat_1x1;                  // 1: pixels flattened into one axis (1x1, stride 1, no padding)
+    size_t smem_bytes;
+    size_t workspace_bytes;        // split-K partial tiles (0 when split_k == 1)
+    size_t counter_bytes;          // split-K arrival counters
+    int cout_pad;                  // rows of the packed weight matrix
+    alignas(64) unsigned char tmap_a[128];   // CUtensorMap over the input view
+    alignas(64) unsigned char tmap_b[128];   // CUtensorMap over the packed weights
+};
+struct ConvTcParams {
+    TensorRef in, out;
+    const float *weight_packed;
+    const float *bias;
+    float *workspace;
+    unsigned int *counters;
+    int *error_flag;               // device word set to non-zero when a bounded wait ran out
+    ConvGeom g;
+};
+// Returns false when the shape / view cannot use the tensor-core kernel.
+bool conv_tc_supported(const TensorRef &in, const ConvGeom &g);
+// Chooses the tiling; sm_count and target_ctas steer bn / split_k.  Does not touch the device.
+void conv_tc_choose(const ConvGeom &g, int sm_count, int concurrency_hint, ConvTcPlan *plan);
+// Encodes the two tensor maps (needs final device addresses).  Returns a CUDA driver error text or nullptr.
+const char *conv_tc_encode(const ConvTcParams &p, ConvTcPlan *plan);
+// Raises the kernel's dynamic shared-memory limit; call once per device before the first launch.
+cudaError_t conv_tc_prepare();
+void launch_conv_tc(const ConvTcParams &p, const ConvTcPlan &plan, cudaStream_t stream);
+size_t conv_tc_packed_floats(const ConvGeom &g, const ConvTcPlan &plan);
+// Host-side packing of OIHW weights into the tensor-core layout (rounds to TF32, nearest even).
+void conv_tc_pack_weights(const float *oihw, const ConvGeom &g, const ConvTcPlan &plan, float *packed);
+// Host-side packing for the CUDA-core kernels.
+void conv_direct_pack_weights(const float *oihw, const ConvGeom &g, float *packed);   // [tap][Cin/g][Cout]
+void conv_depthwise_pack_weights(const float *oihw, const ConvGeom &g, float *packed); // [tap][C]
+
+}  // namespace ios

@@ -1,0 +1,76 @@
+// Lowering of a scheduled Model to a list of kernel launches over one device arena.
+//
+// Replaces Graph::map / unmap and the per-operator map() methods of the reference
+// (src/ios/ios_runtime.cu:1273-1285, 1318-1327, 263-307, 639-651, 700-717, 776-787), which issue
+// one cudaMalloc per operator output and per assembled input:
+//  * every tensor is a channel window of an NHWC buffer inside ONE arena, sized by a dry lowering
+//    pass, so building a plan performs no allocation once the arena has grown;
+//  * a value that is a channel slice is a pointer offset (at every batch size, not only batch 1);
+//  * a concat whose terms are whole operator outputs is performed by placement: the producers are
+//    given their window of the concat buffer as output, so no copy kernel runs;
+//  * other assembled inputs (sums, partial slices) are built by one sum/copy launch per term,
+//    fused with the consumer when the consumer is an element-wise operator.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <string>
+#include <vector>
+
+#include "graph.h"
+#include "kernels.h"
+
+namespace ios {
+
+struct Options {
+    bool tf32 = true;           // precision: tf32 (tensor cores) or fp32 (CUDA cores)
+    bool use_graph = true;      // executor: CUDA graph or plain streams
+    bool allow_tc = true;       // conv: auto or direct
+    int force_split_k = 0;      // testing aid: > 0 overrides the split-K choice
+};
+
+enum class StepKind { SumAct, Pool, ConvTc, ConvDirect, ConvDepthwise };
+
+struct Step {
+    StepKind kind;
+    int stage = 0, group = 0;
+    int op = -1;                // operator that caused the launch (reporting)
+    bool vec4 = false;
+    SumActParams sum;
+    PoolParams pool;
+    ConvDirectParams direct;
+    ConvTcParams tc;
+    ConvTcPlan tcplan;
+};
+
+struct ConvSlot {               // where a convolution's parameters live in the arena
+    int op;
+    StepKind impl;
+    ConvGeom geom;
+    ConvTcPlan tcplan;
+    size_t weight_offset, weight_floats;
+    size_t bias_offset;
+};
+
+struct Plan {
+    Model model;
+    Options options;
+    std::vector<Step> steps;               // in stage, group, launch order
+    std::vector<ConvSlot> convs;
+    std::vector<TensorRef> tensors;        // output window of every operator
+    std::vector<size_t> input_offsets;     // arena offset of every placeholder buffer
+    size_t arena_bytes = 0;                // activations + workspaces + weights + staging
+    size_t zero_begin = 0, zero_bytes = 0; // split-K counters: must start at zero
+    size_t staging_in_offset = 0, staging_out_offset = 0;   // NCHW staging for host transfers
+    size_t error_flag_offset = 0;
+    size_t workspace_bytes = 0;
+    bool input_round_tf32 = false;
+    int launches_per_forward = 0;
+    int max_groups = 1;
+};
+
+// Two-pass construction: plan_layout() sizes the arena (no device access), plan_bind() lowers
+// against the real base address, encodes tensor maps.  Both throw GraphError / std::runtime_error.
+void plan_layout(Plan *plan, int sm_count);
+void plan_bind(Plan *plan, char *arena_base, int sm_count);
+
+}  // namespace ios

@@ -1,0 +1,800 @@
+// Stage executor, latency measurement and the C-ABI of libios_runtime.so.
+//
+// Counterpart of Graph::forward, measure_latency, measure_stage_latency and the four extern "C"
+// functions of the reference (src/ios/ios_runtime.cu:1297-1315, 1328-1455, 1478-1519), rebuilt
+// around a launch list and CUDA graphs:
+//  * group j of a stage is issued on stream j; stream 0 is the spine: a multi-group stage forks the
+//    other streams off an event on stream 0 and joins them back before the next stage, so stage
+//    boundaries cost event edges instead of the reference's cudaDeviceSynchronize (:1309-1312);
+//  * a whole forward (or `number` repetitions of a candidate stage) is captured once into a CUDA
+//    graph and replayed, which removes the per-kernel host launch cost that dominates batch 1;
+//  * all device memory of a plan comes from one grow-only arena per process, so the thousands of
+//    stage_latency calls of a schedule search allocate nothing after the first few.
+// Errors never terminate the process: every entry point catches, records a message for
+// ios_last_error() and returns a status.
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <memory>
+#include <mutex>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "../../include/ios_runtime.h"
+#include "graph.h"
+#include "kernels.h"
+#include "plan.h"
+
+namespace ios {
+namespace {
+
+thread_local std::string g_last_error;
+std::mutex g_mutex;              // the process-wide arena and option block are shared
+Options g_options;
+int g_device = 0;
+
+struct CudaError : std::runtime_error {
+    explicit CudaError(const std::string &what) : std::runtime_error(what) {}
+};
+struct TimeoutError : std::runtime_error {
+    explicit TimeoutError(const std::string &what) : std::runtime_error(what) {}
+};
+struct ArgumentError : std::runtime_error {
+    explicit ArgumentError(const std::string &what) : std::runtime_error(what) {}
+};
+struct MissingWeights : std::runtime_error {
+    explicit MissingWeights(const std::string &what) : std::runtime_error(what) {}
+};
+
+#define CUDA_OK(expr)                                                                                   \
+    do {                                                                                                \
+        cudaError_t err__ = (expr);                                                                     \
+        if (err__ != cudaSuccess)                                                                       \
+            throw CudaError(std::string(#expr) + ": " + cudaGetErrorString(err__));                     \
+    } while (0)
+
+// ---- device context: streams, events, arena ------------------------------------------------
+struct DeviceContext {
+    int device = -1;
+    int sm_count = 148;
+    std::vector<cudaStream_t> streams;
+    std::vector<cudaEvent_t> events;       // fork / join edges, reused by every plan
+    cudaEvent_t t_start = nullptr, t_end = nullptr;
+    char *arena = nullptr;
+    size_t arena_capacity = 0;
+
+    void init(int dev) {
+        if (device == dev) return;
+        release();
+        int count = 0;
+        cudaError_t err = cudaGetDeviceCount(&count);
+        if (err != cudaSuccess || count == 0)
+            throw CudaError("no CUDA device is available: this library has no CPU path (" +
+                            std::string(err == cudaSuccess ? "device count is 0" : cudaGetErrorString(err)) + ")");
+        if (dev < 0 || dev >= count) throw ArgumentError("device index out of range");
+        CUDA_OK(cudaSetDevice(dev));
+        cudaDeviceProp prop;
+        CUDA_OK(cudaGetDeviceProperties(&prop, dev));
+        if (prop.major < 10)
+            throw CudaError(std::string("device '") + prop.name + "' is not sm_100: the kernels are built for B200 only");
+        sm_count = prop.multiProcessorCount;
+        CUDA_OK(conv_tc_prepare());
+        CUDA_OK(cudaEventCreate(&t_start));
+        CUDA_OK(cudaEventCreate(&t_end));
+        device = dev;
+    }
+    void need_streams(int n) {
+        while (int(streams.size()) < n) {
+            cudaStream_t s;
+            CUDA_OK(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+            streams.push_back(s);
+        }
+    }
+    cudaEvent_t event(size_t i) {
+        while (events.size() <= i) {
+            cudaEvent_t e;
+            CUDA_OK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+            events.push_back(e);
+        }
+        return events[i];
+    }
+    char *need_arena(size_t bytes) {
+        if (bytes > arena_capacity) {
+            if (arena) {
+                CUDA_OK(cudaDeviceSynchronize());
+                CUDA_OK(cudaFree(arena));
+                arena = nullptr;
+                arena_capacity = 0;
+            }
+            size_t want = bytes + bytes / 4;
+            want = (want + (size_t(1) << 21) - 1) >> 21 << 21;
+            cudaError_t err = cudaMalloc(&arena, want);
+            if (err != cudaSuccess) {
+                cudaGetLastError();
+                want = (bytes + 4095) / 4096 * 4096;
+                CUDA_OK(cudaMalloc(&arena, want));
+            }
+            arena_capacity = want;
+        }
+        return arena;
+    }
+    void release() {
+        if (device < 0) return;
+        cudaSetDevice(device);
+        for (cudaStream_t s : streams) cudaStreamDestroy(s);
+        for (cudaEvent_t e : events) cudaEventDestroy(e);
+        if (t_start) cudaEventDestroy(t_start);
+        if (t_end) cudaEventDestroy(t_end);
+        if (arena) cudaFree(arena);
+        streams.clear();
+        events.clear();
+        t_start = t_end = nullptr;
+        arena = nullptr;
+        arena_capacity = 0;
+        device = -1;
+    }
+};
+
+DeviceContext g_ctx;
+
+DeviceContext &context() {
+    g_ctx.init(g_device);
+    CUDA_OK(cudaSetDevice(g_device));
+    return g_ctx;
+}
+
+// ---- issuing a plan -------------------------------------------------------------------------
+void launch_step(const Step &s, cudaStream_t stream) {
+    switch (s.kind) {
+        case StepKind::SumAct: launch_sum_act(s.sum, s.vec4, stream); break;
+        case StepKind::Pool: launch_pool(s.pool, stream); break;
+        case StepKind::ConvTc: launch_conv_tc(s.tc, s.tcplan, stream); break;
+        case StepKind::ConvDirect: launch_conv_direct(s.direct, stream); break;
+        case StepKind::ConvDepthwise: launch_conv_depthwise(s.direct, stream); break;
+    }
+}
+
+// Issues one forward on the context's streams.  stage_marks (optional) receives one timing event
+// per stage, recorded on stream 0 after the stage's groups have joined.
+void issue_forward(DeviceContext &ctx, const Plan &plan, const std::vector<cudaEvent_t> *stage_marks) {
+    ctx.need_streams(plan.max_groups);
+    cudaStream_t spine = ctx.streams[0];
+    size_t next = 0;
+    size_t ev = 0;
+    const auto &stages = plan.model.stages;
+    for (size_t si = 0; si < stages.size(); ++si) {
+        const int groups = int(stages[si].size());
+        if (groups > 1) {
+            cudaEvent_t fork = ctx.event(ev++);
+            CUDA_OK(cudaEventRecord(fork, spine));
+            for (int g = 1; g < groups; ++g) CUDA_OK(cudaStreamWaitEvent(ctx.streams[g], fork, 0));
+        }
+        // steps are stored stage by stage, group by group
+        for (int g = 0; g < groups; ++g) {
+            while (next < plan.steps.size() && plan.steps[next].stage == int(si) && plan.steps[next].group == g) {
+                launch_step(plan.steps[next], ctx.streams[g]);
+                ++next;
+            }
+        }
+        for (int g = 1; g < groups; ++g) {
+            cudaEvent_t done = ctx.event(ev++);
+            CUDA_OK(cudaEventRecord(done, ctx.streams[g]));
+            CUDA_OK(cudaStreamWaitEvent(spine, done, 0));
+        }
+        if (stage_marks) CUDA_OK(cudaEventRecord((*stage_marks)[si], spine));
+    }
+    CUDA_OK(cudaGetLastError());
+}
+
+struct GraphExec {
+    cudaGraphExec_t exec = nullptr;
+    ~GraphExec() {
+        if (exec) cudaGraphExecDestroy(exec);
+    }
+};
+
+template <class F>
+void capture(DeviceContext &ctx, GraphExec *out, F &&body) {
+    cudaStream_t spine = ctx.streams[0];
+    cudaGraph_t graph = nullptr;
+    CUDA_OK(cudaStreamBeginCapture(spine, cudaStreamCaptureModeThreadLocal));
+    try {
+        body();
+    } catch (...) {
+        cudaStreamEndCapture(spine, &graph);
+        if (graph) cudaGraphDestroy(graph);
+        cudaGetLastError();
+        throw;
+    }
+    CUDA_OK(cudaStreamEndCapture(spine, &graph));
+    cudaError_t err = cudaGraphInstantiate(&out->exec, graph, 0);
+    cudaGraphDestroy(graph);
+    CUDA_OK(err);
+}
+
+// ---- building a bound plan in the shared arena ---------------------------------------------
+struct HostWeights {
+    int count = 0;
+    char **names = nullptr;
+    float **filters = nullptr;
+    float **biases = nullptr;
+};
+
+void check_error_flag(const Plan &plan, char *base) {
+    int flag = 0;
+    CUDA_OK(cudaMemcpy(&flag, base + plan.error_flag_offset, sizeof flag, cudaMemcpyDeviceToHost));
+    if (flag != 0) {
+        CUDA_OK(cudaMemset(base + plan.error_flag_offset, 0, sizeof(int)));
+        throw TimeoutError("a bounded wait inside the convolution kernel ran out (code " + std::to_string(flag) + ")");
+    }
+}
+
+// Packs and uploads (or synthesises) the parameters of every convolution of a bound plan.
+void load_parameters(const Plan &plan, char *base, const HostWeights *host, cudaStream_t stream) {
+    std::vector<float> packed;
+    uint32_t seed = 1;
+    for (const ConvSlot &slot : plan.convs) {
+        const Op &op = plan.model.ops[slot.op];
+        float *w_dev = reinterpret_cast<float *>(base + slot.weight_offset);
+        float *b_dev = reinterpret_cast<float *>(base + slot.bias_offset);
+        const int fan_in = slot.geom.kh * slot.geom.kw * (slot.geom.Cin / slot.geom.groups);
+        if (!host) {
+            // timing run: bounded pseudo-random parameters keep the activations finite
+            launch_fill(w_dev, long(slot.weight_floats), seed++, std::sqrt(3.0f / float(fan_in)), stream);
+            launch_fill(b_dev, slot.geom.Cout, seed++, 0.05f, stream);
+            continue;
+        }
+        int found = -1;
+        for (int i = 0; i < host->count; ++i)
+            if (host->names[i] && op.name == host->names[i]) {
+                found = i;
+                break;
+            }
+        if (found < 0 || !host->filters[found] || !host->biases[found])
+            throw MissingWeights("convolution '" + op.name + "' was given no weight or bias");
+        packed.resize(slot.weight_floats);
+        switch (slot.impl) {
+            case StepKind::ConvTc: conv_tc_pack_weights(host->filters[found], slot.geom, slot.tcplan, packed.data()); break;
+            case StepKind::ConvDepthwise: conv_depthwise_pack_weights(host->filters[found], slot.geom, packed.data()); break;
+            default: conv_direct_pack_weights(host->filters[found], slot.geom, packed.data()); break;
+        }
+        CUDA_OK(cudaMemcpyAsync(w_dev, packed.data(), slot.weight_floats * sizeof(float), cudaMemcpyHostToDevice, stream));
+        CUDA_OK(cudaStreamSynchronize(stream));   // `packed` is reused for the next convolution
+        CUDA_OK(cudaMemcpyAsync(b_dev, host->biases[found], size_t(slot.geom.Cout) * sizeof(float), cudaMemcpyHostToDevice, stream));
+    }
+    CUDA_OK(cudaStreamSynchronize(stream));
+}
+
+// Lays the plan out, binds it to `base` (or to the shared arena when base is null).
+char *bind_plan(DeviceContext &ctx, Plan *plan, char *base) {
+    plan->options = g_options;
+    plan_layout(plan, ctx.sm_count);
+    if (!base) base = ctx.need_arena(plan->arena_bytes);
+    plan_bind(plan, base, ctx.sm_count);
+    ctx.need_streams(plan->max_groups);
+    CUDA_OK(cudaMemsetAsync(base + plan->error_flag_offset, 0, 256, ctx.streams[0]));
+    if (plan->zero_bytes) CUDA_OK(cudaMemsetAsync(base + plan->zero_begin, 0, plan->zero_bytes, ctx.streams[0]));
+    return base;
+}
+
+void fill_inputs(DeviceContext &ctx, const Plan &plan, char *base) {
+    uint32_t seed = 1000;
+    for (size_t i = 0; i < plan.model.placeholders.size(); ++i) {
+        const TensorRef &t = plan.tensors[plan.model.placeholders[i]];
+        launch_fill(reinterpret_cast<float *>(base + plan.input_offsets[i]), t.pixels() * t.pitch, seed++, 1.0f, ctx.streams[0]);
+    }
+}
+
+void fill_nan(float *dst, int count) {
+    if (!dst) return;
+    for (int i = 0; i < count; ++i) dst[i] = std::nanf("");
+}
+
+// ---- measurement ----------------------------------------------------------------------------
+void measure_graph(const Model &model_in, int warmup, int number, int repeat, bool profile_stage, float *results,
+                   float *stage_results) {
+    if (!results) throw ArgumentError("results must not be NULL");
+    if (number <= 0 || repeat <= 0 || warmup < 0) throw ArgumentError("warmup, number and repeat must be positive");
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceContext &ctx = context();
+    Plan plan;
+    plan.model = model_in;
+    char *base = bind_plan(ctx, &plan, nullptr);
+    load_parameters(plan, base, nullptr, ctx.streams[0]);
+    fill_inputs(ctx, plan, base);
+    cudaStream_t spine = ctx.streams[0];
+    const size_t num_stages = plan.model.stages.size();
+
+    std::vector<cudaEvent_t> marks;
+    GraphExec exec;
+    const bool replay = plan.options.use_graph && !profile_stage;
+    if (profile_stage) {
+        if (!stage_results) throw ArgumentError("stage_results must not be NULL when stages are profiled");
+        marks.resize(num_stages);
+        for (auto &e : marks) CUDA_OK(cudaEventCreate(&e));
+    }
+    auto forward = [&]() {
+        if (replay) CUDA_OK(cudaGraphLaunch(exec.exec, spine));
+        else issue_forward(ctx, plan, profile_stage ? &marks : nullptr);
+    };
+    try {
+        if (replay) capture(ctx, &exec, [&]() { issue_forward(ctx, plan, nullptr); });
+        for (int i = 0; i < warmup; ++i) forward();
+        CUDA_OK(cudaDeviceSynchronize());
+        check_error_flag(plan, base);
+        for (int i = 0; i < repeat; ++i) {
+            double total = 0.0;
+            std::vector<double> per_stage(num_stages, 0.0);
+            for (int t = 0; t < number; ++t) {
+                CUDA_OK(cudaDeviceSynchronize());
+                CUDA_OK(cudaEventRecord(ctx.t_start, spine));
+                forward();
+                CUDA_OK(cudaEventRecord(ctx.t_end, spine));
+                CUDA_OK(cudaDeviceSynchronize());
+                float ms = 0.f;
+                CUDA_OK(cudaEventElapsedTime(&ms, ctx.t_start, ctx.t_end));
+                total += ms;
+                if (profile_stage)
+                    for (size_t j = 0; j < num_stages; ++j) {
+                        CUDA_OK(cudaEventElapsedTime(&ms, j == 0 ? ctx.t_start : marks[j - 1], marks[j]));
+                        per_stage[j] += ms;
+                    }
+            }
+            results[i] = float(total / number);
+            if (profile_stage)
+                for (size_t j = 0; j < num_stages; ++j) stage_results[size_t(i) * num_stages + j] = float(per_stage[j] / number);
+        }
+        check_error_flag(plan, base);
+    } catch (...) {
+        for (auto &e : marks) cudaEventDestroy(e);
+        throw;
+    }
+    for (auto &e : marks) cudaEventDestroy(e);
+}
+
+// One candidate stage: `number` repetitions are captured into ONE graph, so a sample measures the
+// stage as it will run inside a captured schedule (fork, kernels, join), not a host launch each.
+void measure_stage(const Model &model_in, int warmup, int number, int repeat, float *results) {
+    if (!results) throw ArgumentError("results must not be NULL");
+    if (number <= 0 || repeat <= 0 || warmup < 0) throw ArgumentError("warmup, number and repeat must be positive");
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceContext &ctx = context();
+    Plan plan;
+    plan.model = model_in;
+    char *base = bind_plan(ctx, &plan, nullptr);
+    load_parameters(plan, base, nullptr, ctx.streams[0]);
+    fill_inputs(ctx, plan, base);
+    cudaStream_t spine = ctx.streams[0];
+    GraphExec exec;
+    const bool replay = plan.options.use_graph;
+    if (replay) capture(ctx, &exec, [&]() { for (int t = 0; t < number; ++t) issue_forward(ctx, plan, nullptr); });
+    auto sample = [&]() {
+        if (replay) CUDA_OK(cudaGraphLaunch(exec.exec, spine));
+        else for (int t = 0; t < number; ++t) issue_forward(ctx, plan, nullptr);
+    };
+    for (int i = 0; i < (warmup + number - 1) / number; ++i) sample();
+    for (int i = 0; i < repeat; ++i) {
+        CUDA_OK(cudaDeviceSynchronize());
+        CUDA_OK(cudaEventRecord(ctx.t_start, spine));
+        sample();
+        CUDA_OK(cudaEventRecord(ctx.t_end, spine));
+        CUDA_OK(cudaDeviceSynchronize());
+        float ms = 0.f;
+        CUDA_OK(cudaEventElapsedTime(&ms, ctx.t_start, ctx.t_end));
+        results[i] = ms / float(number);
+    }
+    check_error_flag(plan, base);
+}
+
+void require_single_group_output(const Model &model) {
+    if (!model.output_is_single_group)
+        throw GraphError("the last stage must have exactly one group: its last operator is the graph output");
+}
+
+void run_inference(const Model &model_in, const float *input, const HostWeights &weights, float *output) {
+    if (!input || !output) throw ArgumentError("input and output must not be NULL");
+    require_single_group_output(model_in);
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceContext &ctx = context();
+    Plan plan;
+    plan.model = model_in;
+    char *base = bind_plan(ctx, &plan, nullptr);
+    cudaStream_t spine = ctx.streams[0];
+    load_parameters(plan, base, &weights, spine);
+    const Op &in_op = plan.model.ops[plan.model.placeholders[0]];
+    const Op &out_op = plan.model.ops[plan.model.output];
+    const size_t in_bytes = size_t(plan.model.batch) * in_op.C * in_op.H * in_op.W * sizeof(float);
+    const size_t out_bytes = size_t(plan.model.batch) * out_op.C * out_op.H * out_op.W * sizeof(float);
+    float *stage_in = reinterpret_cast<float *>(base + plan.staging_in_offset);
+    float *stage_out = reinterpret_cast<float *>(base + plan.staging_out_offset);
+    CUDA_OK(cudaMemcpyAsync(stage_in, input, in_bytes, cudaMemcpyHostToDevice, spine));
+    launch_nchw_to_nhwc(stage_in, plan.tensors[plan.model.placeholders[0]], plan.input_round_tf32, spine);
+    issue_forward(ctx, plan, nullptr);
+    launch_nhwc_to_nchw(plan.tensors[plan.model.output], stage_out, spine);
+    CUDA_OK(cudaMemcpyAsync(output, stage_out, out_bytes, cudaMemcpyDeviceToHost, spine));
+    CUDA_OK(cudaDeviceSynchronize());
+    check_error_flag(plan, base);
+}
+
+// ---- status plumbing -------------------------------------------------------------------------
+template <class F>
+int guarded(F &&body) {
+    try {
+        body();
+        g_last_error.clear();
+        return IOS_OK;
+    } catch (const JsonError &e) {
+        g_last_error = e.what();
+        return IOS_ERR_JSON;
+    } catch (const GraphError &e) {
+        g_last_error = e.what();
+        return std::strncmp(e.what(), "limit:", 6) == 0 ? IOS_ERR_LIMIT : IOS_ERR_GRAPH;
+    } catch (const ArgumentError &e) {
+        g_last_error = e.what();
+        return IOS_ERR_ARGUMENT;
+    } catch (const TimeoutError &e) {
+        g_last_error = e.what();
+        return IOS_ERR_TIMEOUT;
+    } catch (const MissingWeights &e) {
+        g_last_error = e.what();
+        return IOS_ERR_MISSING;
+    } catch (const CudaError &e) {
+        g_last_error = e.what();
+        cudaGetLastError();
+        return IOS_ERR_CUDA;
+    } catch (const std::exception &e) {
+        g_last_error = e.what();
+        return IOS_ERR_CUDA;
+    }
+}
+
+}  // namespace
+
+// ---- engine ----------------------------------------------------------------------------------
+struct EngineImpl {
+    Plan plan;
+    int device = 0;
+    char *base = nullptr;
+    size_t bytes = 0;
+    GraphExec exec;            // staging -> NHWC, forward, NHWC -> staging
+    GraphExec exec_core;       // forward only (resident input)
+    size_t in_bytes = 0, out_bytes = 0;
+    ~EngineImpl() {
+        if (base) {
+            cudaSetDevice(device);
+            cudaFree(base);
+        }
+    }
+};
+
+}  // namespace ios
+
+struct ios_engine {
+    ios::EngineImpl impl;
+};
+
+using namespace ios;
+
+extern "C" {
+
+const char *ios_last_error(void) { return g_last_error.c_str(); }
+
+int ios_graph_latency(const char *graph_json, int batch_size, int warmup, int number, int repeat,
+                      int profile_stage_latency, float *results, float *stage_results) {
+    int status = guarded([&]() {
+        Model model = model_from_graph(Json::parse(graph_json), batch_size);
+        measure_graph(model, warmup, number, repeat, profile_stage_latency != 0, results, stage_results);
+    });
+    if (status != IOS_OK && repeat > 0) fill_nan(results, repeat);
+    return status;
+}
+
+int ios_block_latency(const char *block_json, int batch_size, int warmup, int number, int repeat,
+                      int profile_stage_latency, float *results, float *stage_results) {
+    int status = guarded([&]() {
+        Model model = model_from_block(Json::parse(block_json), batch_size);
+        measure_graph(model, warmup, number, repeat, profile_stage_latency != 0, results, stage_results);
+    });
+    if (status != IOS_OK && repeat > 0) fill_nan(results, repeat);
+    return status;
+}
+
+int ios_stage_latency(const char *stage_json, const char *input_json, int batch_size, int warmup, int number,
+                      int repeat, int profile_stage_latency, float *results, float *stage_results) {
+    (void)stage_results;   // the reference never writes it for a stage (src/ios/ios_runtime.cu:1329)
+    int status = guarded([&]() {
+        if (profile_stage_latency) throw ArgumentError("a single stage cannot be profiled per stage");
+        Model model = model_from_stage(Json::parse(stage_json), Json::parse(input_json), batch_size);
+        measure_stage(model, warmup, number, repeat, results);
+    });
+    if (status != IOS_OK && repeat > 0) fill_nan(results, repeat);
+    return status;
+}
+
+int ios_graph_inference(const char *graph_json, int batch_size, const float *input, int num_convs, char **conv_names,
+                        float **filter_data, float **bias_data, float *output) {
+    return guarded([&]() {
+        if (num_convs < 0 || (num_convs > 0 && (!conv_names || !filter_data || !bias_data)))
+            throw ArgumentError("conv_names, filter_data and bias_data must hold num_convs entries");
+        Model model = model_from_graph(Json::parse(graph_json), batch_size);
+        HostWeights hw{num_convs, conv_names, filter_data, bias_data};
+        run_inference(model, input, hw, output);
+    });
+}
+
+void graph_latency(const char *graph_json, int batch_size, int warmup, int number, int repeat,
+                   int profile_stage_latency, float *results, float *stage_results) {
+    int status = ios_graph_latency(graph_json, batch_size, warmup, number, repeat, profile_stage_latency, results, stage_results);
+    if (status != IOS_OK) std::fprintf(stderr, "ios_runtime: graph_latency failed: %s\n", g_last_error.c_str());
+}
+void block_latency(const char *block_json, int batch_size, int warmup, int number, int repeat,
+                   int profile_stage_latency, float *results, float *stage_results) {
+    int status = ios_block_latency(block_json, batch_size, warmup, number, repeat, profile_stage_latency, results, stage_results);
+    if (status != IOS_OK) std::fprintf(stderr, "ios_runtime: block_latency failed: %s\n", g_last_error.c_str());
+}
+void stage_latency(const char *stage_json, const char *input_json, int batch_size, int warmup, int number, int repeat,
+                   int profile_stage_latency, float *results, float *stage_results) {
+    int status = ios_stage_latency(stage_json, input_json, batch_size, warmup, number, repeat, profile_stage_latency, results, stage_results);
+    if (status != IOS_OK) std::fprintf(stderr, "ios_runtime: stage_latency failed: %s\n", g_last_error.c_str());
+}
+void graph_inference(const char *graph_json, int batch_size, float *input, int num_convs, char **conv_names,
+                     float **filter_data, float **bias_data, float *output) {
+    int status = ios_graph_inference(graph_json, batch_size, input, num_convs, conv_names, filter_data, bias_data, output);
+    if (status != IOS_OK) std::fprintf(stderr, "ios_runtime: graph_inference failed: %s\n", g_last_error.c_str());
+}
+
+int ios_set_option(const char *key, const char *value) {
+    return guarded([&]() {
+        if (!key || !value) throw ArgumentError("key and value must not be NULL");
+        std::lock_guard<std::mutex> lock(g_mutex);
+        const std::string k = key, v = value;
+        if (k == "precision" && (v == "tf32" || v == "fp32")) g_options.tf32 = v == "tf32";
+        else if (k == "executor" && (v == "graph" || v == "streams")) g_options.use_graph = v == "graph";
+        else if (k == "conv" && (v == "auto" || v == "direct")) g_options.allow_tc = v == "auto";
+        else if (k == "split_k") g_options.force_split_k = std::atoi(value);
+        else throw ArgumentError("unknown option " + k + "=" + v);
+    });
+}
+
+int ios_get_option(const char *key, char *value, int capacity) {
+    return guarded([&]() {
+        if (!key || !value || capacity <= 0) throw ArgumentError("key and value must not be NULL");
+        const std::string k = key;
+        std::string v;
+        if (k == "precision") v = g_options.tf32 ? "tf32" : "fp32";
+        else if (k == "executor") v = g_options.use_graph ? "graph" : "streams";
+        else if (k == "conv") v = g_options.allow_tc ? "auto" : "direct";
+        else if (k == "split_k") v = std::to_string(g_options.force_split_k);
+        else throw ArgumentError("unknown option " + k);
+        std::snprintf(value, size_t(capacity), "%s", v.c_str());
+    });
+}
+
+int ios_set_device(int device) {
+    return guarded([&]() {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        int count = 0;
+        CUDA_OK(cudaGetDeviceCount(&count));
+        if (device < 0 || device >= count) throw ArgumentError("device index out of range");
+        g_device = device;
+    });
+}
+
+int ios_device_count(int *count) {
+    return guarded([&]() {
+        if (!count) throw ArgumentError("count must not be NULL");
+        CUDA_OK(cudaGetDeviceCount(count));
+    });
+}
+
+int ios_engine_create(const char *graph_json, int batch_size, int num_convs, char **conv_names, float **filter_data,
+                      float **bias_data, ios_engine **engine) {
+    return guarded([&]() {
+        if (!engine) throw ArgumentError("engine must not be NULL");
+        *engine = nullptr;
+        Model model = model_from_graph(Json::parse(graph_json), batch_size);
+        require_single_group_output(model);
+        std::lock_guard<std::mutex> lock(g_mutex);
+        DeviceContext &ctx = context();
+        std::unique_ptr<ios_engine> holder(new ios_engine);
+        EngineImpl &e = holder->impl;
+        e.device = g_device;
+        e.plan.model = model;
+        e.plan.options = g_options;
+        plan_layout(&e.plan, ctx.sm_count);
+        e.bytes = e.plan.arena_bytes;
+        CUDA_OK(cudaMalloc(&e.base, e.bytes));
+        bind_plan(ctx, &e.plan, e.base);
+        cudaStream_t spine = ctx.streams[0];
+        if (filter_data && bias_data && conv_names) {
+            HostWeights hw{num_convs, conv_names, filter_data, bias_data};
+            load_parameters(e.plan, e.base, &hw, spine);
+        } else {
+            load_parameters(e.plan, e.base, nullptr, spine);
+        }
+        fill_inputs(ctx, e.plan, e.base);
+        const Op &in_op = e.plan.model.ops[e.plan.model.placeholders[0]];
+        const Op &out_op = e.plan.model.ops[e.plan.model.output];
+        e.in_bytes = size_t(batch_size) * in_op.C * in_op.H * in_op.W * sizeof(float);
+        e.out_bytes = size_t(batch_size) * out_op.C * out_op.H * out_op.W * sizeof(float);
+        float *stage_in = reinterpret_cast<float *>(e.base + e.plan.staging_in_offset);
+        float *stage_out = reinterpret_cast<float *>(e.base + e.plan.staging_out_offset);
+        if (e.plan.options.use_graph) {
+            capture(ctx, &e.exec, [&]() {
+                launch_nchw_to_nhwc(stage_in, e.plan.tensors[e.plan.model.placeholders[0]], e.plan.input_round_tf32, spine);
+                issue_forward(ctx, e.plan, nullptr);
+                launch_nhwc_to_nchw(e.plan.tensors[e.plan.model.output], stage_out, spine);
+            });
+            capture(ctx, &e.exec_core, [&]() { issue_forward(ctx, e.plan, nullptr); });
+        }
+        CUDA_OK(cudaDeviceSynchronize());
+        *engine = holder.release();
+    });
+}
+
+int ios_engine_destroy(ios_engine *engine) {
+    return guarded([&]() {
+        if (!engine) return;
+        std::lock_guard<std::mutex> lock(g_mutex);
+        cudaSetDevice(engine->impl.device);
+        cudaDeviceSynchronize();
+        delete engine;
+    });
+}
+
+static void engine_forward(DeviceContext &ctx, EngineImpl &e, bool with_layout) {
+    cudaStream_t spine = ctx.streams[0];
+    float *stage_in = reinterpret_cast<float *>(e.base + e.plan.staging_in_offset);
+    float *stage_out = reinterpret_cast<float *>(e.base + e.plan.staging_out_offset);
+    if (e.plan.options.use_graph) {
+        CUDA_OK(cudaGraphLaunch(with_layout ? e.exec.exec : e.exec_core.exec, spine));
+        return;
+    }
+    if (with_layout)
+        launch_nchw_to_nhwc(stage_in, e.plan.tensors[e.plan.model.placeholders[0]], e.plan.input_round_tf32, spine);
+    issue_forward(ctx, e.plan, nullptr);
+    if (with_layout) launch_nhwc_to_nchw(e.plan.tensors[e.plan.model.output], stage_out, spine);
+}
+
+int ios_engine_run(ios_engine *engine, const float *input, float *output) {
+    return guarded([&]() {
+        if (!engine || !input || !output) throw ArgumentError("engine, input and output must not be NULL");
+        EngineImpl &e = engine->impl;
+        std::lock_guard<std::mutex> lock(g_mutex);
+        g_device = e.device;
+        DeviceContext &ctx = context();
+        cudaStream_t spine = ctx.streams[0];
+        CUDA_OK(cudaMemcpyAsync(e.base + e.plan.staging_in_offset, input, e.in_bytes, cudaMemcpyHostToDevice, spine));
+        engine_forward(ctx, e, true);
+        CUDA_OK(cudaMemcpyAsync(output, e.base + e.plan.staging_out_offset, e.out_bytes, cudaMemcpyDeviceToHost, spine));
+        CUDA_OK(cudaStreamSynchronize(spine));
+        check_error_flag(e.plan, e.base);
+    });
+}
+
+int ios_engine_set_input(ios_engine *engine, const float *input) {
+    return guarded([&]() {
+        if (!engine || !input) throw ArgumentError("engine and input must not be NULL");
+        EngineImpl &e = engine->impl;
+        std::lock_guard<std::mutex> lock(g_mutex);
+        g_device = e.device;
+        DeviceContext &ctx = context();
+        cudaStream_t spine = ctx.streams[0];
+        float *stage_in = reinterpret_cast<float *>(e.base + e.plan.staging_in_offset);
+        CUDA_OK(cudaMemcpyAsync(stage_in, input, e.in_bytes, cudaMemcpyHostToDevice, spine));
+        launch_nchw_to_nhwc(stage_in, e.plan.tensors[e.plan.model.placeholders[0]], e.plan.input_round_tf32, spine);
+        CUDA_OK(cudaStreamSynchronize(spine));
+    });
+}
+
+int ios_engine_get_output(ios_engine *engine, float *output) {
+    return guarded([&]() {
+        if (!engine || !output) throw ArgumentError("engine and output must not be NULL");
+        EngineImpl &e = engine->impl;
+        std::lock_guard<std::mutex> lock(g_mutex);
+        g_device = e.device;
+        DeviceContext &ctx = context();
+        cudaStream_t spine = ctx.streams[0];
+        float *stage_out = reinterpret_cast<float *>(e.base + e.plan.staging_out_offset);
+        launch_nhwc_to_nchw(e.plan.tensors[e.plan.model.output], stage_out, spine);
+        CUDA_OK(cudaMemcpyAsync(output, stage_out, e.out_bytes, cudaMemcpyDeviceToHost, spine));
+        CUDA_OK(cudaStreamSynchronize(spine));
+        check_error_flag(e.plan, e.base);
+    });
+}
+
+int ios_engine_time(ios_engine *engine, int iters, float *ms_per_iter) {
+    return guarded([&]() {
+        if (!engine || !ms_per_iter || iters <= 0) throw ArgumentError("engine, ms_per_iter must not be NULL and iters > 0");
+        EngineImpl &e = engine->impl;
+        std::lock_guard<std::mutex> lock(g_mutex);
+        g_device = e.device;
+        DeviceContext &ctx = context();
+        cudaStream_t spine = ctx.streams[0];
+        CUDA_OK(cudaStreamSynchronize(spine));
+        CUDA_OK(cudaEventRecord(ctx.t_start, spine));
+        for (int i = 0; i < iters; ++i) engine_forward(ctx, e, false);
+        CUDA_OK(cudaEventRecord(ctx.t_end, spine));
+        CUDA_OK(cudaStreamSynchronize(spine));
+        float ms = 0.f;
+        CUDA_OK(cudaEventElapsedTime(&ms, ctx.t_start, ctx.t_end));
+        *ms_per_iter = ms / float(iters);
+        check_error_flag(e.plan, e.base);
+    });
+}
+
+int ios_engine_describe(ios_engine *engine, char *text, int capacity) {
+    return guarded([&]() {
+        if (!engine || !text || capacity <= 0) throw ArgumentError("engine and text must not be NULL");
+        const EngineImpl &e = engine->impl;
+        const Plan &p = e.plan;
+        int n_tc = 0, n_direct = 0, n_dw = 0, n_sum = 0, n_pool = 0, n_split = 0;
+        for (const Step &s : p.steps) {
+            switch (s.kind) {
+                case StepKind::ConvTc: ++n_tc; if (s.tcplan.split_k > 1) ++n_split; break;
+                case StepKind::ConvDirect: ++n_direct; break;
+                case StepKind::ConvDepthwise: ++n_dw; break;
+                case StepKind::SumAct: ++n_sum; break;
+                case StepKind::Pool: ++n_pool; break;
+            }
+        }
+        size_t weight_bytes = 0;
+        for (const ConvSlot &c : p.convs) weight_bytes += (c.weight_floats + c.geom.Cout) * sizeof(float);
+        const Op &out = p.model.ops[p.model.output];
+        std::snprintf(text, size_t(capacity),
+                      "{\"launches\": %d, \"conv_tc\": %d, \"conv_tc_split_k\": %d, \"conv_direct\": %d, \"conv_depthwise\": %d, "
+                      "\"sum_act\": %d, \"pool\": %d, \"stages\": %zu, \"arena_bytes\": %zu, \"workspace_bytes\": %zu, "
+                      "\"weight_bytes\": %zu, \"conv_flops\": %.0f, \"output_shape\": [%d, %d, %d, %d], \"executor\": \"%s\", "
+                      "\"precision\": \"%s\"}",
+                      p.launches_per_forward, n_tc, n_split, n_direct, n_dw, n_sum, n_pool, p.model.stages.size(), e.bytes,
+                      p.workspace_bytes, weight_bytes, p.model.conv_flops(), p.model.batch, out.C, out.H, out.W,
+                      p.options.use_graph ? "graph" : "streams", p.options.tf32 ? "tf32" : "fp32");
+    });
+}
+
+int ios_conv2d(const float *x, const float *w, const float *bias, float *y, int n, int cin, int h, int wdt, int cout,
+               int kh, int kw, int sh, int sw, int ph, int pw, int groups, int act, int impl) {
+    return guarded([&]() {
+        if (!x || !w || !y) throw ArgumentError("x, w and y must not be NULL");
+        if (n <= 0 || cin <= 0 || h <= 0 || wdt <= 0 || cout <= 0 || groups <= 0 || act < 0 || act > 3 || impl < 0 || impl > 2)
+            throw ArgumentError("bad convolution arguments");
+        // a one-operator graph drives exactly the code path a scheduled convolution takes
+        static const char *acts[] = {"identity", "relu", "sigmoid", "tanh"};
+        char json[1024];
+        std::snprintf(json, sizeof json,
+                      "{\"name\":\"conv2d\",\"input\":{\"type\":\"placeholder\",\"name\":\"x\",\"hint_name\":\"x\",\"output_shape\":[%d,%d,%d]},"
+                      "\"blocks\":[{\"enter_name\":\"x\",\"enter_node\":{},\"inner_nodes\":[],\"exit_node\":{\"type\":\"conv\",\"name\":\"y\","
+                      "\"hint_name\":\"y\",\"inputs\":[[[\"x\",0,%d]]],\"out_channels\":%d,\"kernel\":[%d,%d],\"stride\":[%d,%d],"
+                      "\"padding\":[%d,%d],\"groups\":%d,\"act\":\"%s\",\"output_shape\":null},\"stages\":[[[\"y\"]]]}]}",
+                      cin, h, wdt, cin, cout, kh, kw, sh, sw, ph, pw, groups, acts[act]);
+        Model model = model_from_graph(Json::parse(json), n);
+        std::vector<float> zero_bias;
+        if (!bias) zero_bias.assign(size_t(cout), 0.0f);
+        char name[] = "y";
+        char *names[1] = {name};
+        float *filters[1] = {const_cast<float *>(w)};
+        float *biases[1] = {bias ? const_cast<float *>(bias) : zero_bias.data()};
+        HostWeights hw{1, names, filters, biases};
+        Options saved;
+        {
+            std::lock_guard<std::mutex> lock(g_mutex);
+            saved = g_options;
+            if (impl == 1) g_options.allow_tc = false;
+            if (impl == 2) { g_options.allow_tc = true; g_options.tf32 = true; }
+        }
+        try {
+            run_inference(model, x, hw, y);
+        } catch (...) {
+            std::lock_guard<std::mutex> lock(g_mutex);
+            g_options = saved;
+            throw;
+        }
+        std::lock_guard<std::mutex> lock(g_mutex);
+        g_options = saved;
+    });
+}
+
+}  // extern "C"

@@ -1,0 +1,273 @@
+"""
+ctypes front-end of ``libios_runtime.so``.
+
+Same functions, arguments and return shapes as the reference's
+``python/ios/contrib/ios_runtime.py`` (``graph_latency`` :26, ``block_latency`` :53,
+``stage_latency`` :80, ``graph_inference`` :114).  Differences that a caller can observe:
+
+* failures raise ``RuntimeError`` with the library's message instead of ending the interpreter
+  (the reference's ``FatalError`` calls ``exit(1)``);
+* ``graph_inference`` converts its input to C-contiguous float32 first (the reference passes the
+  raw buffer of whatever array it is given, ``ios_runtime.py:126``);
+* there is no CPU path: without a CUDA device every call raises.
+
+``Engine`` is the build-once / run-many handle used for serving and benchmarking.
+"""
+import ctypes
+import json
+import os
+from typing import List
+
+import numpy as np
+
+from ios.ir import Conv, Graph, Block, Node
+from .ctypes_utils import c_string, c_string_list, c_ndarray_list, get_nodes_by_type
+
+cur_dir = os.path.dirname(os.path.abspath(os.path.realpath(__file__)))
+
+libname_list = [
+    'libios_runtime.so',
+    '../libios_runtime.so',
+    '../../libios_runtime.so',
+    '../build/libios_runtime.so',
+    '../../build/libios_runtime.so',
+    '../../../build/libios_runtime.so',
+]
+lib = None
+
+_INT, _FLOATP, _CHARP = ctypes.c_int, ctypes.POINTER(ctypes.c_float), ctypes.c_char_p
+_VOIDPP = ctypes.POINTER(ctypes.c_void_p)
+_LATENCY_ARGS = [_CHARP, _INT, _INT, _INT, _INT, _INT, _FLOATP, _FLOATP]
+
+
+def load_ios_library():
+    """Find and load the runtime next to this package (same search list as the reference, :8-23)."""
+    override = os.environ.get('IOS_RUNTIME_LIBRARY')
+    candidates = [override] if override else [os.path.join(cur_dir, name) for name in libname_list]
+    for path in candidates:
+        try:
+            handle = ctypes.cdll.LoadLibrary(path)
+        except OSError:
+            continue
+        handle.ios_last_error.restype = ctypes.c_char_p
+        handle.ios_graph_latency.argtypes = _LATENCY_ARGS
+        handle.ios_block_latency.argtypes = _LATENCY_ARGS
+        handle.ios_stage_latency.argtypes = [_CHARP] + _LATENCY_ARGS
+        handle.ios_graph_inference.argtypes = [_CHARP, _INT, ctypes.c_void_p, _INT, ctypes.POINTER(_CHARP), _VOIDPP,
+                                               _VOIDPP, ctypes.c_void_p]
+        handle.ios_engine_create.argtypes = [_CHARP, _INT, _INT, ctypes.POINTER(_CHARP), _VOIDPP, _VOIDPP,
+                                             ctypes.POINTER(ctypes.c_void_p)]
+        handle.ios_engine_destroy.argtypes = [ctypes.c_void_p]
+        handle.ios_engine_run.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+        handle.ios_engine_time.argtypes = [ctypes.c_void_p, _INT, _FLOATP]
+        handle.ios_engine_describe.argtypes = [ctypes.c_void_p, ctypes.c_char_p, _INT]
+        handle.ios_engine_set_input.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+        handle.ios_engine_get_output.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+        handle.ios_set_option.argtypes = [_CHARP, _CHARP]
+        handle.ios_get_option.argtypes = [_CHARP, ctypes.c_char_p, _INT]
+        handle.ios_set_device.argtypes = [_INT]
+        handle.ios_device_count.argtypes = [ctypes.POINTER(_INT)]
+        handle.ios_conv2d.argtypes = [ctypes.c_void_p] * 4 + [_INT] * 14
+        return handle
+    raise FileNotFoundError('IOS Backend library not found (build it with inter-operator-scheduler_b200/build.py)')
+
+
+def _library():
+    global lib
+    if lib is None:
+        lib = load_ios_library()
+    return lib
+
+
+def _check(status):
+    if status != 0:
+        message = _library().ios_last_error().decode(errors='replace')
+        raise RuntimeError(f'ios_runtime error {status}: {message}')
+
+
+def set_option(key: str, value: str):
+    """Run-time switches: precision tf32|fp32, executor graph|streams, conv auto|direct."""
+    _check(_library().ios_set_option(key.encode(), str(value).encode()))
+
+
+def get_option(key: str) -> str:
+    buf = ctypes.create_string_buffer(64)
+    _check(_library().ios_get_option(key.encode(), buf, 64))
+    return buf.value.decode()
+
+
+def set_device(device: int):
+    _check(_library().ios_set_device(int(device)))
+
+
+def device_count() -> int:
+    n = ctypes.c_int(0)
+    _check(_library().ios_device_count(ctypes.byref(n)))
+    return n.value
+
+
+def _timed(entry, head_args, batch_size, warmup, number, repeat, profile_stage, num_stage_slots):
+    results = (ctypes.c_float * int(repeat))()
+    stage_results = (ctypes.c_float * max(1, int(num_stage_slots)))()
+    _check(entry(*head_args, int(batch_size), int(warmup), int(number), int(repeat), 1 if profile_stage else 0,
+                 ctypes.cast(results, _FLOATP), ctypes.cast(stage_results, _FLOATP)))
+    values = [float(v) for v in results]
+    if profile_stage:
+        return values, [float(v) for v in stage_results][:int(num_stage_slots)]
+    return values
+
+
+def graph_latency(graph: Graph, batch_size=1, warmup=2, number=6, repeat=6, profile_stage=False):
+    """
+    Latency of the whole graph under its schedule: ``repeat`` samples in ms, each the mean of
+    ``number`` forwards after ``warmup`` untimed ones.  With ``profile_stage`` also returns the
+    flattened ``repeat x num_stages`` per-stage times.
+    """
+    num_stages = sum(len(b.stages) for b in graph.blocks)
+    text = json.dumps(graph.export_config()).encode()
+    return _timed(_library().ios_graph_latency, (text,), batch_size, warmup, number, repeat, profile_stage,
+                  repeat * num_stages)
+
+
+def block_latency(block: Block, batch_size, warmup, number, repeat, profile_stage=False):
+    text = json.dumps(block.export_config()).encode()
+    return _timed(_library().ios_block_latency, (text,), batch_size, warmup, number, repeat, profile_stage,
+                  repeat * len(block.stages))
+
+
+def stage_config(stage: List[List[Node]]):
+    """(stage json, input json) of a candidate stage: full node configs plus the shapes of outside producers."""
+    groups = [[node.export_config() for node in group] for group in stage]
+    inside = {node.name for group in stage for node in group}
+    producers = {}
+    for group in stage:
+        for node in group:
+            for term in node.inputs:
+                for value in term:
+                    if value.node.name not in inside:
+                        producers.setdefault(value.node.name, value.node.output_shape)
+    return json.dumps(groups), json.dumps({name: list(shape) for name, shape in producers.items()})
+
+
+def stage_latency(stage: List[List[Node]], batch_size, warmup, number, repeat, profile_stage=False):
+    """Latency of one candidate stage (groups x operators) on synthetic inputs; what the DP search calls."""
+    stage_text, input_text = stage_config(stage)
+    return _timed(_library().ios_stage_latency, (stage_text.encode(), input_text.encode()), batch_size, warmup,
+                  number, repeat, profile_stage, repeat)
+
+
+def _conv_arrays(graph: Graph):
+    convs: List[Conv] = list(get_nodes_by_type(graph.nodes(), Conv))
+    weights, biases = [], []
+    for node in convs:
+        if node.weight is None or node.bias is None:
+            raise RuntimeError(f'conv {node.name} has no weights: call graph.init_weights() '
+                               f'(or optimize(..., compute_weight=True))')
+        weights.append(np.ascontiguousarray(node.weight, dtype=np.float32))
+        biases.append(np.ascontiguousarray(node.bias, dtype=np.float32))
+    return convs, weights, biases
+
+
+def graph_inference(graph: Graph, batch_size, input: np.ndarray):
+    """Execute the graph once on ``input`` (N, C, H, W) and return the exit node's output as float32."""
+    output = np.empty(shape=(batch_size, *graph.blocks[-1].exit_node.output_shape), dtype=np.float32)
+    convs, weights, biases = _conv_arrays(graph)
+    data = np.ascontiguousarray(input, dtype=np.float32)
+    expected = (batch_size, *graph.input.output_shape)
+    if tuple(data.shape) != tuple(expected):
+        raise ValueError(f'input has shape {tuple(data.shape)}, the graph expects {tuple(expected)}')
+    _check(_library().ios_graph_inference(
+        json.dumps(graph.export_config()).encode(), int(batch_size), data.ctypes.data_as(ctypes.c_void_p),
+        len(convs), c_string_list([node.name for node in convs]), c_ndarray_list(weights), c_ndarray_list(biases),
+        output.ctypes.data_as(ctypes.c_void_p)))
+    return output
+
+
+def conv2d(x: np.ndarray, weight: np.ndarray, bias=None, stride=(1, 1), padding=(0, 0), groups=1, act='identity',
+           impl='auto'):
+    """One convolution through the runtime (testing aid).  x: NCHW, weight: OIHW."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    weight = np.ascontiguousarray(weight, dtype=np.float32)
+    n, cin, h, w = x.shape
+    cout, _, kh, kw = weight.shape
+    oh = 1 + (h - kh + 2 * padding[0]) // stride[0]
+    ow = 1 + (w - kw + 2 * padding[1]) // stride[1]
+    y = np.empty((n, cout, oh, ow), dtype=np.float32)
+    b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+    _check(_library().ios_conv2d(
+        x.ctypes.data_as(ctypes.c_void_p), weight.ctypes.data_as(ctypes.c_void_p),
+        None if b is None else b.ctypes.data_as(ctypes.c_void_p), y.ctypes.data_as(ctypes.c_void_p),
+        n, cin, h, w, cout, kh, kw, stride[0], stride[1], padding[0], padding[1], groups,
+        ['identity', 'relu', 'sigmoid', 'tanh'].index(act), ['auto', 'direct', 'tensor'].index(impl)))
+    return y
+
+
+class Engine:
+    """
+    A graph bound to one GPU: weights packed and resident, schedule captured once.  ``run`` takes
+    host NCHW input and returns host NCHW output; ``time`` replays the resident forward.
+    """
+
+    def __init__(self, graph: Graph, batch_size: int, synthetic_weights=False):
+        self._lib = _library()
+        self._handle = ctypes.c_void_p(None)
+        self.batch_size = int(batch_size)
+        self.input_shape = (self.batch_size, *graph.input.output_shape)
+        self.output_shape = (self.batch_size, *graph.blocks[-1].exit_node.output_shape)
+        text = json.dumps(graph.export_config()).encode()
+        if synthetic_weights:
+            status = self._lib.ios_engine_create(text, self.batch_size, 0, None, None, None, ctypes.byref(self._handle))
+        else:
+            convs, weights, biases = _conv_arrays(graph)
+            status = self._lib.ios_engine_create(text, self.batch_size, len(convs),
+                                                 c_string_list([node.name for node in convs]),
+                                                 c_ndarray_list(weights), c_ndarray_list(biases),
+                                                 ctypes.byref(self._handle))
+        _check(status)
+
+    def run(self, input, output=None):
+        """``input`` / ``output`` may be numpy arrays or raw host addresses (ints) of float32 NCHW buffers."""
+        if isinstance(input, np.ndarray):
+            data = np.ascontiguousarray(input, dtype=np.float32)
+            if tuple(data.shape) != tuple(self.input_shape):
+                raise ValueError(f'input has shape {tuple(data.shape)}, the engine expects {self.input_shape}')
+            in_ptr = data.ctypes.data_as(ctypes.c_void_p)
+        else:
+            in_ptr = ctypes.c_void_p(int(input))
+        result = output
+        if output is None:
+            result = np.empty(self.output_shape, dtype=np.float32)
+        out_ptr = result.ctypes.data_as(ctypes.c_void_p) if isinstance(result, np.ndarray) else ctypes.c_void_p(int(result))
+        _check(self._lib.ios_engine_run(self._handle, in_ptr, out_ptr))
+        return result
+
+    def set_input(self, input: np.ndarray):
+        data = np.ascontiguousarray(input, dtype=np.float32)
+        _check(self._lib.ios_engine_set_input(self._handle, data.ctypes.data_as(ctypes.c_void_p)))
+
+    def get_output(self):
+        out = np.empty(self.output_shape, dtype=np.float32)
+        _check(self._lib.ios_engine_get_output(self._handle, out.ctypes.data_as(ctypes.c_void_p)))
+        return out
+
+    def time(self, iters=10) -> float:
+        """Milliseconds per forward over ``iters`` back-to-back replays (CUDA events, resident input)."""
+        ms = ctypes.c_float(0.0)
+        _check(self._lib.ios_engine_time(self._handle, int(iters), ctypes.byref(ms)))
+        return float(ms.value)
+
+    def describe(self) -> dict:
+        buf = ctypes.create_string_buffer(2048)
+        _check(self._lib.ios_engine_describe(self._handle, buf, 2048))
+        return json.loads(buf.value.decode())
+
+    def close(self):
+        if self._handle:
+            self._lib.ios_engine_destroy(self._handle)
+            self._handle = ctypes.c_void_p(None)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
