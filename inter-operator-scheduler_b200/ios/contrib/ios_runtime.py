@@ -123,7 +123,7 @@ def graph_latency(graph: Graph, batch_size=1, warmup=2, number=6, repeat=6, prof
     ``number`` forwards after ``warmup`` untimed ones.  With ``profile_stage`` also returns the
     flattened ``repeat x num_stages`` per-stage times.
     """
-    num_stages = sum(len(b.stages) for b in graph.blocks)
+    num_stages = sum(len(b.stages or []) for b in graph.blocks)
     text = json.dumps(graph.export_config()).encode()
     return _timed(_library().ios_graph_latency, (text,), batch_size, warmup, number, repeat, profile_stage,
                   repeat * num_stages)
@@ -132,7 +132,7 @@ def graph_latency(graph: Graph, batch_size=1, warmup=2, number=6, repeat=6, prof
 def block_latency(block: Block, batch_size, warmup, number, repeat, profile_stage=False):
     text = json.dumps(block.export_config()).encode()
     return _timed(_library().ios_block_latency, (text,), batch_size, warmup, number, repeat, profile_stage,
-                  repeat * len(block.stages))
+                  repeat * len(block.stages or []))
 
 
 def stage_config(stage: List[List[Node]]):

@@ -1,0 +1,254 @@
+"""
+GPU parity: the CUDA path, called through the C-ABI (ctypes), against the CPU oracle and against
+the golden vectors produced by the reference implementation.
+
+Metric and tolerances (stated by the parity contract): max|y - ref| / max|ref| <= 1e-3 for the
+TF32 tensor-core path (fp32 accumulate), and 2e-5 for the CUDA-core fp32 path.
+"""
+import json
+import os
+
+import numpy as np
+import pytest
+
+import ios
+import ios_oracle as oracle
+from ios.contrib import ios_runtime as rt
+from helpers import (GOLDEN_DIR, TOL_FP32, TOL_TF32, load_ref_schedule, sample_block, seeded, set_weights,
+                     weights_of)
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def default_options():
+    rt.set_option('precision', 'tf32')
+    rt.set_option('executor', 'graph')
+    rt.set_option('conv', 'auto')
+    rt.set_option('split_k', '0')
+    yield
+
+
+def _conv_case(shape, impl, act='relu', seed=0):
+    n, cin, h, w, cout, kh, kw, sh, sw, ph, pw, groups = shape
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((n, cin, h, w)).astype(np.float32)
+    wt = (rng.standard_normal((cout, cin // groups, kh, kw)) / np.sqrt(kh * kw * cin / groups)).astype(np.float32)
+    b = rng.standard_normal(cout).astype(np.float32) * 0.1
+    ref = oracle.conv2d_numpy(x, wt, b, (sh, sw), (ph, pw), groups, act)
+    got = rt.conv2d(x, wt, b, stride=(sh, sw), padding=(ph, pw), groups=groups, act=act, impl=impl)
+    assert got.shape == ref.shape
+    return oracle.max_rel_err(got, ref)
+
+
+# n, cin, h, w, cout, kh, kw, sh, sw, ph, pw, groups
+TC_SHAPES = [
+    (1, 32, 8, 8, 16, 1, 1, 1, 1, 0, 0, 1),        # smallest: one K step, 64 pixels
+    (1, 64, 12, 12, 48, 1, 1, 1, 1, 0, 0, 1),      # flat 1x1, two pixel tiles
+    (1, 48, 35, 35, 64, 5, 5, 1, 1, 2, 2, 1),      # Inception-A 5x5, 25 taps
+    (1, 96, 17, 17, 80, 3, 3, 1, 1, 1, 1, 1),      # 3x3 pad 1
+    (1, 40, 17, 17, 24, 1, 7, 1, 1, 0, 3, 1),      # 1x7
+    (1, 40, 17, 17, 24, 7, 1, 1, 1, 3, 0, 1),      # 7x1
+    (1, 30, 35, 35, 36, 3, 3, 2, 2, 0, 0, 1),      # stride 2, channels not a multiple of 32 / 16
+    (1, 3, 59, 59, 32, 3, 3, 2, 2, 0, 0, 1),       # stem-like: 3 input channels
+    (1, 3, 64, 64, 20, 7, 7, 2, 2, 3, 3, 1),       # SqueezeNet stem-like 7x7 stride 2 pad 3
+    (1, 16, 20, 150, 24, 3, 3, 1, 1, 1, 1, 1),     # rows wider than one pixel tile
+    (1, 375, 15, 15, 200, 3, 3, 1, 1, 1, 1, 1),    # sample-block shape: split-K, ragged channels
+    (3, 24, 9, 9, 40, 3, 3, 1, 1, 1, 1, 1),        # batch 3, several images per tile
+    (5, 20, 4, 4, 300, 1, 1, 1, 1, 0, 0, 1),       # batch 5 flat, Cout > 256
+    (2, 36, 8, 8, 130, 3, 1, 1, 1, 1, 0, 1),       # 3x1, ragged Cout
+]
+
+
+@pytest.mark.parametrize('shape', TC_SHAPES)
+def test_conv_tensor_core_vs_oracle(shape):
+    assert _conv_case(shape, 'tensor') <= TOL_TF32
+
+
+@pytest.mark.parametrize('shape', TC_SHAPES[:6] + [
+    (2, 12, 9, 7, 12, 3, 3, 1, 1, 1, 1, 12),       # depthwise
+    (1, 78, 28, 28, 78, 3, 3, 2, 2, 1, 1, 78),     # RandWire depthwise stride 2, C % 4 != 0
+    (1, 80, 14, 14, 80, 3, 3, 1, 1, 1, 1, 80),     # depthwise, vector path
+    (2, 8, 10, 10, 12, 3, 3, 2, 1, 1, 0, 4),       # grouped
+])
+def test_conv_cuda_core_vs_oracle(shape):
+    assert _conv_case(shape, 'direct', act='tanh') <= TOL_FP32
+
+
+@pytest.mark.parametrize('split', [2, 3, 7])
+def test_conv_split_k_is_exact_sum_of_partials(split):
+    shape = (1, 160, 8, 8, 96, 3, 3, 1, 1, 1, 1, 1)
+    rt.set_option('split_k', '1')
+    base = _conv_case(shape, 'tensor')
+    rt.set_option('split_k', str(split))
+    assert _conv_case(shape, 'tensor') <= TOL_TF32
+    assert base <= TOL_TF32
+
+
+def test_conv_activations_and_no_bias():
+    shape = (1, 32, 9, 9, 32, 3, 3, 1, 1, 1, 1, 1)
+    for act in ('identity', 'relu', 'sigmoid', 'tanh'):
+        assert _conv_case(shape, 'tensor', act=act) <= TOL_TF32
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((1, 32, 9, 9)).astype(np.float32)
+    w = rng.standard_normal((8, 32, 1, 1)).astype(np.float32) * 0.1
+    got = rt.conv2d(x, w, None)
+    assert oracle.max_rel_err(got, oracle.conv2d_numpy(x, w, None, (1, 1), (0, 0))) <= TOL_TF32
+
+
+def _run_both(graph, weights, batch, xseed):
+    config = graph.export_config()
+    x = oracle.normal_input(config, batch, xseed)
+    ref = oracle.run_config(config, weights, x)
+    got = rt.graph_inference(graph, batch, x)
+    return got, ref
+
+
+def test_all_operator_types_graph(golden):
+    with open(os.path.join(GOLDEN_DIR, 'all_ops.json')) as fh:
+        config = json.load(fh)
+    graph = ios.Graph.from_config(config)
+    weights = oracle.uniform_weights(graph.export_config(), 3)
+    set_weights(graph, weights)
+    x = oracle.normal_input(config, 3, 4)
+    for precision, tol in (('fp32', TOL_FP32), ('tf32', TOL_TF32)):
+        rt.set_option('precision', precision)
+        y = rt.graph_inference(graph, 3, x)
+        golden.expect('all_ops_b3', y, tol)
+    rt.set_option('executor', 'streams')
+    golden.expect('all_ops_b3', rt.graph_inference(graph, 3, x), TOL_TF32)
+
+
+@pytest.mark.parametrize('case,model,law,wseed,xseed,batch', [
+    ('sample_block', 'sample_block', 'he', 0, 0, 1),
+    ('inception_v3', 'inception_v3', 'he', 0, 0, 1),
+    ('inception_v3_uniform_b2', 'inception_v3', 'uniform', 1, 1, 2),
+    ('squeezenet', 'squeezenet', 'he', 0, 0, 1),
+    ('randwire_small', 'randwire_small', 'he', 0, 0, 1),
+])
+def test_networks_match_reference_outputs(golden, case, model, law, wseed, xseed, batch):
+    graph = sample_block() if model == 'sample_block' else getattr(ios.models, model)()
+    graph.sequential_schedule()
+    config, weights = seeded(graph, wseed, law)
+    x = oracle.normal_input(config, batch, xseed)
+    y = rt.graph_inference(graph, batch, x)
+    golden.expect(case, y, TOL_TF32)
+
+
+def test_inception_cuda_core_path_is_fp32_exact(golden):
+    rt.set_option('precision', 'fp32')
+    graph = ios.models.inception_v3()
+    graph.sequential_schedule()
+    config, weights = seeded(graph, 0)
+    y = rt.graph_inference(graph, 1, oracle.normal_input(config, 1, 0))
+    golden.expect('inception_v3', y, 5e-5)
+
+
+@pytest.mark.parametrize('model,opt_type', [('squeezenet', 'dp_parallel_merge'), ('inception_v3', 'dp_parallel_merge'),
+                                            ('inception_v3', 'dp_parallel')])
+def test_optimized_schedules_compute_the_same_function(golden, model, opt_type):
+    graph = getattr(ios.models, model)()
+    config, weights = seeded(graph, 0)
+    np.random.seed(7)
+    opt = ios.optimize(graph, batch_size=1, cost_model=ios.RandomCostModel(), opt_type=opt_type, compute_weight=True,
+                       max_part_size=50)
+    y = rt.graph_inference(opt, 1, oracle.normal_input(config, 1, 0))
+    golden.expect(f'{model}_{opt_type}_seed7', y, TOL_TF32)
+
+
+@pytest.mark.parametrize('name', ['1', '128', 'k80'])
+def test_reference_schedule_fixtures_execute(golden, name):
+    graph = ios.Graph.from_config(load_ref_schedule(name))
+    config = graph.export_config()
+    set_weights(graph, oracle.he_normal_weights(config, 0))
+    y = rt.graph_inference(graph, 1, oracle.normal_input(config, 1, 0))
+    golden.expect('ref_schedule_' + name, y, TOL_TF32)
+
+
+def test_batched_inference_equals_per_image_inference():
+    graph = ios.models.squeezenet()
+    graph.sequential_schedule()
+    config, weights = seeded(graph, 5, 'uniform')
+    x = oracle.normal_input(config, 4, 11)
+    y = rt.graph_inference(graph, 4, x)
+    ref = oracle.run_config(config, weights, x)
+    assert oracle.max_rel_err(y, ref) <= TOL_TF32
+    y0 = rt.graph_inference(graph, 1, x[2:3])
+    assert oracle.max_rel_err(y0, y[2:3]) <= 1e-6      # same arithmetic per image, whatever the batch
+
+
+def test_results_are_deterministic_across_runs_and_executors():
+    graph = sample_block()
+    config, weights = seeded(graph, 0)
+    np.random.seed(3)
+    opt = ios.optimize(graph, batch_size=1, cost_model=ios.RandomCostModel(), opt_type='dp_parallel', compute_weight=True)
+    x = oracle.normal_input(config, 1, 0)
+    a = rt.graph_inference(opt, 1, x)
+    b = rt.graph_inference(opt, 1, x)
+    rt.set_option('executor', 'streams')
+    c = rt.graph_inference(opt, 1, x)
+    assert np.array_equal(a, b) and np.array_equal(a, c)
+
+
+def test_latency_entry_points():
+    graph = sample_block()
+    graph.sequential_schedule()
+    lat = rt.graph_latency(graph, batch_size=1, warmup=2, number=3, repeat=4)
+    assert len(lat) == 4 and all(0 < v < 100 for v in lat)
+    lat, stages = rt.graph_latency(graph, batch_size=1, warmup=1, number=2, repeat=3, profile_stage=True)
+    stages = np.array(stages).reshape(3, -1)
+    assert stages.shape == (3, 5) and (stages > 0).all()
+    assert abs(stages.sum(axis=1).mean() - np.mean(lat)) < 0.5 * np.mean(lat) + 0.05
+    block = graph.blocks[0]
+    lat = rt.block_latency(block, 1, 1, 2, 3)
+    assert len(lat) == 3 and all(v > 0 for v in lat)
+    nodes = block.inner_nodes
+    one = rt.stage_latency([[nodes[0]]], 1, 2, 6, 3)
+    two = rt.stage_latency([[nodes[0], nodes[3]], [nodes[1]], [nodes[2]]], 1, 2, 6, 3)
+    assert len(one) == 3 and len(two) == 3 and all(v > 0 for v in one + two)
+    cm = ios.IOSCostModel()
+    assert len(cm.get_stage_latency([[nodes[1]]], 1, 1, 2, 2)) == 2
+
+
+def test_optimize_with_measured_cost_model_and_inference():
+    """examples/sample.py end to end: optimize on measured latencies, time, run."""
+    graph = sample_block()
+    opt = ios.optimize(graph, batch_size=1, opt_type='dp_parallel', compute_weight=True, number=2, repeat=2)
+    graph.sequential_schedule()
+    seq = np.mean(rt.graph_latency(graph, batch_size=1, repeat=3))
+    fast = np.mean(rt.graph_latency(opt, batch_size=1, repeat=3))
+    assert fast > 0 and seq > 0
+    x = np.random.randn(1, 375, 15, 15)          # float64 on purpose, as in the README
+    y = rt.graph_inference(opt, batch_size=1, input=x)
+    ref = oracle.run_config(graph.export_config(), weights_of(graph), x.astype(np.float32))
+    assert oracle.max_rel_err(y, ref) <= TOL_TF32
+
+
+def test_engine_run_matches_graph_inference():
+    graph = ios.models.squeezenet()
+    graph.sequential_schedule()
+    config, weights = seeded(graph, 0)
+    x = oracle.normal_input(config, 2, 1)
+    engine = rt.Engine(graph, 2)
+    try:
+        y = engine.run(x)
+        assert np.array_equal(y, rt.graph_inference(graph, 2, x))
+        info = engine.describe()
+        assert info['launches'] > 0 and info['conv_tc'] > 0 and info['output_shape'] == [2, 1000, 1, 1]
+        assert engine.time(5) > 0
+        y2 = engine.run(x)
+        assert np.array_equal(y, y2)
+    finally:
+        engine.close()
+
+
+def test_missing_weights_and_bad_last_stage_are_errors():
+    graph = sample_block()
+    graph.sequential_schedule()
+    for conv in graph.convs():
+        conv.weight = None
+    with pytest.raises(RuntimeError):
+        rt.graph_inference(graph, 1, np.zeros((1, 375, 15, 15), np.float32))
+    graph = sample_block()
+    graph.blocks[0].stages = [[['1'], ['2'], ['3']], [['4']], [['5']]]
+    assert len(rt.graph_latency(graph, 1, 1, 1, 1)) == 1

@@ -1,0 +1,124 @@
+"""
+The Python surface: IR wire format, schedules, printing and the DP optimizer.  No GPU: the search
+runs on RandomCostModel, and the fixtures pin it to what the reference's optimizer produced from
+the same numpy random seed (tests/golden/make_golden.py).
+"""
+import json
+
+import numpy as np
+import pytest
+
+import ios
+import ios_oracle as oracle
+from helpers import load_ref_schedule, sample_block, seeded, sha, weights_of
+
+
+def test_sample_block_names_and_print():
+    graph = sample_block()
+    graph.sequential_schedule()
+    assert graph.input.name == '0'
+    assert [n.name for n in graph.blocks[0].inner_nodes] == ['1', '2', '3', '4'] and graph.exit_node.name == '5'
+    text = str(graph)
+    assert text.splitlines() == ['Sequential(', '  [1]Conv2d(0)', '  [2]Conv2d(0)', '  [3]Conv2d(0)', '  [4]Conv2d(1)',
+                                 '  [5]Concat(4,2,3)', ')']
+    assert graph.blocks[0].stages == [[['1']], [['2']], [['3']], [['4']], [['5']]]
+    assert graph.exit_node.output_shape == (1875, 15, 15)
+
+
+def test_config_round_trip():
+    for maker in (ios.models.inception_v3, ios.models.squeezenet, ios.models.randwire_small):
+        graph = maker()
+        graph.sequential_schedule()
+        config = graph.export_config()
+        clone = ios.Graph.from_config(json.loads(json.dumps(config)))
+        assert json.dumps(clone.export_config()) == json.dumps(json.loads(json.dumps(config)))
+        assert clone.flops() == graph.flops() and clone.kernels() == graph.kernels()
+
+
+def test_model_shapes():
+    g = ios.models.inception_v3()
+    assert g.exit_node.output_shape == [2048, 1, 1]
+    assert len(g.blocks) == 13 and len(list(g.convs())) == 94
+    g = ios.models.squeezenet()
+    assert g.exit_node.output_shape == [1000, 1, 1] and len(list(g.convs())) == 30
+    g = ios.models.randwire_small()
+    assert g.exit_node.output_shape == [1280, 1, 1]
+    convs = list(g.convs())
+    assert len(convs) == 195 and sum(1 for c in convs if c.groups > 1) == 96
+    assert [b.exit_node.output_shape for b in g.blocks[1:4]] == [(78, 28, 28), (156, 14, 14), (312, 7, 7)]
+
+
+def test_greedy_schedule_covers_every_operator():
+    g = ios.models.inception_v3()
+    g.greedy_schedule(max_num_stream=4)
+    for block in g.blocks:
+        names = [n for stage in block.stages for group in stage for n in group]
+        assert sorted(names) == sorted(n.name for n in block.inner_nodes + [block.exit_node])
+        assert all(len(stage) <= 4 for stage in block.stages)
+
+
+@pytest.mark.parametrize('model,opt_type', [('squeezenet', 'dp_parallel_merge'), ('inception_v3', 'dp_parallel_merge'),
+                                            ('inception_v3', 'dp_parallel')])
+def test_optimizer_reproduces_reference_schedule(golden, model, opt_type):
+    graph = getattr(ios.models, model)()
+    config, weights = seeded(graph, 0)
+    np.random.seed(7)
+    opt = ios.optimize(graph, batch_size=1, cost_model=ios.RandomCostModel(), opt_type=opt_type, compute_weight=True,
+                       max_part_size=50)
+    case = f'{model}_{opt_type}_seed7'
+    meta = golden.meta(case)
+    out_config = opt.export_config()
+    assert sha(out_config) == meta['config_sha256'], 'the optimized graph differs from the reference optimizer output'
+    assert sum(len(b.stages) for b in opt.blocks) == meta['num_stages']
+    assert opt.name == f'{model}_{opt_type}'
+    # merged weights included: the optimized graph computes the same function
+    y = oracle.run_config(out_config, weights_of(opt), oracle.normal_input(out_config, 1, 0))
+    golden.expect(case, y, 2e-5)
+    y_seq = oracle.run_config(config, weights, oracle.normal_input(config, 1, 0))
+    assert oracle.max_rel_err(y, y_seq) < 2e-5
+
+
+def test_schedule_invariance_random_schedules():
+    """Any schedule the search can emit computes the same function as the sequential one."""
+    graph = ios.models.squeezenet()
+    config, weights = seeded(graph, 2, law='uniform')
+    x = oracle.normal_input(config, 2, 9)
+    y_seq = oracle.run_config(config, weights, x)
+    for seed, opt_type in ((1, 'dp_parallel'), (2, 'dp_merge'), (3, 'dp_parallel_merge')):
+        np.random.seed(seed)
+        opt = ios.optimize(graph, batch_size=2, cost_model=ios.RandomCostModel(), opt_type=opt_type,
+                           compute_weight=True, max_group_size=2, max_num_groups=4)
+        y = oracle.run_config(opt.export_config(), weights_of(opt), x)
+        assert oracle.max_rel_err(y, y_seq) < 2e-5
+
+
+def test_optimize_sample_block_structure():
+    graph = sample_block()
+    np.random.seed(0)
+    info = {}
+    opt = ios.optimize(graph, batch_size=1, cost_model=ios.RandomCostModel(), opt_type='dp_parallel',
+                       compute_weight=True, debug_dp_info=info)
+    names = sorted(n for stage in opt.blocks[0].stages for group in stage for n in group)
+    assert names == ['1', '2', '3', '4', '5']
+    assert opt.name == 'demo_dp_parallel'
+    assert info['#operators'] == [5] and info['#states'][0] > 0 and info['#transitions'][0] > 0
+    # without compute_weight the new convolutions carry no weights
+    opt2 = ios.optimize(graph, batch_size=1, cost_model=ios.RandomCostModel(), opt_type='dp_merge')
+    assert all(c.weight is None for c in opt2.convs())
+
+
+def test_reference_schedule_fixtures_load():
+    for name in ('1', '16', '32', '64', '128', 'k80', 'v100'):
+        graph = ios.Graph.from_config(load_ref_schedule(name))
+        assert len(graph.blocks) == 13
+        for block in graph.blocks:
+            scheduled = [n for stage in block.stages for group in stage for n in group]
+            assert sorted(scheduled) == sorted(n.name for n in block.inner_nodes + [block.exit_node])
+
+
+def test_iter_subset_and_counters():
+    from ios.utils import iter_subset
+    assert list(iter_subset(0b101)) == [0b101, 0b100, 0b001]
+    assert list(iter_subset(0b11, include_emtpy_set=True)) == [3, 2, 1, 0]
+    g = sample_block()
+    assert g.flops() > 0 and g.schedule_operators() == 5
