@@ -508,7 +508,7 @@ const char *conv_tc_encode(const ConvTcParams &p, ConvTcPlan *plan) {
 }
 
 cudaError_t conv_tc_prepare() {
-    return cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    return cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024);
 }
 
 void launch_conv_tc(const ConvTcParams &p, const ConvTcPlan &q, cudaStream_t stream) {
