@@ -1,0 +1,443 @@
+"""
+Benchmark of the hot path: executing a scheduled CNN on B200 through libios_runtime.so.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--model inception_v3|squeezenet|randwire_small|sample_block] [--batch B]
+                    [--schedule dp|sequential|greedy]
+
+One step = one forward of the model over one batch of synthetic input (seeded N(0,1) input,
+He-normal seeded weights, the distribution the workload is defined on).  The default workload is
+Inception-v3, batch 1 per GPU, under the schedule found by ``ios.optimize`` (the DP search) on the
+GPU it runs on.  Batch 1 does not shard, so N > 1 runs N independent replicas (one process per
+GPU, no collective on the data path) and reports the aggregate images/s; ``ms_per_step`` is the
+batch-1 latency.
+
+What is timed:
+* ``value`` / ``ms_per_step``: device time of K forwards with input and weights resident in HBM,
+  CUDA events on the launching stream around each step, an L2 flush (a 256 MiB write) between
+  steps, max over ranks;
+* ``e2e``: the same K steps through the host-buffer entry point (``ios_engine_run``): pinned host
+  input -> H2D -> forward -> D2H -> pinned host output, wall clock around the blocking call;
+* ``roofline``: per-launch device times of the convolution kernel measured live
+  (``ios_engine_profile``), algorithmic FLOPs = 2 * MACs of the original convolutions;
+* ``cpu_baseline``: the CPU oracle (a torch float32 restatement of the reference's CPU executor) on
+  the host cores, a bounded number of forwards of the same workload.
+
+``--impl reference`` times the reference's own runtime (its cuDNN executor, built unmodified from
+its sources into oracle/_ref/) on the same workload through its own ``graph_latency`` protocol; if
+that library cannot be loaded, the CPU oracle is timed instead.
+"""
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _sub in ('inter-operator-scheduler_b200', 'oracle'):
+    sys.path.insert(0, os.path.join(ROOT, _sub))
+
+import numpy as np  # noqa: E402
+
+METRIC = 'images/sec on Inception-v3 under the DP schedule (ms_per_step = batch-1 end-to-end latency ms)'
+L2_FLUSH_BYTES = 256 << 20
+
+
+def log(*args):
+    print(*args, file=sys.stderr, flush=True)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    if os.path.exists(path):
+        with open(path) as fh:
+            peaks = json.load(fh)
+        return peaks, 'measured'
+    return {'hbm_gbs': 6650.0, 'bf16_tflops': 1590.0, 'bf16_tflops_sustained': 1400.0}, 'fallback'
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    QUERY = ('index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,'
+             'clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,'
+             'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, device_index):
+        self.device_index = device_index
+        self.proc = None
+        self.lines = []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(['nvidia-smi', f'--id={self.device_index}', f'--query-gpu={self.QUERY}',
+                                          '--format=csv,noheader,nounits', '-lms', '50'],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._drain, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _drain(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap']
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(',')]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[5:9]):
+                if flag.lower().startswith('active'):
+                    reasons.add(name)
+        if not sm:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': [], 'samples': 0}
+        return {'sm_mhz': statistics.median(sm), 'sm_max_mhz': max(mx), 'reasons': sorted(reasons), 'samples': len(sm)}
+
+
+def build_graph(model):
+    import ios
+    if model == 'sample_block':
+        ios.reset_name()
+        v = ios.placeholder(output_shape=(375, 15, 15))
+        block = ios.Block(enter_node=v.node)
+        v1 = ios.conv2d(block, inputs=[[v]], out_channels=375, kernel=(3, 3), stride=(1, 1), padding=(1, 1))
+        v2 = ios.conv2d(block, inputs=[[v]], out_channels=750, kernel=(3, 3), stride=(1, 1), padding=(1, 1))
+        v3 = ios.conv2d(block, inputs=[[v]], out_channels=375, kernel=(3, 3), stride=(1, 1), padding=(1, 1))
+        v1 = ios.conv2d(block, inputs=[[v1]], out_channels=750, kernel=(3, 3), stride=(1, 1), padding=(1, 1))
+        ios.identity(block, inputs=[[v1], [v2], [v3]], is_exit=True)
+        graph = ios.Graph(name='demo', input=v.node, blocks=[block])
+    else:
+        graph = getattr(ios.models, model)()
+    return graph
+
+
+def seeded_weights(graph, seed=0):
+    import ios_oracle as oracle
+    config = graph.export_config()
+    weights = oracle.he_normal_weights(config, seed)
+    for conv in graph.convs():
+        conv.weight, conv.bias = weights[conv.name]
+    return weights
+
+
+def schedule_graph(graph, schedule, batch, cost_model=None):
+    """Returns the graph to execute and the seconds the schedule search took."""
+    import ios
+    t0 = time.time()
+    if schedule == 'sequential':
+        graph.sequential_schedule()
+        return graph, 0.0
+    if schedule == 'greedy':
+        graph.greedy_schedule()
+        return graph, 0.0
+    opt = ios.optimize(graph, batch_size=batch, cost_model=cost_model, opt_type='dp_parallel_merge',
+                       compute_weight=True, max_part_size=50, number=4, repeat=2)
+    return opt, time.time() - t0
+
+
+# ------------------------------------------------------------------------------------------------
+# distributed plumbing (one process per GPU; only a barrier and a max-reduce of the timing)
+# ------------------------------------------------------------------------------------------------
+class Ranks:
+    def __init__(self, gpus):
+        self.world = int(os.environ.get('WORLD_SIZE', '1'))
+        self.rank = int(os.environ.get('RANK', '0'))
+        self.local = int(os.environ.get('LOCAL_RANK', '0'))
+        self.dist = None
+        if self.world > 1:
+            import torch
+            import torch.distributed as dist
+            torch.cuda.set_device(self.local)
+            dist.init_process_group('nccl', device_id=torch.device('cuda', self.local))
+            self.dist = dist
+        elif gpus > 1:
+            log(f'--gpus {gpus} was given without torchrun: running a single replica on GPU 0')
+
+    def barrier(self):
+        import torch
+        if self.dist:
+            self.dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(self, value):
+        if not self.dist:
+            return value
+        import torch
+        t = torch.tensor([value], dtype=torch.float64, device='cuda')
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum_over_ranks(self, value):
+        if not self.dist:
+            return value
+        import torch
+        t = torch.tensor([value], dtype=torch.float64, device='cuda')
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM)
+        return float(t.item())
+
+    def finish(self):
+        if self.dist:
+            self.dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import ios
+    import ios_oracle as oracle
+    from ios.contrib import ios_runtime as rt
+
+    ranks = Ranks(args.gpus)
+    device = ranks.local
+    torch.cuda.set_device(device)
+    rt.set_device(device)
+    rt.set_option('executor', args.executor)
+    if args.precision:
+        rt.set_option('precision', args.precision)
+    peaks, peak_kind = measured_peaks()
+
+    graph = build_graph(args.model)
+    weights = seeded_weights(graph, 0)
+    base_config = graph.export_config()
+    exec_graph, search_s = schedule_graph(graph, args.schedule, args.batch)
+    log(f'[rank {ranks.rank}] schedule "{args.schedule}": {sum(len(b.stages) for b in exec_graph.blocks)} stages, '
+        f'search took {search_s:.1f} s')
+
+    engine = rt.Engine(exec_graph, args.batch)
+    info = engine.describe()
+    x = oracle.normal_input(base_config, args.batch, 0)
+    host_in = torch.from_numpy(x).pin_memory()
+    host_out = torch.empty(engine.output_shape, dtype=torch.float32).pin_memory()
+    engine.set_input(x)
+    flush = torch.empty(L2_FLUSH_BYTES // 4, dtype=torch.float32, device='cuda')
+
+    def flush_l2():
+        flush.zero_()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing ------------------------------------------------------------
+    for _ in range(args.warmup):
+        flush_l2()
+        engine.time(1)
+    ranks.barrier()
+    with ClockSampler(device) as sampler:
+        device_ms = 0.0
+        t_wall = time.perf_counter()
+        for _ in range(args.steps):
+            flush_l2()
+            device_ms += engine.time(1)
+        ranks.barrier()
+        wall_s = time.perf_counter() - t_wall
+        warm_ms = engine.time(max(10, args.steps))          # back-to-back replays, weights stay in L2
+        # ---- end to end through the host-buffer entry point -------------------------------------
+        for _ in range(args.warmup):
+            engine.run(host_in.data_ptr(), host_out.data_ptr())
+        ranks.barrier()
+        e2e_s = 0.0
+        for _ in range(args.steps):
+            flush_l2()
+            t0 = time.perf_counter()
+            engine.run(host_in.data_ptr(), host_out.data_ptr())
+            e2e_s += time.perf_counter() - t0
+        ranks.barrier()
+    clocks = sampler.summary()
+    ms_per_step = ranks.max_over_ranks(device_ms / args.steps)
+    e2e_ms = ranks.max_over_ranks(1e3 * e2e_s / args.steps)
+    images = args.batch * ranks.world
+    value = images / (ms_per_step * 1e-3)
+    e2e_value = images / (e2e_ms * 1e-3)
+
+    # the end-to-end result must be the function the oracle computes
+    y = host_out.numpy().copy()
+
+    # ---- roofline of the dominant kernel ----------------------------------------------------
+    steps = engine.profile(5)
+    by_kind = {}
+    for kind, ms, work in steps:
+        slot = by_kind.setdefault(kind, {'launches': 0, 'ms': 0.0, 'work': 0.0})
+        slot['launches'] += 1
+        slot['ms'] += ms
+        slot['work'] += work
+    total_ms = sum(v['ms'] for v in by_kind.values())
+    conv = by_kind.get('conv_tc', {'launches': 0, 'ms': 0.0, 'work': 0.0})
+    tf32_peak = peaks['bf16_tflops'] / 2.0
+    achieved = conv['work'] / (conv['ms'] * 1e-3) / 1e12 if conv['ms'] > 0 else 0.0
+    roofline = {
+        'bound': 'tensor', 'kernel': 'conv_tc_kernel', 'achieved': round(achieved, 3), 'peak': tf32_peak,
+        'unit': 'TFLOP/s', 'frac': round(achieved / tf32_peak, 5),
+        'peak_source': f'{peak_kind} bf16 burst / 2 (dense TF32 is half the bf16 rate; not measured separately)',
+        'traffic': None,
+        'launches_per_step': conv['launches'], 'avg_launch_us': round(1e3 * conv['ms'] / max(1, conv['launches']), 3),
+        'flops_per_step': conv['work'],
+        'share_of_device_time': round(conv['ms'] / total_ms, 4) if total_ms else None,
+        'other_kernels': {k: {'launches': v['launches'], 'ms': round(v['ms'], 4),
+                              'GB/s': round(v['work'] / (v['ms'] * 1e-3) / 1e9, 1) if v['ms'] > 0 else None}
+                          for k, v in by_kind.items() if k != 'conv_tc'},
+    }
+    ncu_traffic = os.path.join(ROOT, 'profiles', 'conv_tc_traffic.json')
+    if os.path.exists(ncu_traffic):
+        with open(ncu_traffic) as fh:
+            roofline['traffic'] = json.load(fh).get('dram_bytes_per_step')
+
+    line = {
+        'metric': METRIC, 'value': round(value, 2), 'unit': 'images/s', 'n_gpus': ranks.world, 'steps': args.steps,
+        'warmup': args.warmup, 'ms_per_step': round(ms_per_step, 5), 'higher_is_better': True, 'scaling': 'weak',
+        'vs_baseline': None, 'dtype': 'tf32 (fp32 storage and accumulate)', 'data': 'synthetic',
+        'config': {'workload': f'{args.model} batch {args.batch} per GPU, schedule {args.schedule} '
+                               f'({info["stages"]} stages, {info["launches"]} launches)',
+                   'global_batch': images, 'input': list(x.shape[1:]), 'parallelism':
+                       'single GPU' if ranks.world == 1 else f'{ranks.world} independent replicas (batch 1 does not shard)',
+                   'l2': 'flushed between steps by a 256 MiB write', 'schedule_search_s': round(search_s, 1)},
+        'e2e': {'value': round(e2e_value, 2), 'unit': 'images/s', 'ms_per_step': round(e2e_ms, 5),
+                'h2d_bytes_per_step': int(x.nbytes), 'd2h_bytes_per_step': int(y.nbytes)},
+        'gpu_launches': (info['launches'] + 2) * args.steps * 2 + info['launches'] * max(10, args.steps),
+        'warm_l2_ms_per_step': round(warm_ms, 5),
+        'wall_s_timed_region': round(wall_s, 3),
+        'clocks': clocks, 'roofline': roofline,
+    }
+
+    if ranks.rank == 0:
+        ref = oracle.run_config(base_config, weights, x)
+        line['parity_max_rel_err'] = float(f'{oracle.max_rel_err(y, ref):.3e}')
+        if ranks.world == 1 and not args.no_cpu_baseline:
+            line['cpu_baseline'] = cpu_baseline(base_config, weights, x, args.batch)
+        print(json.dumps(line), flush=True)
+    engine.close()
+    ranks.finish()
+
+
+def cpu_baseline(config, weights, x, batch, budget_s=15.0):
+    """The CPU oracle on the host cores: as many forwards of the same workload as fit the budget."""
+    import torch
+    import ios_oracle as oracle
+    cores = torch.get_num_threads()
+    oracle.run_config(config, weights, x)
+    t0 = time.perf_counter()
+    n = 0
+    while n < 3 or (time.perf_counter() - t0 < budget_s and n < 200):
+        oracle.run_config(config, weights, x)
+        n += 1
+    per = (time.perf_counter() - t0) / n
+    return {'value': round(batch / per, 2), 'unit': 'images/s', 'ms_per_step': round(per * 1e3, 3), 'cores': cores,
+            'kind': 'port', 'sample': f'{n} forwards of the same graph and input on the host cores (torch CPU float32 '
+                                      f'restatement of the reference executor ios.torch_utils.Net)'}
+
+
+# ------------------------------------------------------------------------------------------------
+class ReferenceRuntime:
+    """The reference's own libios_runtime.so (cuDNN), driven with this package's JSON."""
+
+    def __init__(self):
+        self.lib = ctypes.cdll.LoadLibrary(os.path.join(ROOT, 'oracle', '_ref', 'libios_runtime_ref.so'))
+
+    def graph_latency(self, graph, batch, warmup, number, repeat):
+        text = json.dumps(graph.export_config()).encode()
+        n_stages = sum(len(b.stages) for b in graph.blocks)
+        res = (ctypes.c_float * repeat)()
+        stage = (ctypes.c_float * (repeat * n_stages))()
+        self.lib.graph_latency(ctypes.c_char_p(text), batch, warmup, number, repeat, 0, res, stage)
+        return [float(v) for v in res]
+
+    def stage_latency(self, stage, batch, warmup, number, repeat):
+        from ios.contrib.ios_runtime import stage_config
+        stage_text, input_text = stage_config(stage)
+        res = (ctypes.c_float * repeat)()
+        unused = (ctypes.c_float * repeat)()
+        self.lib.stage_latency(ctypes.c_char_p(stage_text.encode()), ctypes.c_char_p(input_text.encode()), batch,
+                               warmup, number, repeat, 0, res, unused)
+        return [float(v) for v in res]
+
+
+def run_reference(args):
+    rank = int(os.environ.get('RANK', '0'))
+    if rank != 0:
+        return
+    import ios
+    import ios_oracle as oracle
+    graph = build_graph(args.model)
+    weights = seeded_weights(graph, 0)
+    config = graph.export_config()
+    x = oracle.normal_input(config, args.batch, 0)
+    line = {'impl': 'reference', 'metric': METRIC, 'unit': 'images/s', 'n_gpus': 1, 'steps': args.steps,
+            'warmup': args.warmup, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
+            'data': 'synthetic'}
+    try:
+        ref = ReferenceRuntime()
+    except OSError as err:
+        ref = None
+        log(f'reference runtime not loadable ({err}); timing the CPU oracle instead')
+    if ref is not None:
+        class RefCost(ios.cost_model.CostModel):
+            def get_stage_latency(self, stage, batch_size, warmup, number, repeat, profile_stage=False):
+                return ref.stage_latency(stage, batch_size, warmup, number, repeat)
+
+        exec_graph, search_s = schedule_graph(graph, args.schedule, args.batch, cost_model=RefCost())
+        samples = ref.graph_latency(exec_graph, args.batch, args.warmup, 1, args.steps)
+        ms = float(np.mean(samples))
+        value = args.batch / (ms * 1e-3)
+        line.update({
+            'value': round(value, 2), 'ms_per_step': round(ms, 5), 'dtype': 'fp32 (cuDNN default math)',
+            'config': {'workload': f'{args.model} batch {args.batch}, schedule {args.schedule} found by the same DP '
+                                   f'search on the reference runtime\'s own stage_latency '
+                                   f'({sum(len(b.stages) for b in exec_graph.blocks)} stages)',
+                       'global_batch': args.batch, 'parallelism': 'single GPU', 'schedule_search_s': round(search_s, 1),
+                       'l2': 'not flushed (the reference times back-to-back forwards inside graph_latency)'},
+            'cpu_baseline': {'value': round(value, 2), 'unit': 'images/s', 'kind': 'reference', 'cores': 0,
+                             'sample': 'the reference runtime executes on the GPU through cuDNN (it has no CPU '
+                                       'executor in C++); graph_latency(warmup, number=1, repeat=steps) on device 0'},
+            'e2e': {'value': round(value, 2), 'unit': 'images/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+        })
+    else:
+        graph.sequential_schedule()
+        base = cpu_baseline(config, weights, x, args.batch, budget_s=20.0)
+        line.update({'value': base['value'], 'ms_per_step': base['ms_per_step'], 'dtype': 'fp32',
+                     'config': {'workload': f'{args.model} batch {args.batch} on the host cores', 'global_batch': args.batch},
+                     'cpu_baseline': base,
+                     'e2e': {'value': base['value'], 'unit': 'images/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0}})
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=200)
+    ap.add_argument('--warmup', type=int, default=5)
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--model', default='inception_v3')
+    ap.add_argument('--batch', type=int, default=1, help='images per GPU per step')
+    ap.add_argument('--schedule', default='dp', choices=['dp', 'sequential', 'greedy'])
+    ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--executor', default='graph', choices=['graph', 'streams'],
+                    help='streams: plain launches instead of a CUDA graph (used for kernel-level profiling)')
+    ap.add_argument('--precision', default=None, help='runtime precision option (default: the library default)')
+    args = ap.parse_args()
+    args.warmup = max(3, args.warmup)
+    if args.impl == 'reference':
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == '__main__':
+    main()

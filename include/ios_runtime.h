@@ -67,11 +67,14 @@ IOS_API int ios_graph_inference(const char *graph_json, int batch_size, const fl
 IOS_API const char *ios_last_error(void);
 
 /* ---- run-time options (replace the reference's compile-time switches, config.cmake:8-17) ----
- * key "precision": "tf32" (default; fp32 storage, TF32 tensor-core products, fp32 accumulate),
+ * key "precision": "tf32x3" (default; fp32 storage, every product formed from three TF32 tensor-core
+ *                  products of value/residual operand pairs, fp32 accumulate: fp32-grade results),
+ *                  "tf32" (one TF32 product per multiply: fastest, about 3e-4 relative error per layer),
  *                  "fp32" (CUDA-core fp32 products, the slow exact path)
  * key "executor":  "graph" (default; a schedule is captured once into a CUDA graph),
  *                  "streams" (group j of every stage is launched on stream j, events between stages)
  * key "conv":      "auto" (default), "direct" (never use the tensor-core kernel)
+ * key "pdl":       "1" (default; consecutive convolution kernels use programmatic dependent launch), "0"
  * Options apply to plans built afterwards on the calling process. */
 IOS_API int ios_set_option(const char *key, const char *value);
 IOS_API int ios_get_option(const char *key, char *value, int capacity);
@@ -97,6 +100,13 @@ IOS_API int ios_engine_time(ios_engine *engine, int iters, float *ms_per_iter);
 /* Describe the plan: writes a JSON text (kernel launches per forward, arena bytes, workspace bytes,
  * algorithmic FLOPs, output shape) into text[capacity]. */
 IOS_API int ios_engine_describe(ios_engine *engine, char *text, int capacity);
+/* Per-launch device times of one forward: the launches run one after another on a single stream
+ * with a CUDA event between them, averaged over `iters` passes.  step_kind: 0 sum/copy, 1 pool,
+ * 2 tensor-core conv, 3 CUDA-core conv, 4 depthwise conv.  step_work: algorithmic FLOPs (2*MAC) for
+ * kinds 2 and 3, algorithmic bytes (inputs read once + output written once) for kinds 0, 1, 4.
+ * Replaces the CUPTI sampling thread of the reference (src/ios/profile.cu:49-143). */
+IOS_API int ios_engine_profile(ios_engine *engine, int iters, int capacity, int *count, float *step_ms,
+                               int *step_kind, double *step_work);
 /* Upload the input once (for ios_engine_time) / read back the last output. */
 IOS_API int ios_engine_set_input(ios_engine *engine, const float *input);
 IOS_API int ios_engine_get_output(ios_engine *engine, float *output);
@@ -105,7 +115,8 @@ IOS_API int ios_engine_get_output(ios_engine *engine, float *output);
  *      reference reaches its operators only through a graph; ConvOP::forward is
  *      src/ios/ios_runtime.cu:309-332, PoolOP::forward :563-566) ------------------------------ */
 /* y[n, cout, oh, ow] = act(conv(x[n, cin, h, w], w[cout, cin/groups, kh, kw]) + bias).
- * act: 0 identity, 1 relu, 2 sigmoid, 3 tanh.  impl: 0 auto, 1 direct (CUDA cores), 2 tensor core. */
+ * act: 0 identity, 1 relu, 2 sigmoid, 3 tanh.  impl: 0 auto, 1 direct (CUDA cores), 2 tensor cores with the
+ * current precision option, 3 tensor cores single-pass TF32. */
 IOS_API int ios_conv2d(const float *x, const float *w, const float *bias, float *y, int n, int cin, int h,
                        int wdt, int cout, int kh, int kw, int sh, int sw, int ph, int pw, int groups,
                        int act, int impl);

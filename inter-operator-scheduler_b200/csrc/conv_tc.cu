@@ -48,7 +48,10 @@ struct TileGeom {
     int bn, cchunks, k_iters, split_k, stages, flat;
     int a_bytes;      // bytes one A load delivers
     int tmem_cols;
-    int round_tf32;   // round the stored result to TF32 (the consumer is a tensor-core convolution)
+    int round_tf32;   // round the stored result to TF32 (the consumer is a single-pass tensor-core convolution)
+    int x3;           // 1: three-pass TF32 (value + residual of both operands), fp32-grade products
+    int cout_pad;     // rows of one plane of the packed weight matrix
+    int tma_store;    // 1: the epilogue stages the tile in shared memory and stores it with bulk tensor stores
 };
 
 // ---- PTX wrappers ----------------------------------------------------------------------------
@@ -77,13 +80,17 @@ __device__ __forceinline__ uint64_t global_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-// Bounded wait: false when the budget ran out.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+// Bounded wait: false when the budget ran out, or when another CTA of the grid has already
+// reported a wait that ran out (so that one stuck tile does not cost the budget once per CTA).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const int *error_flag) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_ns();
     for (uint32_t spin = 1;; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((spin & 255u) == 0 && global_ns() - t0 > kWaitBudgetNs) return false;
+        if ((spin & 1023u) == 0) {
+            if (global_ns() - t0 > kWaitBudgetNs) return false;
+            if (error_flag && *reinterpret_cast<const volatile int *>(error_flag) != 0) return false;
+        }
     }
 }
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void *tmap, uint32_t bar, int c0, int c1, int c2, int c3) {
@@ -97,6 +104,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void *tmap, uint
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1)
         : "memory");
+}
+__device__ __forceinline__ void tma_store_4d(const void *tmap, uint32_t src, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 ::"l"(tmap), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
@@ -155,28 +167,42 @@ __device__ __forceinline__ float round_tf32(float v) {
     return __uint_as_float(r);
 }
 
+// Optional diagnostics: CTA (0,0,0) stamps the SM clock at fixed points of its life.
+#define STAMP(slot)                                                                     \
+    do {                                                                                \
+        if (p.timeline && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) p.timeline[slot] = clock64(); \
+    } while (0)
+
+// Byte offset of 16-byte column `c4` of row `row` inside a [rows][128 B] tile with the 128-byte swizzle.
+__device__ __forceinline__ uint32_t sw128_offset(int row, int c4) {
+    return uint32_t(row) * 128u + (uint32_t(c4 ^ (row & 7)) << 4);
+}
+
 // ---- the kernel ------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kThreads, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-               const ConvTcParams p, const TileGeom t) {
+               const __grid_constant__ CUtensorMap tmap_c, const ConvTcParams p, const TileGeom t) {
     extern __shared__ uint8_t smem_raw[];
+    __shared__ float bias_s[256];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const int b_bytes = t.bn * kChunk * 4;
-    const int stage_bytes = kATileBytes + b_bytes;
-    const uint32_t bars = smem_base + uint32_t(t.stages) * stage_bytes;   // full[stages], empty[stages], accum
-    const uint32_t full0 = bars, empty0 = bars + 8u * t.stages, accum_bar = bars + 16u * t.stages;
     uint8_t *generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
-    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(generic_base + size_t(t.stages) * stage_bytes + 16 * t.stages + 8);
+    const int b_bytes = t.bn * kChunk * 4;
+    const int passes = t.x3 ? 2 : 1;                       // operand planes per stage: value (+ residual)
+    const int stage_bytes = passes * (kATileBytes + b_bytes);
+    // stage layout: A | A residual | B | B residual
+    const uint32_t a_lo_off = kATileBytes;
+    const uint32_t b_off = uint32_t(passes) * kATileBytes;
+    const uint32_t b_lo_off = b_off + uint32_t(b_bytes);
+    const uint32_t bars = smem_base + uint32_t(t.stages) * stage_bytes;
+    const uint32_t full0 = bars, empty0 = bars + 8u * t.stages, ready0 = bars + 16u * t.stages;
+    const uint32_t accum_bar = bars + 24u * t.stages;
+    volatile uint32_t *tmem_slot =
+        reinterpret_cast<volatile uint32_t *>(generic_base + size_t(t.stages) * stage_bytes + 24 * t.stages + 8);
     volatile int *ticket_slot = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const ConvGeom &g = p.g;
-
-    // a wait that ran out in an earlier CTA of this launch makes the rest of the grid return at once
-    __shared__ int abort_launch;
-    if (threadIdx.x == 0) abort_launch = *reinterpret_cast<volatile int *>(p.error_flag);
-    __syncthreads();
-    if (abort_launch != 0) return;
+    if (threadIdx.x == 0) STAMP(0);
 
     // tile coordinates
     const int m_tile = blockIdx.x, n_tile = blockIdx.y, split = blockIdx.z;
@@ -199,6 +225,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         for (int s = 0; s < t.stages; ++s) {
             mbar_init(full0 + 8u * s, 1);
             mbar_init(empty0 + 8u * s, 1);
+            mbar_init(ready0 + 8u * s, 128);
         }
         mbar_init(accum_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -212,64 +239,116 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) STAMP(1);
+    // Everything above touches no global memory, so under programmatic dependent launch it overlaps
+    // the tail of the previous kernel; the next kernel may start its own prologue from here on.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == 0) {
         if (lane == 0) {
             // ---------------- TMA producer ----------------
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             bool ok = true;
             int issued = 0;
             for (int i = 0; i < n_it && ok; ++i) {
                 const int s = i % t.stages;
-                if (i >= t.stages) ok = mbar_wait(empty0 + 8u * s, uint32_t((i / t.stages - 1) & 1));
+                if (i >= t.stages) ok = mbar_wait(empty0 + 8u * s, uint32_t((i / t.stages - 1) & 1), p.error_flag);
                 if (!ok) break;
                 const int it = it_begin + i;
                 const int tap = it / t.cchunks, cc = it - tap * t.cchunks;
                 const int r = tap / g.kw, sx = tap - r * g.kw;
-                const uint32_t a_dst = smem_base + uint32_t(s) * stage_bytes;
+                const uint32_t stage = smem_base + uint32_t(s) * stage_bytes;
                 const uint32_t bar = full0 + 8u * s;
-                mbar_expect_tx(bar, uint32_t(t.a_bytes + b_bytes));
-                if (t.flat) tma_load_4d(a_dst, &tmap_a, bar, cc * kChunk, ow0, 0, 0);
-                else tma_load_4d(a_dst, &tmap_a, bar, cc * kChunk, ow0 * g.sw - g.pw + sx, oh0 * g.sh - g.ph + r, n0);
-                tma_load_2d(a_dst + kATileBytes, &tmap_b, bar, it * kChunk, cout0);
+                mbar_expect_tx(bar, uint32_t(t.a_bytes + passes * b_bytes));
+                if (t.flat) tma_load_4d(stage, &tmap_a, bar, cc * kChunk, ow0, 0, 0);
+                else tma_load_4d(stage, &tmap_a, bar, cc * kChunk, ow0 * g.sw - g.pw + sx, oh0 * g.sh - g.ph + r, n0);
+                tma_load_2d(stage + b_off, &tmap_b, bar, it * kChunk, cout0);
+                if (t.x3) tma_load_2d(stage + b_lo_off, &tmap_b, bar, it * kChunk, t.cout_pad + cout0);
+                if (i == 0) STAMP(2);
                 issued = i + 1;
             }
             if (!ok) {
                 atomicExch(p.error_flag, 1);
                 // drain: the loads already issued still land in this CTA's shared memory
                 for (int i = max(0, issued - t.stages); i < issued; ++i)
-                    mbar_wait(full0 + 8u * (i % t.stages), uint32_t((i / t.stages) & 1));
+                    mbar_wait(full0 + 8u * (i % t.stages), uint32_t((i / t.stages) & 1), nullptr);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             // ---------------- MMA issuer ----------------
             const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(t.bn >> 3) << 17) | (uint32_t(kTileM >> 4) << 24);
+            const uint32_t wait0 = t.x3 ? ready0 : full0;
             bool ok = true;
             for (int i = 0; i < n_it; ++i) {
                 const int s = i % t.stages;
-                ok = mbar_wait(full0 + 8u * s, uint32_t((i / t.stages) & 1));
+                ok = mbar_wait(wait0 + 8u * s, uint32_t((i / t.stages) & 1), p.error_flag);
                 if (!ok) break;
+                if (i == 0) STAMP(3);
                 tc_fence_after();
-                const uint32_t a_addr = smem_base + uint32_t(s) * stage_bytes;
-                const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + kATileBytes);
+                const uint32_t stage = smem_base + uint32_t(s) * stage_bytes;
+                const uint64_t da = smem_desc_sw128(stage), db = smem_desc_sw128(stage + b_off);
+                if (t.x3) {
+                    // a*w ~= a_lo*w_hi + a_hi*w_lo + a_hi*w_hi, small terms first
+                    const uint64_t dal = smem_desc_sw128(stage + a_lo_off), dbl = smem_desc_sw128(stage + b_lo_off);
 #pragma unroll
-                for (int k = 0; k < kChunk / 8; ++k)
-                    umma_tf32(tmem_base, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < kChunk / 8; ++k) {
+                        umma_tf32(tmem_base, dal + uint64_t(k * 2), db + uint64_t(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+                        umma_tf32(tmem_base, da + uint64_t(k * 2), dbl + uint64_t(k * 2), idesc, 1u);
+                        umma_tf32(tmem_base, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, 1u);
+                    }
+                } else {
+#pragma unroll
+                    for (int k = 0; k < kChunk / 8; ++k)
+                        umma_tf32(tmem_base, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+                }
                 umma_commit(empty0 + 8u * s);   // frees the stage once these MMAs have read it
             }
             if (ok) umma_commit(accum_bar);
             else atomicExch(p.error_flag, 2);
+            STAMP(4);
         }
     } else {
-        // ---------------- epilogue: warps 2..5, one thread per TMEM lane ----------------
+        // ---------------- warps 2..5: operand split (3-pass mode), then the epilogue ----------------
+        const int tid = threadIdx.x - 64;           // 0..127
         const int quad = warp & 3;                  // TMEM lane group this warp may read
         const int row = quad * 32 + lane;
-        bool ok = mbar_wait(accum_bar, 0);
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        for (int j = tid; j < t.bn; j += 128) bias_s[j] = (p.bias && cout0 + j < g.Cout) ? p.bias[cout0 + j] : 0.0f;
+        bool ok = true;
+        if (t.x3) {
+            // Split every fp32 activation that landed into a TF32-exact value (in place) and its residual.
+            const int n_vec = t.a_bytes >> 4;
+            for (int i = 0; i < n_it && ok; ++i) {
+                const int s = i % t.stages;
+                ok = mbar_wait(full0 + 8u * s, uint32_t((i / t.stages) & 1), p.error_flag);
+                if (!ok) break;
+                uint8_t *stage = generic_base + size_t(s) * stage_bytes;
+                float4 *hi = reinterpret_cast<float4 *>(stage);
+                float4 *lo = reinterpret_cast<float4 *>(stage + a_lo_off);
+                for (int v = tid; v < n_vec; v += 128) {
+                    float4 x = hi[v];
+                    float4 h, l;
+                    h.x = __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u); l.x = x.x - h.x;
+                    h.y = __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u); l.y = x.y - h.y;
+                    h.z = __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u); l.z = x.z - h.z;
+                    h.w = __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u); l.w = x.w - h.w;
+                    hi[v] = h;
+                    lo[v] = l;
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(ready0 + 8u * s) : "memory");
+            }
+        }
+        if (ok) ok = mbar_wait(accum_bar, 0, p.error_flag);
+        ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
         if (!ok && lane == 0) atomicExch(p.error_flag, 3);
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (threadIdx.x == 64) STAMP(5);
         tc_fence_after();
+        asm volatile("bar.sync 1, 128;" ::: "memory");          // bias_s is complete
+        if (threadIdx.x == 64) STAMP(9);
         const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16);
         const int tile_id = m_tile * gridDim.y + n_tile;
         bool finisher = true;
@@ -291,9 +370,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             asm volatile("bar.sync 1, 128;" ::: "memory");
             finisher = (*ticket_slot == t.split_k - 1);
             if (finisher) __threadfence();
+            if (threadIdx.x == 64) STAMP(6);
         }
         if (ok && finisher) {
-            // which output pixel does this row hold?
+            // which output pixel does this row hold? (only the direct-store path needs it)
             long pix_off = -1;
             if (t.flat) {
                 const long pix = long(ow0) + row;
@@ -317,20 +397,38 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 } else {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) v[j] = 0.0f;
-                    for (int s = 0; s < t.split_k; ++s) {
-                        const float *src = ws_tile + size_t(s) * t.bn * kTileM + size_t(c) * kTileM + row;
+                    // four partial tiles per round trip, added in split order
+                    for (int s0 = 0; s0 < t.split_k; s0 += 4) {
+                        float part[4][16];
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) v[j] += __ldcg(src + size_t(j) * kTileM);
+                        for (int u = 0; u < 4; ++u) {
+                            const float *src = ws_tile + size_t(min(s0 + u, t.split_k - 1)) * t.bn * kTileM + size_t(c) * kTileM + row;
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) part[u][j] = __ldcg(src + size_t(j) * kTileM);
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+                            if (s0 + u < t.split_k) {
+#pragma unroll
+                                for (int j = 0; j < 16; ++j) v[j] += part[u][j];
+                            }
                     }
                 }
-                if (pix_off < 0 || c >= valid) continue;
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                    const int co = cout0 + c + j;
-                    float o = v[j] + ((p.bias && co < g.Cout) ? p.bias[co] : 0.0f);
-                    o = act_apply(o, g.act);
+                    float o = act_apply(v[j] + bias_s[c + j], g.act);
                     v[j] = t.round_tf32 ? round_tf32(o) : o;
                 }
+                if (t.tma_store) {
+                    // stage the tile as [32-channel slab][row][128 B], swizzled like a TMA box, for the bulk store
+                    uint8_t *slab = generic_base + size_t(c >> 5) * kATileBytes;
+                    const int c4 = (c & 31) >> 2;
+#pragma unroll
+                    for (int j = 0; j < 16; j += 4)
+                        *reinterpret_cast<float4 *>(slab + sw128_offset(row, c4 + (j >> 2))) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    continue;
+                }
+                if (pix_off < 0 || c >= valid) continue;
                 if (vec_ok && c + 16 <= valid) {
 #pragma unroll
                     for (int j = 0; j < 16; j += 4)
@@ -341,14 +439,33 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         if (c + j < valid) dst[c + j] = v[j];
                 }
             }
+            if (threadIdx.x == 64) STAMP(10);
+            if (t.tma_store) {
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (threadIdx.x == 64) {
+                    STAMP(11);
+                    // one bulk tensor store per 32-channel slab; pixels and channels outside the tensor are clipped
+                    for (int c = 0; c < valid; c += 32) {
+                        const uint32_t src = smem_base + uint32_t(c >> 5) * kATileBytes;
+                        if (t.flat) tma_store_4d(&tmap_c, src, cout0 + c, ow0, 0, 0);
+                        else tma_store_4d(&tmap_c, src, cout0 + c, ow0, oh0, n0);
+                    }
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    STAMP(12);
+                    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                }
+            }
             if (t.split_k > 1 && threadIdx.x == 64) p.counters[tile_id] = 0;   // ready for the next launch
         }
+        if (threadIdx.x == 64) STAMP(7);
         tc_fence_before();
     }
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, uint32_t(t.tmem_cols));
+        if (lane == 0) STAMP(8);
     }
 }
 
@@ -392,8 +509,9 @@ bool conv_tc_supported(const TensorRef &in, const ConvGeom &g) {
     return true;
 }
 
-void conv_tc_choose(const ConvGeom &g, int sm_count, int concurrency_hint, ConvTcPlan *plan) {
+void conv_tc_choose(const ConvGeom &g, int sm_count, int concurrency_hint, bool three_pass, ConvTcPlan *plan) {
     ConvTcPlan &q = *plan;
+    q.x3 = three_pass ? 1 : 0;
     const bool flat = g.kh == 1 && g.kw == 1 && g.sh == 1 && g.sw == 1 && g.ph == 0 && g.pw == 0;
     q.flat_1x1 = flat ? 1 : 0;
     if (flat) {
@@ -422,41 +540,58 @@ void conv_tc_choose(const ConvGeom &g, int sm_count, int concurrency_hint, ConvT
     }
     const int m_tiles = q.tiles_w * q.tiles_h * q.tiles_n;
     const int target = std::max(1, sm_count / std::max(1, concurrency_hint));
-    // output-channel tiling: wide tiles when the pixel tiles alone fill the machine, else narrow
-    int n_tiles = ceil_div(g.Cout, m_tiles * ceil_div(g.Cout, 128) >= target ? 128 : 64);
-    q.bn = std::min(256, ceil_div(ceil_div(g.Cout, n_tiles), 16) * 16);
+    // output-channel tiling (multiples of 32: one 128-byte slab of the store staging per 32 channels):
+    // wide tiles when the pixel tiles alone fill the machine, else narrow ones for more CTAs
+    const int n_tiles = ceil_div(g.Cout, m_tiles * ceil_div(g.Cout, 128) >= target ? 128 : 64);
+    q.bn = std::min(256, ceil_div(ceil_div(g.Cout, n_tiles), 32) * 32);
     q.n_tiles = ceil_div(g.Cout, q.bn);
     q.cout_pad = q.n_tiles * q.bn;
     q.cchunks = ceil_div(g.Cin, kChunk);
     q.k_iters = g.kh * g.kw * q.cchunks;
+    // Split K only when the K loop is long: a split costs a trip through the workspace and one
+    // atomic ticket, which is worth about ten K steps.
     const int base = m_tiles * q.n_tiles;
     int split = 1;
-    if (base < target) {
-        split = std::min(target / base, q.k_iters / 3);
+    if (base < target && q.k_iters >= 16) {
+        split = std::min(target / base, q.k_iters / 8);
         split = std::max(1, std::min(split, 32));
     }
+    conv_tc_set_split(&q, split);
+}
+
+void conv_tc_set_split(ConvTcPlan *plan, int split) {
+    ConvTcPlan &q = *plan;
+    split = std::max(1, std::min(split, q.k_iters));
+    const int base = q.tiles_w * q.tiles_h * q.tiles_n * q.n_tiles;
     q.split_k = split;
-    const int stage_bytes = kATileBytes + q.bn * kChunk * 4;
+    const int stage_bytes = (q.x3 ? 2 : 1) * (kATileBytes + q.bn * kChunk * 4);
     const int per_split = ceil_div(q.k_iters, split);
-    q.stages = std::max(2, std::min({6, per_split, (200 * 1024) / stage_bytes}));
-    q.smem_bytes = size_t(q.stages) * stage_bytes + 16 * q.stages + 64 + 1024;
+    q.stages = std::max(2, std::min({8, per_split, (200 * 1024) / stage_bytes}));
+    // the store staging needs one 16 KiB slab per 32 output channels inside the pipeline buffers
+    while (q.stages * stage_bytes < (q.bn / 32) * kATileBytes) ++q.stages;
+    q.smem_bytes = size_t(q.stages) * stage_bytes + 24 * q.stages + 64 + 1024;
     q.workspace_bytes = split > 1 ? size_t(base) * split * q.bn * kTileM * sizeof(float) : 0;
     q.counter_bytes = split > 1 ? size_t(base) * sizeof(unsigned int) : 0;
 }
 
 size_t conv_tc_packed_floats(const ConvGeom &g, const ConvTcPlan &plan) {
-    return size_t(plan.cout_pad) * g.kh * g.kw * plan.cchunks * kChunk;
+    return size_t(plan.x3 ? 2 : 1) * plan.cout_pad * g.kh * g.kw * plan.cchunks * kChunk;
 }
 
 void conv_tc_pack_weights(const float *oihw, const ConvGeom &g, const ConvTcPlan &plan, float *packed) {
     const int taps = g.kh * g.kw;
     const size_t row = size_t(taps) * plan.cchunks * kChunk;
-    std::memset(packed, 0, size_t(plan.cout_pad) * row * sizeof(float));
+    const size_t plane = size_t(plan.cout_pad) * row;
+    std::memset(packed, 0, (plan.x3 ? 2 : 1) * plane * sizeof(float));
     for (int o = 0; o < g.Cout; ++o)
         for (int c = 0; c < g.Cin; ++c)
-            for (int tp = 0; tp < taps; ++tp)
-                packed[size_t(o) * row + size_t(tp) * plan.cchunks * kChunk + c] =
-                    tf32_round_host(oihw[(size_t(o) * g.Cin + c) * taps + tp]);
+            for (int tp = 0; tp < taps; ++tp) {
+                const float w = oihw[(size_t(o) * g.Cin + c) * taps + tp];
+                const float hi = tf32_round_host(w);
+                const size_t at = size_t(o) * row + size_t(tp) * plan.cchunks * kChunk + c;
+                packed[at] = hi;
+                if (plan.x3) packed[plane + at] = tf32_round_host(w - hi);   // residual plane
+            }
 }
 
 const char *conv_tc_encode(const ConvTcParams &p, ConvTcPlan *plan) {
@@ -464,7 +599,11 @@ const char *conv_tc_encode(const ConvTcParams &p, ConvTcPlan *plan) {
     if (!encode) return "cuTensorMapEncodeTiled is not available from the driver";
     const ConvGeom &g = p.g;
     ConvTcPlan &q = *plan;
-    static char msg[160];
+    static thread_local char msg[160];
+    auto fail = [&](const char *what, CUresult r) {
+        std::snprintf(msg, sizeof msg, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, int(r));
+        return msg;
+    };
     {
         cuuint64_t dims[4];
         cuuint64_t strides[3];
@@ -484,14 +623,11 @@ const char *conv_tc_encode(const ConvTcParams &p, ConvTcPlan *plan) {
         CUresult r = encode(reinterpret_cast<CUtensorMap *>(q.tmap_a), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.in.ptr, dims,
                             strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) {
-            std::snprintf(msg, sizeof msg, "cuTensorMapEncodeTiled(activations) failed with CUresult %d", int(r));
-            return msg;
-        }
+        if (r != CUDA_SUCCESS) return fail("activations", r);
     }
     {
         const cuuint64_t krow = cuuint64_t(g.kh) * g.kw * q.cchunks * kChunk;
-        cuuint64_t dims[2] = {krow, cuuint64_t(q.cout_pad)};
+        cuuint64_t dims[2] = {krow, cuuint64_t(q.cout_pad) * (q.x3 ? 2 : 1)};
         cuuint64_t strides[1] = {krow * 4};
         cuuint32_t box[2] = {kChunk, cuuint32_t(q.bn)};
         cuuint32_t estr[2] = {1, 1};
@@ -499,10 +635,31 @@ const char *conv_tc_encode(const ConvTcParams &p, ConvTcPlan *plan) {
                             const_cast<float *>(p.weight_packed), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) {
-            std::snprintf(msg, sizeof msg, "cuTensorMapEncodeTiled(weights) failed with CUresult %d", int(r));
-            return msg;
+        if (r != CUDA_SUCCESS) return fail("weights", r);
+    }
+    // the output window: bulk tensor stores need a 16-byte aligned base
+    // and a window whose end is 16-byte aligned too, so that clipping never lands inside a 16-byte unit
+    q.tma_store = ((reinterpret_cast<uintptr_t>(p.out.ptr) & 15) == 0 && p.out.pitch % 4 == 0 && g.Cout % 4 == 0) ? 1 : 0;
+    std::memcpy(q.tmap_c, q.tmap_a, sizeof q.tmap_c);
+    if (q.tma_store) {
+        cuuint64_t dims[4];
+        cuuint64_t strides[3];
+        cuuint32_t box[4];
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        const cuuint64_t pix_bytes = cuuint64_t(p.out.pitch) * 4;
+        if (q.flat_1x1) {
+            dims[0] = cuuint64_t(g.Cout); dims[1] = cuuint64_t(g.N) * g.OH * g.OW; dims[2] = 1; dims[3] = 1;
+            strides[0] = pix_bytes; strides[1] = pix_bytes * dims[1]; strides[2] = strides[1];
+            box[0] = kChunk; box[1] = cuuint32_t(q.box_w); box[2] = 1; box[3] = 1;
+        } else {
+            dims[0] = cuuint64_t(g.Cout); dims[1] = cuuint64_t(g.OW); dims[2] = cuuint64_t(g.OH); dims[3] = cuuint64_t(g.N);
+            strides[0] = pix_bytes; strides[1] = pix_bytes * g.OW; strides[2] = pix_bytes * g.OW * g.OH;
+            box[0] = kChunk; box[1] = cuuint32_t(q.box_w); box[2] = cuuint32_t(q.box_h); box[3] = cuuint32_t(q.box_n);
         }
+        CUresult r = encode(reinterpret_cast<CUtensorMap *>(q.tmap_c), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.out.ptr, dims,
+                            strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                            CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail("output", r);
     }
     return nullptr;
 }
@@ -522,9 +679,22 @@ void launch_conv_tc(const ConvTcParams &p, const ConvTcPlan &q, cudaStream_t str
     while (cols < q.bn) cols *= 2;
     t.tmem_cols = cols;
     t.round_tf32 = p.g.round_out;
-    dim3 grid(q.tiles_w * q.tiles_h * q.tiles_n, q.n_tiles, q.split_k);
-    conv_tc_kernel<<<grid, kThreads, q.smem_bytes, stream>>>(*reinterpret_cast<const CUtensorMap *>(q.tmap_a),
-                                                             *reinterpret_cast<const CUtensorMap *>(q.tmap_b), p, t);
+    t.x3 = q.x3;
+    t.cout_pad = q.cout_pad;
+    t.tma_store = q.tma_store;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(q.tiles_w * q.tiles_h * q.tiles_n, q.n_tiles, q.split_k);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = q.smem_bytes;
+    cfg.stream = stream;
+    // programmatic dependent launch: this kernel's prologue may overlap the tail of its predecessor
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = q.pdl ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, conv_tc_kernel, *reinterpret_cast<const CUtensorMap *>(q.tmap_a),
+                       *reinterpret_cast<const CUtensorMap *>(q.tmap_b), *reinterpret_cast<const CUtensorMap *>(q.tmap_c), p, t);
 }
 
 }  // namespace ios

@@ -76,7 +76,8 @@ void launch_conv_direct(const ConvDirectParams &p, cudaStream_t stream);
 void launch_conv_depthwise(const ConvDirectParams &p, cudaStream_t stream);
 
 // Tensor-core implicit-GEMM convolution (tcgen05 + TMEM + TMA), groups == 1.
-// Packed weights: [Cout_pad][taps][cchunks*32] float32 (TF32-rounded), zero padded.
+// Packed weights: [planes][Cout_pad][taps][cchunks*32] float32, zero padded; plane 0 holds the
+// weights rounded to TF32, plane 1 (three-pass mode only) the TF32-rounded residuals.
 struct ConvTcPlan {
     // tile geometry chosen by conv_tc_plan()
     int box_w, box_h, box_n;       // output pixels covered by one M tile along W, H, batch
@@ -88,12 +89,16 @@ struct ConvTcPlan {
     int split_k;                   // CTAs sharing one output tile
     int stages;                    // smem pipeline depth
     int flat_1x1;                  // 1: pixels flattened into one axis (1x1, stride 1, no padding)
+    int x3;                        // 1: three-pass TF32 (operands split into value + residual)
+    int tma_store;                 // 1: the output window is 16-byte aligned, the epilogue uses bulk tensor stores
+    int pdl;                       // 1: launch with programmatic stream serialization
     size_t smem_bytes;
     size_t workspace_bytes;        // split-K partial tiles (0 when split_k == 1)
     size_t counter_bytes;          // split-K arrival counters
     int cout_pad;                  // rows of the packed weight matrix
     alignas(64) unsigned char tmap_a[128];   // CUtensorMap over the input view
     alignas(64) unsigned char tmap_b[128];   // CUtensorMap over the packed weights
+    alignas(64) unsigned char tmap_c[128];   // CUtensorMap over the output window (when tma_store)
 };
 struct ConvTcParams {
     TensorRef in, out;
@@ -102,12 +107,16 @@ struct ConvTcParams {
     float *workspace;
     unsigned int *counters;
     int *error_flag;               // device word set to non-zero when a bounded wait ran out
+    long long *timeline;           // optional diagnostics: 16 SM-clock stamps written by CTA (0,0,0), or null
     ConvGeom g;
 };
 // Returns false when the shape / view cannot use the tensor-core kernel.
 bool conv_tc_supported(const TensorRef &in, const ConvGeom &g);
-// Chooses the tiling; sm_count and target_ctas steer bn / split_k.  Does not touch the device.
-void conv_tc_choose(const ConvGeom &g, int sm_count, int concurrency_hint, ConvTcPlan *plan);
+// Chooses the tiling; sm_count and concurrency_hint (groups running beside this one) steer bn and
+// split_k.  three_pass selects the fp32-grade 3xTF32 product.  Does not touch the device.
+void conv_tc_choose(const ConvGeom &g, int sm_count, int concurrency_hint, bool three_pass, ConvTcPlan *plan);
+// Overrides the K split (recomputes pipeline depth, shared memory and workspace sizes).
+void conv_tc_set_split(ConvTcPlan *plan, int split);
 // Encodes the two tensor maps (needs final device addresses).  Returns a CUDA driver error text or nullptr.
 const char *conv_tc_encode(const ConvTcParams &p, ConvTcPlan *plan);
 // Raises the kernel's dynamic shared-memory limit; call once per device before the first launch.

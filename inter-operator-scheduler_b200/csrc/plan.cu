@@ -137,7 +137,7 @@ private:
     // that takes it unchanged, and it is not the tensor handed back to the caller.
     // Identity operators hand their single-value terms on unchanged, so the test looks through them.
     bool rounds_for_consumers(int idx) const {
-        if (!plan_.options.tf32 || idx == m_.output || users_[idx].empty()) return false;
+        if (!plan_.options.tf32 || plan_.options.three_pass || idx == m_.output || users_[idx].empty()) return false;
         for (const UserRef &u : users_[idx]) {
             const Op &c = m_.ops[u.op];
             if (!u.sole_value || !c.scheduled) return false;
@@ -383,8 +383,9 @@ private:
             slot.weight_floats = size_t(op.kh) * op.kw * op.C;
         } else if (tc_wanted && conv_tc_supported(in, g)) {
             slot.impl = StepKind::ConvTc;
-            conv_tc_choose(g, sms_, width_, &slot.tcplan);
-            if (plan_.options.force_split_k > 0) force_split(g, &slot.tcplan, plan_.options.force_split_k);
+            conv_tc_choose(g, sms_, width_, plan_.options.three_pass, &slot.tcplan);
+            if (plan_.options.force_split_k > 0) conv_tc_set_split(&slot.tcplan, plan_.options.force_split_k);
+            slot.tcplan.pdl = plan_.options.pdl ? 1 : 0;
             slot.weight_floats = conv_tc_packed_floats(g, slot.tcplan);
         } else {
             slot.impl = StepKind::ConvDirect;
@@ -403,6 +404,7 @@ private:
             s.tc.error_flag = reinterpret_cast<int *>(at(plan_.error_flag_offset));
             s.tc.workspace = nullptr;
             s.tc.counters = nullptr;
+            s.tc.timeline = plan_.options.timeline ? reinterpret_cast<long long *>(at(plan_.error_flag_offset) + 16) : nullptr;
             if (slot.tcplan.split_k > 1) {
                 s.tc.workspace = at(alloc(slot.tcplan.workspace_bytes));
                 plan_.workspace_bytes += slot.tcplan.workspace_bytes;
@@ -426,14 +428,6 @@ private:
             s.direct.g = g;
         }
         plan_.convs.push_back(slot);
-    }
-
-    static void force_split(const ConvGeom &, ConvTcPlan *q, int want) {
-        const int base = q->tiles_w * q->tiles_h * q->tiles_n * q->n_tiles;
-        int split = std::max(1, std::min(want, q->k_iters));
-        q->split_k = split;
-        q->workspace_bytes = split > 1 ? size_t(base) * split * q->bn * 128 * sizeof(float) : 0;
-        q->counter_bytes = split > 1 ? size_t(base) * sizeof(unsigned int) : 0;
     }
 };
 

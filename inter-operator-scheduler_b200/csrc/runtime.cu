@@ -118,6 +118,8 @@ struct DeviceContext {
                 CUDA_OK(cudaMalloc(&arena, want));
             }
             arena_capacity = want;
+            // padding lanes of the NHWC buffers are never written: keep them finite
+            CUDA_OK(cudaMemset(arena, 0, want));
         }
         return arena;
     }
@@ -224,6 +226,16 @@ struct HostWeights {
 };
 
 void check_error_flag(const Plan &plan, char *base) {
+    if (plan.options.timeline) {
+        long long stamps[13];
+        CUDA_OK(cudaMemcpy(stamps, base + plan.error_flag_offset + 64, sizeof stamps, cudaMemcpyDeviceToHost));
+        std::fprintf(stderr, "conv_tc timeline (SM cycles since entry): setup %lld, first load issued %lld, first tile landed %lld, "
+                     "last mma issued %lld, accumulator ready %lld, bias ready %lld, partial published %lld, tile staged %lld, "
+                     "staging fenced %lld, stores issued %lld, epilogue done %lld, tmem freed %lld\n",
+                     stamps[1] - stamps[0], stamps[2] - stamps[0], stamps[3] - stamps[0], stamps[4] - stamps[0],
+                     stamps[5] - stamps[0], stamps[9] - stamps[0], stamps[6] - stamps[0], stamps[10] - stamps[0],
+                     stamps[11] - stamps[0], stamps[12] - stamps[0], stamps[7] - stamps[0], stamps[8] - stamps[0]);
+    }
     int flag = 0;
     CUDA_OK(cudaMemcpy(&flag, base + plan.error_flag_offset, sizeof flag, cudaMemcpyDeviceToHost));
     if (flag != 0) {
@@ -551,10 +563,14 @@ int ios_set_option(const char *key, const char *value) {
         if (!key || !value) throw ArgumentError("key and value must not be NULL");
         std::lock_guard<std::mutex> lock(g_mutex);
         const std::string k = key, v = value;
-        if (k == "precision" && (v == "tf32" || v == "fp32")) g_options.tf32 = v == "tf32";
+        if (k == "precision" && (v == "tf32x3" || v == "tf32" || v == "fp32")) {
+            g_options.tf32 = v != "fp32";
+            g_options.three_pass = v == "tf32x3";
+        } else if (k == "pdl" && (v == "0" || v == "1")) g_options.pdl = v == "1";
         else if (k == "executor" && (v == "graph" || v == "streams")) g_options.use_graph = v == "graph";
         else if (k == "conv" && (v == "auto" || v == "direct")) g_options.allow_tc = v == "auto";
         else if (k == "split_k") g_options.force_split_k = std::atoi(value);
+        else if (k == "timeline") g_options.timeline = v == "1";
         else throw ArgumentError("unknown option " + k + "=" + v);
     });
 }
@@ -564,7 +580,8 @@ int ios_get_option(const char *key, char *value, int capacity) {
         if (!key || !value || capacity <= 0) throw ArgumentError("key and value must not be NULL");
         const std::string k = key;
         std::string v;
-        if (k == "precision") v = g_options.tf32 ? "tf32" : "fp32";
+        if (k == "precision") v = !g_options.tf32 ? "fp32" : g_options.three_pass ? "tf32x3" : "tf32";
+        else if (k == "pdl") v = g_options.pdl ? "1" : "0";
         else if (k == "executor") v = g_options.use_graph ? "graph" : "streams";
         else if (k == "conv") v = g_options.allow_tc ? "auto" : "direct";
         else if (k == "split_k") v = std::to_string(g_options.force_split_k);
@@ -607,6 +624,7 @@ int ios_engine_create(const char *graph_json, int batch_size, int num_convs, cha
         plan_layout(&e.plan, ctx.sm_count);
         e.bytes = e.plan.arena_bytes;
         CUDA_OK(cudaMalloc(&e.base, e.bytes));
+        CUDA_OK(cudaMemset(e.base, 0, e.bytes));
         bind_plan(ctx, &e.plan, e.base);
         cudaStream_t spine = ctx.streams[0];
         if (filter_data && bias_data && conv_names) {
@@ -726,6 +744,64 @@ int ios_engine_time(ios_engine *engine, int iters, float *ms_per_iter) {
     });
 }
 
+int ios_engine_profile(ios_engine *engine, int iters, int capacity, int *count, float *step_ms, int *step_kind,
+                       double *step_work) {
+    return guarded([&]() {
+        if (!engine || !count || !step_ms || !step_kind || !step_work || iters <= 0)
+            throw ArgumentError("engine and the output arrays must not be NULL and iters > 0");
+        EngineImpl &e = engine->impl;
+        std::lock_guard<std::mutex> lock(g_mutex);
+        g_device = e.device;
+        DeviceContext &ctx = context();
+        cudaStream_t spine = ctx.streams[0];
+        const int n = int(e.plan.steps.size());
+        *count = n;
+        if (capacity < n) throw ArgumentError("capacity is smaller than the number of launches");
+        std::vector<cudaEvent_t> marks(size_t(n) + 1);
+        for (auto &m : marks) CUDA_OK(cudaEventCreate(&m));
+        for (int i = 0; i < n; ++i) step_ms[i] = 0.f;
+        for (int it = 0; it < iters + 1; ++it) {           // the first pass is a warm-up
+            CUDA_OK(cudaStreamSynchronize(spine));
+            CUDA_OK(cudaEventRecord(marks[0], spine));
+            for (int i = 0; i < n; ++i) {
+                launch_step(e.plan.steps[i], spine);
+                CUDA_OK(cudaEventRecord(marks[i + 1], spine));
+            }
+            CUDA_OK(cudaStreamSynchronize(spine));
+            if (it == 0) continue;
+            for (int i = 0; i < n; ++i) {
+                float ms = 0.f;
+                CUDA_OK(cudaEventElapsedTime(&ms, marks[i], marks[i + 1]));
+                step_ms[i] += ms / float(iters);
+            }
+        }
+        for (auto &m : marks) cudaEventDestroy(m);
+        for (int i = 0; i < n; ++i) {
+            const Step &s = e.plan.steps[i];
+            step_kind[i] = int(s.kind);
+            switch (s.kind) {
+                case StepKind::SumAct:
+                    step_work[i] = double(s.sum.k + 1) * double(s.sum.pixels) * s.sum.C * 4.0;
+                    break;
+                case StepKind::Pool:
+                    step_work[i] = (double(s.pool.in.pixels()) + double(s.pool.out.pixels())) * s.pool.in.C * 4.0;
+                    break;
+                case StepKind::ConvDepthwise: {
+                    const ConvGeom &g = s.direct.g;
+                    step_work[i] = (double(g.N) * g.H * g.W * g.Cin + double(g.N) * g.OH * g.OW * g.Cout +
+                                    double(g.kh) * g.kw * g.Cout) * 4.0;
+                    break;
+                }
+                default: {
+                    const ConvGeom &g = s.kind == StepKind::ConvTc ? s.tc.g : s.direct.g;
+                    step_work[i] = 2.0 * g.N * g.OH * g.OW * double(g.Cout) * g.kh * g.kw * (g.Cin / g.groups);
+                }
+            }
+        }
+        check_error_flag(e.plan, e.base);
+    });
+}
+
 int ios_engine_describe(ios_engine *engine, char *text, int capacity) {
     return guarded([&]() {
         if (!engine || !text || capacity <= 0) throw ArgumentError("engine and text must not be NULL");
@@ -751,7 +827,8 @@ int ios_engine_describe(ios_engine *engine, char *text, int capacity) {
                       "\"precision\": \"%s\"}",
                       p.launches_per_forward, n_tc, n_split, n_direct, n_dw, n_sum, n_pool, p.model.stages.size(), e.bytes,
                       p.workspace_bytes, weight_bytes, p.model.conv_flops(), p.model.batch, out.C, out.H, out.W,
-                      p.options.use_graph ? "graph" : "streams", p.options.tf32 ? "tf32" : "fp32");
+                      p.options.use_graph ? "graph" : "streams",
+                      !p.options.tf32 ? "fp32" : p.options.three_pass ? "tf32x3" : "tf32");
     });
 }
 
@@ -759,7 +836,7 @@ int ios_conv2d(const float *x, const float *w, const float *bias, float *y, int 
                int kh, int kw, int sh, int sw, int ph, int pw, int groups, int act, int impl) {
     return guarded([&]() {
         if (!x || !w || !y) throw ArgumentError("x, w and y must not be NULL");
-        if (n <= 0 || cin <= 0 || h <= 0 || wdt <= 0 || cout <= 0 || groups <= 0 || act < 0 || act > 3 || impl < 0 || impl > 2)
+        if (n <= 0 || cin <= 0 || h <= 0 || wdt <= 0 || cout <= 0 || groups <= 0 || act < 0 || act > 3 || impl < 0 || impl > 3)
             throw ArgumentError("bad convolution arguments");
         // a one-operator graph drives exactly the code path a scheduled convolution takes
         static const char *acts[] = {"identity", "relu", "sigmoid", "tanh"};
@@ -784,6 +861,7 @@ int ios_conv2d(const float *x, const float *w, const float *bias, float *y, int 
             saved = g_options;
             if (impl == 1) g_options.allow_tc = false;
             if (impl == 2) { g_options.allow_tc = true; g_options.tf32 = true; }
+            if (impl == 3) { g_options.allow_tc = true; g_options.tf32 = true; g_options.three_pass = false; }
         }
         try {
             run_inference(model, x, hw, y);

@@ -61,6 +61,8 @@ def load_ios_library():
         handle.ios_engine_run.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
         handle.ios_engine_time.argtypes = [ctypes.c_void_p, _INT, _FLOATP]
         handle.ios_engine_describe.argtypes = [ctypes.c_void_p, ctypes.c_char_p, _INT]
+        handle.ios_engine_profile.argtypes = [ctypes.c_void_p, _INT, _INT, ctypes.POINTER(_INT), _FLOATP,
+                                              ctypes.POINTER(_INT), ctypes.POINTER(ctypes.c_double)]
         handle.ios_engine_set_input.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
         handle.ios_engine_get_output.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
         handle.ios_set_option.argtypes = [_CHARP, _CHARP]
@@ -86,7 +88,7 @@ def _check(status):
 
 
 def set_option(key: str, value: str):
-    """Run-time switches: precision tf32|fp32, executor graph|streams, conv auto|direct."""
+    """Run-time switches: precision tf32x3|tf32|fp32, executor graph|streams, conv auto|direct, pdl 0|1."""
     _check(_library().ios_set_option(key.encode(), str(value).encode()))
 
 
@@ -185,7 +187,11 @@ def graph_inference(graph: Graph, batch_size, input: np.ndarray):
 
 def conv2d(x: np.ndarray, weight: np.ndarray, bias=None, stride=(1, 1), padding=(0, 0), groups=1, act='identity',
            impl='auto'):
-    """One convolution through the runtime (testing aid).  x: NCHW, weight: OIHW."""
+    """
+    One convolution through the runtime (testing aid).  x: NCHW, weight: OIHW.  impl: 'auto',
+    'direct' (CUDA cores), 'tensor' (tensor cores, current precision option), 'tensor1' (tensor
+    cores, single-pass TF32).
+    """
     x = np.ascontiguousarray(x, dtype=np.float32)
     weight = np.ascontiguousarray(weight, dtype=np.float32)
     n, cin, h, w = x.shape
@@ -198,7 +204,7 @@ def conv2d(x: np.ndarray, weight: np.ndarray, bias=None, stride=(1, 1), padding=
         x.ctypes.data_as(ctypes.c_void_p), weight.ctypes.data_as(ctypes.c_void_p),
         None if b is None else b.ctypes.data_as(ctypes.c_void_p), y.ctypes.data_as(ctypes.c_void_p),
         n, cin, h, w, cout, kh, kw, stride[0], stride[1], padding[0], padding[1], groups,
-        ['identity', 'relu', 'sigmoid', 'tanh'].index(act), ['auto', 'direct', 'tensor'].index(impl)))
+        ['identity', 'relu', 'sigmoid', 'tanh'].index(act), ['auto', 'direct', 'tensor', 'tensor1'].index(impl)))
     return y
 
 
@@ -260,6 +266,22 @@ class Engine:
         buf = ctypes.create_string_buffer(2048)
         _check(self._lib.ios_engine_describe(self._handle, buf, 2048))
         return json.loads(buf.value.decode())
+
+    STEP_KINDS = ('sum_act', 'pool', 'conv_tc', 'conv_direct', 'conv_depthwise')
+
+    def profile(self, iters=5):
+        """
+        Per-launch device time of one forward (launches serialised on one stream, CUDA events in
+        between).  Returns a list of ``(kind, ms, work)``; ``work`` is algorithmic FLOPs for the
+        convolutions on ``conv_tc`` / ``conv_direct`` and algorithmic bytes for the other kinds.
+        """
+        capacity = 4096
+        count = ctypes.c_int(0)
+        ms = (ctypes.c_float * capacity)()
+        kinds = (ctypes.c_int * capacity)()
+        work = (ctypes.c_double * capacity)()
+        _check(self._lib.ios_engine_profile(self._handle, int(iters), capacity, ctypes.byref(count), ms, kinds, work))
+        return [(self.STEP_KINDS[kinds[i]], float(ms[i]), float(work[i])) for i in range(count.value)]
 
     def close(self):
         if self._handle:

@@ -3,7 +3,10 @@ GPU parity: the CUDA path, called through the C-ABI (ctypes), against the CPU or
 the golden vectors produced by the reference implementation.
 
 Metric and tolerances (stated by the parity contract): max|y - ref| / max|ref| <= 1e-3 for the
-TF32 tensor-core path (fp32 accumulate), and 2e-5 for the CUDA-core fp32 path.
+TF32 tensor-core path (fp32 accumulate), and 2e-5 for the CUDA-core fp32 path.  The default
+precision, three-pass TF32, is held to the fp32 bound on single layers and to 1e-3 on networks; the
+single-pass mode meets 1e-3 per layer and on the shallower networks (a deep network accumulates
+about 3e-4 per layer, see test_single_pass_tf32_error_growth).
 """
 import json
 import os
@@ -22,7 +25,8 @@ pytestmark = pytest.mark.gpu
 
 @pytest.fixture(autouse=True)
 def default_options():
-    rt.set_option('precision', 'tf32')
+    rt.set_option('precision', 'tf32x3')
+    rt.set_option('pdl', '1')
     rt.set_option('executor', 'graph')
     rt.set_option('conv', 'auto')
     rt.set_option('split_k', '0')
@@ -62,7 +66,8 @@ TC_SHAPES = [
 
 @pytest.mark.parametrize('shape', TC_SHAPES)
 def test_conv_tensor_core_vs_oracle(shape):
-    assert _conv_case(shape, 'tensor') <= TOL_TF32
+    assert _conv_case(shape, 'tensor') <= TOL_FP32          # three-pass TF32: fp32-grade
+    assert _conv_case(shape, 'tensor1') <= TOL_TF32         # single-pass TF32
 
 
 @pytest.mark.parametrize('shape', TC_SHAPES[:6] + [
@@ -111,7 +116,7 @@ def test_all_operator_types_graph(golden):
     weights = oracle.uniform_weights(graph.export_config(), 3)
     set_weights(graph, weights)
     x = oracle.normal_input(config, 3, 4)
-    for precision, tol in (('fp32', TOL_FP32), ('tf32', TOL_TF32)):
+    for precision, tol in (('fp32', TOL_FP32), ('tf32x3', TOL_FP32), ('tf32', TOL_TF32)):
         rt.set_option('precision', precision)
         y = rt.graph_inference(graph, 3, x)
         golden.expect('all_ops_b3', y, tol)
@@ -133,6 +138,17 @@ def test_networks_match_reference_outputs(golden, case, model, law, wseed, xseed
     x = oracle.normal_input(config, batch, xseed)
     y = rt.graph_inference(graph, batch, x)
     golden.expect(case, y, TOL_TF32)
+
+
+def test_single_pass_tf32_error_growth(golden):
+    """Single-pass TF32 meets 1e-3 on the shallower networks; Inception-v3 (47 layers deep) does not, hence the default."""
+    rt.set_option('precision', 'tf32')
+    for model, bound in (('squeezenet', TOL_TF32), ('inception_v3', 6e-3)):
+        graph = getattr(ios.models, model)()
+        graph.sequential_schedule()
+        config, weights = seeded(graph, 0)
+        y = rt.graph_inference(graph, 1, oracle.normal_input(config, 1, 0))
+        golden.expect(model, y, bound)
 
 
 def test_inception_cuda_core_path_is_fp32_exact(golden):
@@ -174,7 +190,7 @@ def test_batched_inference_equals_per_image_inference():
     ref = oracle.run_config(config, weights, x)
     assert oracle.max_rel_err(y, ref) <= TOL_TF32
     y0 = rt.graph_inference(graph, 1, x[2:3])
-    assert oracle.max_rel_err(y0, y[2:3]) <= 1e-6      # same arithmetic per image, whatever the batch
+    assert oracle.max_rel_err(y0, y[2:3]) <= 1e-4      # same function per image; tiling and K split differ with the batch
 
 
 def test_results_are_deterministic_across_runs_and_executors():
@@ -187,7 +203,9 @@ def test_results_are_deterministic_across_runs_and_executors():
     b = rt.graph_inference(opt, 1, x)
     rt.set_option('executor', 'streams')
     c = rt.graph_inference(opt, 1, x)
-    assert np.array_equal(a, b) and np.array_equal(a, c)
+    rt.set_option('pdl', '0')
+    d = rt.graph_inference(opt, 1, x)
+    assert np.array_equal(a, b) and np.array_equal(a, c) and np.array_equal(a, d)
 
 
 def test_latency_entry_points():
