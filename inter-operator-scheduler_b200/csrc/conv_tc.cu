@@ -153,13 +153,14 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
     d |= uint64_t(2) << 61;                  // SWIZZLE_128B
     return d;
 }
+// sigmoid / tanh are rare; keeping them out of line keeps the unrolled epilogue small
+__device__ __noinline__ float act_slow(float v, int act) {
+    return act == 2 ? 1.0f / (1.0f + __expf(-v)) : tanhf(v);
+}
 __device__ __forceinline__ float act_apply(float v, int act) {
-    switch (act) {
-        case 1: return fmaxf(v, 0.0f);
-        case 2: return 1.0f / (1.0f + __expf(-v));
-        case 3: return tanhf(v);
-        default: return v;
-    }
+    if (act == 1) return fmaxf(v, 0.0f);
+    if (act == 0) return v;
+    return act_slow(v, act);
 }
 __device__ __forceinline__ float round_tf32(float v) {
     uint32_t r;
@@ -252,6 +253,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             asm volatile("griddepcontrol.wait;" ::: "memory");
             bool ok = true;
             int issued = 0;
+#pragma unroll 1
             for (int i = 0; i < n_it && ok; ++i) {
                 const int s = i % t.stages;
                 if (i >= t.stages) ok = mbar_wait(empty0 + 8u * s, uint32_t((i / t.stages - 1) & 1), p.error_flag);
@@ -282,6 +284,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(t.bn >> 3) << 17) | (uint32_t(kTileM >> 4) << 24);
             const uint32_t wait0 = t.x3 ? ready0 : full0;
             bool ok = true;
+#pragma unroll 1
             for (int i = 0; i < n_it; ++i) {
                 const int s = i % t.stages;
                 ok = mbar_wait(wait0 + 8u * s, uint32_t((i / t.stages) & 1), p.error_flag);
@@ -321,6 +324,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (t.x3) {
             // Split every fp32 activation that landed into a TF32-exact value (in place) and its residual.
             const int n_vec = t.a_bytes >> 4;
+#pragma unroll 1
             for (int i = 0; i < n_it && ok; ++i) {
                 const int s = i % t.stages;
                 ok = mbar_wait(full0 + 8u * s, uint32_t((i / t.stages) & 1), p.error_flag);
@@ -328,6 +332,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 uint8_t *stage = generic_base + size_t(s) * stage_bytes;
                 float4 *hi = reinterpret_cast<float4 *>(stage);
                 float4 *lo = reinterpret_cast<float4 *>(stage + a_lo_off);
+#pragma unroll 2
                 for (int v = tid; v < n_vec; v += 128) {
                     float4 x = hi[v];
                     float4 h, l;
@@ -355,6 +360,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (ok && t.split_k > 1) {
             // publish this CTA's partial tile: ws[tile][split][col][row], rows contiguous
             float *ws = p.workspace + (size_t(tile_id) * t.split_k + split) * size_t(t.bn) * kTileM;
+#pragma unroll 1
             for (int c = 0; c < t.bn; c += 16) {
                 float v[16];
                 tmem_ld16(taddr + c, v);
@@ -390,14 +396,19 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             float *dst = p.out.ptr + (pix_off < 0 ? 0 : pix_off) + cout0;
             const bool vec_ok = ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
             const float *ws_tile = p.workspace + size_t(tile_id) * t.split_k * size_t(t.bn) * kTileM;
+            // (loops that run a handful of times are kept rolled: the code of a CTA runs once, so its
+            // cost is dominated by instruction fetch, not by loop overhead)
+#pragma unroll 1
             for (int c = 0; c < t.bn; c += 16) {
                 float v[16];
                 if (t.split_k == 1) {
                     tmem_ld16(taddr + c, v);
+                    if (c == 0 && threadIdx.x == 64) STAMP(13);
                 } else {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) v[j] = 0.0f;
                     // four partial tiles per round trip, added in split order
+#pragma unroll 1
                     for (int s0 = 0; s0 < t.split_k; s0 += 4) {
                         float part[4][16];
 #pragma unroll
@@ -419,6 +430,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     float o = act_apply(v[j] + bias_s[c + j], g.act);
                     v[j] = t.round_tf32 ? round_tf32(o) : o;
                 }
+                if (c == 0 && threadIdx.x == 64) STAMP(14);
                 if (t.tma_store) {
                     // stage the tile as [32-channel slab][row][128 B], swizzled like a TMA box, for the bulk store
                     uint8_t *slab = generic_base + size_t(c >> 5) * kATileBytes;
@@ -426,6 +438,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
                     for (int j = 0; j < 16; j += 4)
                         *reinterpret_cast<float4 *>(slab + sw128_offset(row, c4 + (j >> 2))) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    if (c == 0 && threadIdx.x == 64) STAMP(15);
                     continue;
                 }
                 if (pix_off < 0 || c >= valid) continue;

@@ -17,6 +17,7 @@
 #include <cmath>
 #include <cstdio>
 #include <cstring>
+#include <map>
 #include <memory>
 #include <mutex>
 #include <stdexcept>
@@ -68,7 +69,6 @@ struct DeviceContext {
 
     void init(int dev) {
         if (device == dev) return;
-        release();
         int count = 0;
         cudaError_t err = cudaGetDeviceCount(&count);
         if (err != cudaSuccess || count == 0)
@@ -140,12 +140,13 @@ struct DeviceContext {
     }
 };
 
-DeviceContext g_ctx;
+std::map<int, DeviceContext> g_contexts;   // one per device this process has used
 
 DeviceContext &context() {
-    g_ctx.init(g_device);
+    DeviceContext &ctx = g_contexts[g_device];
+    ctx.init(g_device);
     CUDA_OK(cudaSetDevice(g_device));
-    return g_ctx;
+    return ctx;
 }
 
 // ---- issuing a plan -------------------------------------------------------------------------
@@ -227,14 +228,16 @@ struct HostWeights {
 
 void check_error_flag(const Plan &plan, char *base) {
     if (plan.options.timeline) {
-        long long stamps[13];
+        long long stamps[16];
         CUDA_OK(cudaMemcpy(stamps, base + plan.error_flag_offset + 64, sizeof stamps, cudaMemcpyDeviceToHost));
         std::fprintf(stderr, "conv_tc timeline (SM cycles since entry): setup %lld, first load issued %lld, first tile landed %lld, "
                      "last mma issued %lld, accumulator ready %lld, bias ready %lld, partial published %lld, tile staged %lld, "
-                     "staging fenced %lld, stores issued %lld, epilogue done %lld, tmem freed %lld\n",
+                     "staging fenced %lld, stores issued %lld, epilogue done %lld, tmem freed %lld; first chunk: loaded %lld, "
+                     "finished %lld, staged %lld\n",
                      stamps[1] - stamps[0], stamps[2] - stamps[0], stamps[3] - stamps[0], stamps[4] - stamps[0],
                      stamps[5] - stamps[0], stamps[9] - stamps[0], stamps[6] - stamps[0], stamps[10] - stamps[0],
-                     stamps[11] - stamps[0], stamps[12] - stamps[0], stamps[7] - stamps[0], stamps[8] - stamps[0]);
+                     stamps[11] - stamps[0], stamps[12] - stamps[0], stamps[7] - stamps[0], stamps[8] - stamps[0],
+                     stamps[13] - stamps[0], stamps[14] - stamps[0], stamps[15] - stamps[0]);
     }
     int flag = 0;
     CUDA_OK(cudaMemcpy(&flag, base + plan.error_flag_offset, sizeof flag, cudaMemcpyDeviceToHost));
@@ -760,12 +763,34 @@ int ios_engine_profile(ios_engine *engine, int iters, int capacity, int *count, 
         std::vector<cudaEvent_t> marks(size_t(n) + 1);
         for (auto &m : marks) CUDA_OK(cudaEventCreate(&m));
         for (int i = 0; i < n; ++i) step_ms[i] = 0.f;
+        // The serialised launch list is captured into one graph with an event-record node after every
+        // kernel, so the intervals hold device time only (kernel + dependency latency), no host launch cost.
+        GraphExec serial;
+        bool captured = false;
+        if (e.plan.options.use_graph) {
+            try {
+                capture(ctx, &serial, [&]() {
+                    CUDA_OK(cudaEventRecordWithFlags(marks[0], spine, cudaEventRecordExternal));
+                    for (int i = 0; i < n; ++i) {
+                        launch_step(e.plan.steps[i], spine);
+                        CUDA_OK(cudaEventRecordWithFlags(marks[i + 1], spine, cudaEventRecordExternal));
+                    }
+                });
+                captured = true;
+            } catch (const std::exception &) {
+                cudaGetLastError();
+            }
+        }
         for (int it = 0; it < iters + 1; ++it) {           // the first pass is a warm-up
             CUDA_OK(cudaStreamSynchronize(spine));
-            CUDA_OK(cudaEventRecord(marks[0], spine));
-            for (int i = 0; i < n; ++i) {
-                launch_step(e.plan.steps[i], spine);
-                CUDA_OK(cudaEventRecord(marks[i + 1], spine));
+            if (captured) {
+                CUDA_OK(cudaGraphLaunch(serial.exec, spine));
+            } else {
+                CUDA_OK(cudaEventRecord(marks[0], spine));
+                for (int i = 0; i < n; ++i) {
+                    launch_step(e.plan.steps[i], spine);
+                    CUDA_OK(cudaEventRecord(marks[i + 1], spine));
+                }
             }
             CUDA_OK(cudaStreamSynchronize(spine));
             if (it == 0) continue;
