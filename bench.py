@@ -295,10 +295,15 @@ def run_ours(args):
                               'GB/s': round(v['work'] / (v['ms'] * 1e-3) / 1e9, 1) if v['ms'] > 0 else None}
                           for k, v in by_kind.items() if k != 'conv_tc'},
     }
-    ncu_traffic = os.path.join(ROOT, 'profiles', 'conv_tc_traffic.json')
-    if os.path.exists(ncu_traffic):
-        with open(ncu_traffic) as fh:
-            roofline['traffic'] = json.load(fh).get('dram_bytes_per_step')
+    # DRAM bytes of the convolution launches of one forward, from the committed ncu summary
+    summary = os.path.join(ROOT, 'profiles', 'conv_tc_inception_v3_b1_sequential.md')
+    if args.model == 'inception_v3' and args.batch == 1 and os.path.exists(summary):
+        with open(summary) as fh:
+            for text in fh:
+                if text.startswith('dram_bytes_per_step:'):
+                    roofline['traffic'] = int(text.split(':')[1])
+                    roofline['traffic_source'] = 'ncu dram__bytes_read+write over the conv launches of one forward, ' \
+                                                 'sequential schedule (profiles/conv_tc_inception_v3_b1_sequential.md)'
 
     line = {
         'metric': METRIC, 'value': round(value, 2), 'unit': 'images/s', 'n_gpus': ranks.world, 'steps': args.steps,

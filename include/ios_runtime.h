@@ -100,9 +100,9 @@ IOS_API int ios_engine_time(ios_engine *engine, int iters, float *ms_per_iter);
 /* Describe the plan: writes a JSON text (kernel launches per forward, arena bytes, workspace bytes,
  * algorithmic FLOPs, output shape) into text[capacity]. */
 IOS_API int ios_engine_describe(ios_engine *engine, char *text, int capacity);
-/* Per-launch device times of one forward: the launches run one after another on a single stream
- * (captured into one CUDA graph with an event-record node after every kernel, so the intervals hold
- * device time only), averaged over `iters` passes.  step_kind: 0 sum/copy, 1 pool,
+/* Device time of the launches of one forward by kind: all launches of a kind run one after another
+ * on a single stream (captured into one CUDA graph of their own), and every launch is credited with
+ * its kind's mean, averaged over `iters` passes.  step_kind: 0 sum/copy, 1 pool,
  * 2 tensor-core conv, 3 CUDA-core conv, 4 depthwise conv.  step_work: algorithmic FLOPs (2*MAC) for
  * kinds 2 and 3, algorithmic bytes (inputs read once + output written once) for kinds 0, 1, 4.
  * Replaces the CUPTI sampling thread of the reference (src/ios/profile.cu:49-143). */

@@ -760,47 +760,33 @@ int ios_engine_profile(ios_engine *engine, int iters, int capacity, int *count, 
         const int n = int(e.plan.steps.size());
         *count = n;
         if (capacity < n) throw ArgumentError("capacity is smaller than the number of launches");
-        std::vector<cudaEvent_t> marks(size_t(n) + 1);
-        for (auto &m : marks) CUDA_OK(cudaEventCreate(&m));
+        // All launches of one kind are captured, one after another on a single stream, into a graph
+        // of their own; the graph's device time divided by its launch count is what every launch
+        // of that kind is credited with.  (No host launch cost, no timing nodes between kernels.)
         for (int i = 0; i < n; ++i) step_ms[i] = 0.f;
-        // The serialised launch list is captured into one graph with an event-record node after every
-        // kernel, so the intervals hold device time only (kernel + dependency latency), no host launch cost.
-        GraphExec serial;
-        bool captured = false;
-        if (e.plan.options.use_graph) {
-            try {
-                capture(ctx, &serial, [&]() {
-                    CUDA_OK(cudaEventRecordWithFlags(marks[0], spine, cudaEventRecordExternal));
-                    for (int i = 0; i < n; ++i) {
-                        launch_step(e.plan.steps[i], spine);
-                        CUDA_OK(cudaEventRecordWithFlags(marks[i + 1], spine, cudaEventRecordExternal));
-                    }
-                });
-                captured = true;
-            } catch (const std::exception &) {
-                cudaGetLastError();
-            }
-        }
-        for (int it = 0; it < iters + 1; ++it) {           // the first pass is a warm-up
-            CUDA_OK(cudaStreamSynchronize(spine));
-            if (captured) {
-                CUDA_OK(cudaGraphLaunch(serial.exec, spine));
-            } else {
-                CUDA_OK(cudaEventRecord(marks[0], spine));
-                for (int i = 0; i < n; ++i) {
-                    launch_step(e.plan.steps[i], spine);
-                    CUDA_OK(cudaEventRecord(marks[i + 1], spine));
-                }
-            }
-            CUDA_OK(cudaStreamSynchronize(spine));
-            if (it == 0) continue;
-            for (int i = 0; i < n; ++i) {
+        for (int kind = 0; kind < 5; ++kind) {
+            std::vector<int> members;
+            for (int i = 0; i < n; ++i)
+                if (int(e.plan.steps[i].kind) == kind) members.push_back(i);
+            if (members.empty()) continue;
+            auto issue = [&]() { for (int i : members) launch_step(e.plan.steps[i], spine); };
+            GraphExec serial;
+            const bool replay = e.plan.options.use_graph;
+            if (replay) capture(ctx, &serial, issue);
+            float total = 0.f;
+            for (int it = 0; it < iters + 1; ++it) {       // the first pass is a warm-up
+                CUDA_OK(cudaStreamSynchronize(spine));
+                CUDA_OK(cudaEventRecord(ctx.t_start, spine));
+                if (replay) CUDA_OK(cudaGraphLaunch(serial.exec, spine));
+                else issue();
+                CUDA_OK(cudaEventRecord(ctx.t_end, spine));
+                CUDA_OK(cudaStreamSynchronize(spine));
                 float ms = 0.f;
-                CUDA_OK(cudaEventElapsedTime(&ms, marks[i], marks[i + 1]));
-                step_ms[i] += ms / float(iters);
+                CUDA_OK(cudaEventElapsedTime(&ms, ctx.t_start, ctx.t_end));
+                if (it > 0) total += ms;
             }
+            for (int i : members) step_ms[i] = total / float(iters) / float(members.size());
         }
-        for (auto &m : marks) cudaEventDestroy(m);
         for (int i = 0; i < n; ++i) {
             const Step &s = e.plan.steps[i];
             step_kind[i] = int(s.kind);

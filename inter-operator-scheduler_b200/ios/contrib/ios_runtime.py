@@ -271,8 +271,9 @@ class Engine:
 
     def profile(self, iters=5):
         """
-        Per-launch device time of one forward (launches serialised on one stream, CUDA events in
-        between).  Returns a list of ``(kind, ms, work)``; ``work`` is algorithmic FLOPs for the
+        Device time of the launches of one forward: the launches of each kind are replayed one after
+        another as a graph of their own and every launch is credited with its kind's mean.
+        Returns a list of ``(kind, ms, work)``; ``work`` is algorithmic FLOPs for the
         convolutions on ``conv_tc`` / ``conv_direct`` and algorithmic bytes for the other kinds.
         """
         capacity = 4096
