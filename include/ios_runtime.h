@@ -122,6 +122,26 @@ IOS_API int ios_conv2d(const float *x, const float *w, const float *bias, float 
                        int wdt, int cout, int kh, int kw, int sh, int sw, int ph, int pw, int groups,
                        int act, int impl);
 
+/* ---- allocation-free entry point (it has no counterpart in the reference) --------------------
+ * y[pixels][cout] = act(x[pixels][cin] * w[cout][cin]^T + bias): a 1x1 convolution over NHWC data
+ * (pixels = N*H*W), single-pass TF32 products with fp32 accumulation, for callers that are not
+ * allowed to allocate device memory when they need it (a plug-in confined to its host's memory
+ * pool, a latency-critical loop that must stay off the allocator, a process whose device memory
+ * is fully budgeted).  All four pointers are DEVICE pointers the caller owns; w is the plain OIHW
+ * array of a 1x1 convolution, bias may be NULL.  The kernel's split-K scratch (partial tiles,
+ * arrival counters, time-out word) is a fixed 8 MiB + 20 KiB array inside the library image, held
+ * by every GPU that loads the library until the process exits; the call performs no cudaMalloc /
+ * cudaFree.  Requirements: cin % 4 == 0, x and w 16-byte aligned.  split_k: 0 = automatic,
+ * otherwise the number of CTAs sharing one output tile.  A problem whose scratch need exceeds the
+ * array returns IOS_ERR_LIMIT and launches nothing.  The work is enqueued on cuda_stream (a
+ * cudaStream_t, NULL = default stream) and NOT synchronised.  Every call shares the one array,
+ * which keeps the previous call's contents (the words that must be zero are cleared in stream
+ * order at the start of each call): calls that overlap on the GPU race.  The first call on a
+ * device resolves the array's device address; make it before any stream capture begins. */
+IOS_API int ios_pointwise_conv_static_scratch(const float *x, const float *w, const float *bias, float *y,
+                                              int pixels, int cin, int cout, int act, int split_k,
+                                              void *cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -677,6 +677,23 @@ const char *conv_tc_encode(const ConvTcParams &p, ConvTcPlan *plan) {
     return nullptr;
 }
 
+const char *conv_tc_encode_dense_weights(const ConvTcParams &p, ConvTcPlan *plan) {
+    // same as conv_tc_encode, but the weight matrix is the caller's dense [Cout][Cin] array (a 1x1
+    // convolution's OIHW weights): rows and columns beyond it are filled with zeros by the TMA unit
+    const char *err = conv_tc_encode(p, plan);
+    if (err) return err;
+    EncodeTiledFn encode = encode_fn();
+    const ConvGeom &g = p.g;
+    cuuint64_t dims[2] = {cuuint64_t(g.Cin), cuuint64_t(g.Cout)};
+    cuuint64_t strides[1] = {cuuint64_t(g.Cin) * 4};
+    cuuint32_t box[2] = {kChunk, cuuint32_t(plan->bn)};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode(reinterpret_cast<CUtensorMap *>(plan->tmap_b), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+                        const_cast<float *>(p.weight_packed), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? nullptr : "cuTensorMapEncodeTiled(dense weights) failed";
+}
+
 cudaError_t conv_tc_prepare() {
     return cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024);
 }

@@ -119,6 +119,9 @@ void conv_tc_choose(const ConvGeom &g, int sm_count, int concurrency_hint, bool 
 void conv_tc_set_split(ConvTcPlan *plan, int split);
 // Encodes the two tensor maps (needs final device addresses).  Returns a CUDA driver error text or nullptr.
 const char *conv_tc_encode(const ConvTcParams &p, ConvTcPlan *plan);
+// Variant of conv_tc_encode for a 1x1 convolution whose weights stay in the caller's dense
+// [Cout][Cin] float32 array (single-pass TF32 only: nothing is packed or split).
+const char *conv_tc_encode_dense_weights(const ConvTcParams &p, ConvTcPlan *plan);
 // Raises the kernel's dynamic shared-memory limit; call once per device before the first launch.
 cudaError_t conv_tc_prepare();
 void launch_conv_tc(const ConvTcParams &p, const ConvTcPlan &plan, cudaStream_t stream);

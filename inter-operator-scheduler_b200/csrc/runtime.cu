@@ -468,6 +468,9 @@ int guarded(F &&body) {
 
 }  // namespace
 
+// Lets other translation units of the library report through ios_last_error().
+void record_error(const char *message) { g_last_error = message ? message : ""; }
+
 // ---- engine ----------------------------------------------------------------------------------
 struct EngineImpl {
     Plan plan;
