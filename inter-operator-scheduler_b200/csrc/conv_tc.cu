@@ -11,10 +11,13 @@
 //   channels beyond Cin are out of range too, so K needs no padded activation copy.
 // * N = bn output channels (16..256), K advances 32 floats (one 128-byte swizzle row) per step,
 //   four tcgen05.mma.kind::tf32 (K = 8) per step.
-// * split_k CTAs share an output tile when the layer is too small to fill 148 SMs (batch 1):
-//   each writes its fp32 partial tile to a workspace, the last to arrive (one atomic ticket per
-//   tile) adds the partials in split order -- so results do not depend on arrival order -- and
-//   runs the epilogue.
+// * split_k CTAs share an output tile when the layer is too small to fill 148 SMs (batch 1).
+//   Up to 8 of them form a thread-block cluster: each parks its fp32 partial tile in its own
+//   shared memory, and after a cluster barrier CTA r adds rows [r*128/S, (r+1)*128/S) of all S
+//   tiles through distributed shared memory, in split order, and stores them.  Larger splits (and
+//   the allocation-free entry point) go through a global workspace instead: the last CTA to arrive
+//   (one atomic ticket per tile) adds the partials in split order.  Either way the result does not
+//   depend on timing.
 // * Epilogue: tcgen05.ld (one thread per pixel row), + bias, activation, optional rounding to TF32
 //   for a consumer convolution, store into a channel window of the destination (NHWC, pitch), which
 //   is how concat-by-placement and merged convolutions are written without a copy.
@@ -32,6 +35,7 @@
 #include <cstring>
 #include <cmath>
 #include <algorithm>
+#include <vector>
 
 namespace ios {
 namespace {
@@ -52,6 +56,7 @@ struct TileGeom {
     int x3;           // 1: three-pass TF32 (value + residual of both operands), fp32-grade products
     int cout_pad;     // rows of one plane of the packed weight matrix
     int tma_store;    // 1: the epilogue stages the tile in shared memory and stores it with bulk tensor stores
+    int cluster;      // 1: the split_k CTAs of a tile form a thread-block cluster and reduce through shared memory
 };
 
 // ---- PTX wrappers ----------------------------------------------------------------------------
@@ -109,6 +114,26 @@ __device__ __forceinline__ void tma_store_4d(const void *tmap, uint32_t src, int
     asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
                  ::"l"(tmap), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
                  : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Address of the same shared-memory location in CTA `rank` of this cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    return remote;
+}
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
@@ -357,7 +382,22 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16);
         const int tile_id = m_tile * gridDim.y + n_tile;
         bool finisher = true;
-        if (ok && t.split_k > 1) {
+        if (t.split_k > 1 && t.cluster) {
+            // cluster reduction: park this CTA's partial tile in its own shared memory, [row][bn + 4] floats
+            finisher = false;
+            if (ok) {
+                float *part = reinterpret_cast<float *>(generic_base) + size_t(row) * (t.bn + 4);
+#pragma unroll 1
+                for (int c = 0; c < t.bn; c += 16) {
+                    float v[16];
+                    tmem_ld16(taddr + c, v);
+#pragma unroll
+                    for (int j = 0; j < 16; j += 4)
+                        *reinterpret_cast<float4 *>(part + c + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                }
+            }
+            if (threadIdx.x == 64) STAMP(6);
+        } else if (ok && t.split_k > 1) {
             // publish this CTA's partial tile: ws[tile][split][col][row], rows contiguous
             float *ws = p.workspace + (size_t(tile_id) * t.split_k + split) * size_t(t.bn) * kTileM;
 #pragma unroll 1
@@ -474,6 +514,68 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (threadIdx.x == 64) STAMP(7);
         tc_fence_before();
     }
+    if (t.split_k > 1 && t.cluster) {
+        // Every thread of every CTA of the cluster passes both barriers, whatever happened before.
+        cluster_sync_all();                                   // all partial tiles are parked
+        if (warp >= 2) {
+            // CTA r of the cluster finishes rows [r*128/S, (r+1)*128/S) of the tile: it adds the S partial
+            // tiles in split order (so the result does not depend on timing), applies bias and activation
+            // and writes its rows; consecutive threads take consecutive 16-byte columns of a row.
+            const int tid = threadIdx.x - 64;
+            const uint32_t rank = cluster_cta_rank();
+            const int r0 = int(rank) * kTileM / t.split_k, r1 = int(rank + 1) * kTileM / t.split_k;
+            const int quads = t.bn >> 2;
+            const int valid = min(t.bn, g.Cout - cout0);
+            const int n_items = (r1 - r0) * quads;
+#pragma unroll 1
+            for (int item = tid; item < n_items; item += 128) {
+                const int row = r0 + item / quads;
+                const int c = (item - (row - r0) * quads) << 2;
+                long pix_off = -1;
+                if (t.flat) {
+                    const long pix = long(ow0) + row;
+                    if (row < t.box_w && pix < long(g.N) * g.OH * g.OW) pix_off = pix * p.out.pitch;
+                } else {
+                    const int ww = row % t.box_w;
+                    const int hh = (row / t.box_w) % t.box_h;
+                    const int im = row / (t.box_w * t.box_h);
+                    const int ow = ow0 + ww, oh = oh0 + hh, n = n0 + im;
+                    if (im < t.box_n && ow < g.OW && oh < g.OH && n < g.N)
+                        pix_off = ((long(n) * g.OH + oh) * g.OW + ow) * p.out.pitch;
+                }
+                if (pix_off < 0 || c >= valid) continue;
+                const uint32_t local = smem_base + uint32_t((row * (t.bn + 4) + c) * 4);
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+                for (int sp = 0; sp < t.split_k; sp += 4) {
+                    float4 part[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) part[u] = ld_cluster_f4(map_to_cta(local, uint32_t(min(sp + u, t.split_k - 1))));
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        if (sp + u < t.split_k) {
+                            acc.x += part[u].x; acc.y += part[u].y; acc.z += part[u].z; acc.w += part[u].w;
+                        }
+                }
+                float o[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float z = act_apply(o[j] + bias_s[c + j], g.act);
+                    o[j] = t.round_tf32 ? round_tf32(z) : z;
+                }
+                float *dst = p.out.ptr + pix_off + cout0 + c;
+                if (c + 4 <= valid && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                    *reinterpret_cast<float4 *>(dst) = make_float4(o[0], o[1], o[2], o[3]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (c + j < valid) dst[j] = o[j];
+                }
+            }
+            if (threadIdx.x == 64) STAMP(7);
+        }
+        cluster_sync_all();                                   // nobody leaves while its tile may still be read
+    }
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
@@ -522,54 +624,91 @@ bool conv_tc_supported(const TensorRef &in, const ConvGeom &g) {
     return true;
 }
 
-void conv_tc_choose(const ConvGeom &g, int sm_count, int concurrency_hint, bool three_pass, ConvTcPlan *plan) {
+// Tile selection.  At batch 1 a layer is a few dozen CTAs whose cost is fixed overhead plus a K loop
+// that runs at the per-SM rate at which TMA can fill shared memory, so the choice is made with a
+// small cost model (cycles, fitted to a sweep over the 43 distinct Inception-v3 layers on B200):
+//     cta  = fixed + k_steps_per_cta * stage_bytes / fill_rate + epilogue(bn) + cluster_overhead
+//     time = waves * cta,  waves = ceil(ctas / how many fit at once)
+// over every pixel-tile shape, output-channel tile width and K split that the kernel supports.
+// It replaces the reference's run-time algorithm search (src/ios/ios_runtime.cu:150-205).
+void conv_tc_choose(const ConvGeom &g, int sm_count, int concurrency_hint, bool three_pass, ConvTcPlan *plan, int force_bn) {
     ConvTcPlan &q = *plan;
     q.x3 = three_pass ? 1 : 0;
+    q.cluster = 1;
     const bool flat = g.kh == 1 && g.kw == 1 && g.sh == 1 && g.sw == 1 && g.ph == 0 && g.pw == 0;
     q.flat_1x1 = flat ? 1 : 0;
+    q.cchunks = ceil_div(g.Cin, kChunk);
+    q.k_iters = g.kh * g.kw * q.cchunks;
+
+    struct Shape { int box_w, box_h, box_n, tiles_w, tiles_h, tiles_n; };
+    std::vector<Shape> shapes;
     if (flat) {
         const long pixels = long(g.N) * g.OH * g.OW;
         const long tiles = (pixels + kTileM - 1) / kTileM;
-        q.box_w = int((pixels + tiles - 1) / tiles);
-        q.box_h = q.box_n = 1;
-        q.tiles_w = int((pixels + q.box_w - 1) / q.box_w);
-        q.tiles_h = q.tiles_n = 1;
-    } else if (g.OW <= std::min(kTileM, 256 / g.sw)) {
-        q.box_w = g.OW;
-        q.box_h = std::min(g.OH, std::max(1, kTileM / g.OW));
-        if (q.box_h * g.sh > 256) q.box_h = 256 / g.sh;
-        q.box_n = (q.box_h == g.OH) ? std::min(g.N, std::max(1, kTileM / (g.OH * g.OW))) : 1;
-        q.tiles_w = 1;
-        q.tiles_h = ceil_div(g.OH, q.box_h);
-        q.tiles_n = ceil_div(g.N, q.box_n);
+        Shape sh;
+        sh.box_w = int((pixels + tiles - 1) / tiles);
+        sh.box_h = sh.box_n = 1;
+        sh.tiles_w = int((pixels + sh.box_w - 1) / sh.box_w);
+        sh.tiles_h = sh.tiles_n = 1;
+        shapes.push_back(sh);
     } else {
         const int max_w = std::min(kTileM, 256 / g.sw);
-        const int parts = ceil_div(g.OW, max_w);
-        q.box_w = ceil_div(g.OW, parts);
-        q.box_h = q.box_n = 1;
-        q.tiles_w = ceil_div(g.OW, q.box_w);
-        q.tiles_h = g.OH;
-        q.tiles_n = g.N;
+        const int min_parts = ceil_div(g.OW, max_w);
+        for (int parts = min_parts; parts < min_parts + 4; ++parts) {
+            Shape sh;
+            sh.box_w = ceil_div(g.OW, parts);
+            if (sh.box_w < 8 && parts > min_parts) break;
+            sh.tiles_w = ceil_div(g.OW, sh.box_w);
+            sh.box_h = std::min({g.OH, std::max(1, kTileM / sh.box_w), std::max(1, 256 / g.sh)});
+            sh.tiles_h = ceil_div(g.OH, sh.box_h);
+            const bool whole_image = sh.tiles_w == 1 && sh.box_h == g.OH;
+            sh.box_n = whole_image ? std::min(g.N, std::max(1, kTileM / (g.OH * g.OW))) : 1;
+            sh.tiles_n = ceil_div(g.N, sh.box_n);
+            shapes.push_back(sh);
+        }
     }
-    const int m_tiles = q.tiles_w * q.tiles_h * q.tiles_n;
-    const int target = std::max(1, sm_count / std::max(1, concurrency_hint));
-    // output-channel tiling (multiples of 32: one 128-byte slab of the store staging per 32 channels):
-    // wide tiles when the pixel tiles alone fill the machine, else narrow ones for more CTAs
-    const int n_tiles = ceil_div(g.Cout, m_tiles * ceil_div(g.Cout, 128) >= target ? 128 : 64);
-    q.bn = std::min(256, ceil_div(ceil_div(g.Cout, n_tiles), 32) * 32);
+    const double kFixed = 3000.0, kFillBytesPerCycle = 20.0, kEpiloguePer16 = 400.0, kClusterOverhead = 500.0;
+    const int planes = three_pass ? 2 : 1;
+    const int share = std::max(1, concurrency_hint);
+    double best_cost = 1e30;
+    Shape best_shape = shapes[0];
+    int best_bn = 32, best_split = 1;
+    static const int splits[] = {1, 2, 3, 4, 6, 8};
+    for (const Shape &sh : shapes) {
+        const int m_tiles = sh.tiles_w * sh.tiles_h * sh.tiles_n;
+        const int rows = sh.box_w * sh.box_h * sh.box_n;
+        int last_bn = 0;
+        for (int n_tiles = 1; n_tiles <= ceil_div(g.Cout, 32); ++n_tiles) {
+            int bn = std::min(256, ceil_div(ceil_div(g.Cout, n_tiles), 32) * 32);
+            if (force_bn > 0) bn = std::min(256, ceil_div(force_bn, 32) * 32);
+            if (bn == last_bn) continue;
+            last_bn = bn;
+            const int nt = ceil_div(g.Cout, bn);
+            const double stage_bytes = rows * 128.0 + double(planes) * bn * 128.0;
+            for (int split : splits) {
+                if (split > 1 && split * 2 > q.k_iters) break;
+                const long ctas = long(m_tiles) * nt * split;
+                const int fit = std::max(1, (split == 1 ? sm_count : 8 * (16 / split) * split) / share);
+                const double waves = double((ctas + fit - 1) / fit);
+                const double cta = kFixed + ceil_div(q.k_iters, split) * stage_bytes / kFillBytesPerCycle +
+                                   (bn / 16) * kEpiloguePer16 + (split > 1 ? kClusterOverhead : 0.0);
+                const double cost = waves * cta;
+                if (cost < best_cost) {
+                    best_cost = cost;
+                    best_shape = sh;
+                    best_bn = bn;
+                    best_split = split;
+                }
+            }
+            if (force_bn > 0) break;
+        }
+    }
+    q.box_w = best_shape.box_w; q.box_h = best_shape.box_h; q.box_n = best_shape.box_n;
+    q.tiles_w = best_shape.tiles_w; q.tiles_h = best_shape.tiles_h; q.tiles_n = best_shape.tiles_n;
+    q.bn = best_bn;
     q.n_tiles = ceil_div(g.Cout, q.bn);
     q.cout_pad = q.n_tiles * q.bn;
-    q.cchunks = ceil_div(g.Cin, kChunk);
-    q.k_iters = g.kh * g.kw * q.cchunks;
-    // Split K only when the K loop is long: a split costs a trip through the workspace and one
-    // atomic ticket, which is worth about ten K steps.
-    const int base = m_tiles * q.n_tiles;
-    int split = 1;
-    if (base < target && q.k_iters >= 16) {
-        split = std::min(target / base, q.k_iters / 8);
-        split = std::max(1, std::min(split, 32));
-    }
-    conv_tc_set_split(&q, split);
+    conv_tc_set_split(&q, best_split);
 }
 
 void conv_tc_set_split(ConvTcPlan *plan, int split) {
@@ -580,11 +719,16 @@ void conv_tc_set_split(ConvTcPlan *plan, int split) {
     const int stage_bytes = (q.x3 ? 2 : 1) * (kATileBytes + q.bn * kChunk * 4);
     const int per_split = ceil_div(q.k_iters, split);
     q.stages = std::max(2, std::min({8, per_split, (200 * 1024) / stage_bytes}));
-    // the store staging needs one 16 KiB slab per 32 output channels inside the pipeline buffers
+    if (split > 8) q.cluster = 0;          // larger splits go through the global workspace
+    // the store staging needs one 16 KiB slab per 32 output channels inside the pipeline buffers,
+    // the cluster reduction one [128][bn + 4] float tile
     while (q.stages * stage_bytes < (q.bn / 32) * kATileBytes) ++q.stages;
+    if (split > 1 && q.cluster)
+        while (size_t(q.stages) * stage_bytes < size_t(kTileM) * (q.bn + 4) * sizeof(float)) ++q.stages;
     q.smem_bytes = size_t(q.stages) * stage_bytes + 24 * q.stages + 64 + 1024;
-    q.workspace_bytes = split > 1 ? size_t(base) * split * q.bn * kTileM * sizeof(float) : 0;
-    q.counter_bytes = split > 1 ? size_t(base) * sizeof(unsigned int) : 0;
+    const bool through_workspace = split > 1 && !q.cluster;
+    q.workspace_bytes = through_workspace ? size_t(base) * split * q.bn * kTileM * sizeof(float) : 0;
+    q.counter_bytes = through_workspace ? size_t(base) * sizeof(unsigned int) : 0;
 }
 
 size_t conv_tc_packed_floats(const ConvGeom &g, const ConvTcPlan &plan) {
@@ -712,17 +856,29 @@ void launch_conv_tc(const ConvTcParams &p, const ConvTcPlan &q, cudaStream_t str
     t.x3 = q.x3;
     t.cout_pad = q.cout_pad;
     t.tma_store = q.tma_store;
+    t.cluster = (q.split_k > 1 && q.cluster) ? 1 : 0;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(q.tiles_w * q.tiles_h * q.tiles_n, q.n_tiles, q.split_k);
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = q.smem_bytes;
     cfg.stream = stream;
     // programmatic dependent launch: this kernel's prologue may overlap the tail of its predecessor
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    if (q.pdl) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
+    if (t.cluster) {                      // the split_k CTAs of one output tile form a cluster
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = 1;
+        attr[n_attr].val.clusterDim.y = 1;
+        attr[n_attr].val.clusterDim.z = unsigned(q.split_k);
+        ++n_attr;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = q.pdl ? 1 : 0;
+    cfg.numAttrs = n_attr;
     cudaLaunchKernelEx(&cfg, conv_tc_kernel, *reinterpret_cast<const CUtensorMap *>(q.tmap_a),
                        *reinterpret_cast<const CUtensorMap *>(q.tmap_b), *reinterpret_cast<const CUtensorMap *>(q.tmap_c), p, t);
 }

@@ -92,6 +92,7 @@ struct ConvTcPlan {
     int x3;                        // 1: three-pass TF32 (operands split into value + residual)
     int tma_store;                 // 1: the output window is 16-byte aligned, the epilogue uses bulk tensor stores
     int pdl;                       // 1: launch with programmatic stream serialization
+    int cluster;                   // 1: a K split of up to 8 is reduced inside a thread-block cluster (no workspace)
     size_t smem_bytes;
     size_t workspace_bytes;        // split-K partial tiles (0 when split_k == 1)
     size_t counter_bytes;          // split-K arrival counters
@@ -114,7 +115,8 @@ struct ConvTcParams {
 bool conv_tc_supported(const TensorRef &in, const ConvGeom &g);
 // Chooses the tiling; sm_count and concurrency_hint (groups running beside this one) steer bn and
 // split_k.  three_pass selects the fp32-grade 3xTF32 product.  Does not touch the device.
-void conv_tc_choose(const ConvGeom &g, int sm_count, int concurrency_hint, bool three_pass, ConvTcPlan *plan);
+void conv_tc_choose(const ConvGeom &g, int sm_count, int concurrency_hint, bool three_pass, ConvTcPlan *plan,
+                    int force_bn = 0);
 // Overrides the K split (recomputes pipeline depth, shared memory and workspace sizes).
 void conv_tc_set_split(ConvTcPlan *plan, int split);
 // Encodes the two tensor maps (needs final device addresses).  Returns a CUDA driver error text or nullptr.

@@ -111,7 +111,8 @@ extern "C" int ios_pointwise_conv_static_scratch(const float *x, const float *w,
 
     ConvTcPlan plan = {};
     conv_tc_choose(g, dev->sm_count, 1, /*three_pass=*/false, &plan);
-    if (split_k > 0) conv_tc_set_split(&plan, split_k);
+    plan.cluster = 0;                                   // reduce through the (static) workspace, not a cluster
+    conv_tc_set_split(&plan, split_k > 0 ? split_k : plan.split_k);
     plan.pdl = 0;
     const size_t tiles = size_t(plan.tiles_w) * plan.tiles_h * plan.tiles_n * plan.n_tiles;
     if (plan.workspace_bytes > kPartialBytes || tiles * sizeof(unsigned int) > kCounterBytes) {

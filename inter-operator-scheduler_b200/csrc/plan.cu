@@ -383,7 +383,7 @@ private:
             slot.weight_floats = size_t(op.kh) * op.kw * op.C;
         } else if (tc_wanted && conv_tc_supported(in, g)) {
             slot.impl = StepKind::ConvTc;
-            conv_tc_choose(g, sms_, width_, plan_.options.three_pass, &slot.tcplan);
+            conv_tc_choose(g, sms_, width_, plan_.options.three_pass, &slot.tcplan, plan_.options.force_bn);
             if (plan_.options.force_split_k > 0) conv_tc_set_split(&slot.tcplan, plan_.options.force_split_k);
             slot.tcplan.pdl = plan_.options.pdl ? 1 : 0;
             slot.weight_floats = conv_tc_packed_floats(g, slot.tcplan);

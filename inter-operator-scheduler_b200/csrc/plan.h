@@ -25,9 +25,11 @@ struct Options {
     bool tf32 = true;           // precision: tensor cores (tf32x3 / tf32) or CUDA cores (fp32)
     bool three_pass = true;     // tf32x3: operands split into TF32 value + residual, fp32-grade products
     bool pdl = true;            // programmatic dependent launch between consecutive convolution kernels
+    bool stage_barriers = true; // join all groups after every stage (the reference's semantics); false: data-flow edges
     bool use_graph = true;      // executor: CUDA graph or plain streams
     bool allow_tc = true;       // conv: auto or direct
     int force_split_k = 0;      // testing aid: > 0 overrides the split-K choice
+    int force_bn = 0;           // testing aid: > 0 overrides the output-channel tile width
     bool timeline = false;      // diagnostics: the tensor-core kernel stamps its phases (see conv_tc.cu)
 };
 

@@ -160,9 +160,77 @@ void launch_step(const Step &s, cudaStream_t stream) {
     }
 }
 
+// Issues one forward with data-flow edges instead of stage barriers: group j still runs on stream j
+// in schedule order, but an operator only waits for the operators whose outputs it reads (an event
+// edge when the producer ran on another stream).  Legal because no buffer of a plan is ever reused:
+// read-after-write is the only hazard.  The schedule keeps deciding what is merged and what shares
+// a stream; a short branch no longer idles until the longest group of its stage has finished.
+void issue_forward_dataflow(DeviceContext &ctx, const Plan &plan) {
+    ctx.need_streams(plan.max_groups);
+    cudaStream_t spine = ctx.streams[0];
+    const Model &m = plan.model;
+    const int n_ops = int(m.ops.size());
+    std::vector<int> stream_of(n_ops, -1), last_step(n_ops, -1);
+    for (size_t i = 0; i < plan.steps.size(); ++i) {
+        stream_of[plan.steps[i].op] = plan.steps[i].group;
+        last_step[plan.steps[i].op] = int(i);
+    }
+    // producers that launch something, looking through operators that are pure aliases
+    std::vector<std::vector<int>> deps(n_ops);
+    for (int op = 0; op < n_ops; ++op) {
+        for (const Term &term : m.ops[op].inputs)
+            for (const ValueRef &v : term) {
+                if (last_step[v.node] >= 0) deps[op].push_back(v.node);
+                else deps[op].insert(deps[op].end(), deps[v.node].begin(), deps[v.node].end());
+            }
+    }
+    std::vector<char> needs_event(n_ops, 0);
+    for (int op = 0; op < n_ops; ++op)
+        if (stream_of[op] >= 0)
+            for (int d : deps[op])
+                if (stream_of[d] != stream_of[op]) needs_event[d] = 1;
+    // alias operators (no launch) forward their dependencies to consumers; nothing else to do for them
+    size_t ev = 0;
+    cudaEvent_t begin = ctx.event(ev++);
+    CUDA_OK(cudaEventRecord(begin, spine));
+    std::vector<char> started(size_t(plan.max_groups), 0);
+    started[0] = 1;
+    std::vector<cudaEvent_t> done(size_t(n_ops), nullptr);
+    int current = -1;
+    for (size_t i = 0; i < plan.steps.size(); ++i) {
+        const Step &step = plan.steps[i];
+        cudaStream_t stream = ctx.streams[step.group];
+        if (step.op != current) {
+            current = step.op;
+            if (!started[step.group]) {
+                CUDA_OK(cudaStreamWaitEvent(stream, begin, 0));
+                started[step.group] = 1;
+            }
+            for (int d : deps[current])
+                if (stream_of[d] != step.group && done[d]) CUDA_OK(cudaStreamWaitEvent(stream, done[d], 0));
+        }
+        launch_step(step, stream);
+        if (int(i) == last_step[current] && needs_event[current]) {
+            done[current] = ctx.event(ev++);
+            CUDA_OK(cudaEventRecord(done[current], stream));
+        }
+    }
+    for (int g = 1; g < plan.max_groups; ++g)
+        if (started[g]) {
+            cudaEvent_t tail = ctx.event(ev++);
+            CUDA_OK(cudaEventRecord(tail, ctx.streams[g]));
+            CUDA_OK(cudaStreamWaitEvent(spine, tail, 0));
+        }
+    CUDA_OK(cudaGetLastError());
+}
+
 // Issues one forward on the context's streams.  stage_marks (optional) receives one timing event
 // per stage, recorded on stream 0 after the stage's groups have joined.
 void issue_forward(DeviceContext &ctx, const Plan &plan, const std::vector<cudaEvent_t> *stage_marks) {
+    if (!stage_marks && !plan.options.stage_barriers) {
+        issue_forward_dataflow(ctx, plan);
+        return;
+    }
     ctx.need_streams(plan.max_groups);
     cudaStream_t spine = ctx.streams[0];
     size_t next = 0;
@@ -576,7 +644,9 @@ int ios_set_option(const char *key, const char *value) {
         else if (k == "executor" && (v == "graph" || v == "streams")) g_options.use_graph = v == "graph";
         else if (k == "conv" && (v == "auto" || v == "direct")) g_options.allow_tc = v == "auto";
         else if (k == "split_k") g_options.force_split_k = std::atoi(value);
+        else if (k == "bn") g_options.force_bn = std::atoi(value);
         else if (k == "timeline") g_options.timeline = v == "1";
+        else if (k == "stage_barriers" && (v == "0" || v == "1")) g_options.stage_barriers = v == "1";
         else throw ArgumentError("unknown option " + k + "=" + v);
     });
 }
@@ -588,6 +658,7 @@ int ios_get_option(const char *key, char *value, int capacity) {
         std::string v;
         if (k == "precision") v = !g_options.tf32 ? "fp32" : g_options.three_pass ? "tf32x3" : "tf32";
         else if (k == "pdl") v = g_options.pdl ? "1" : "0";
+        else if (k == "stage_barriers") v = g_options.stage_barriers ? "1" : "0";
         else if (k == "executor") v = g_options.use_graph ? "graph" : "streams";
         else if (k == "conv") v = g_options.allow_tc ? "auto" : "direct";
         else if (k == "split_k") v = std::to_string(g_options.force_split_k);

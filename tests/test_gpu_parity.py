@@ -80,7 +80,7 @@ def test_conv_cuda_core_vs_oracle(shape):
     assert _conv_case(shape, 'direct', act='tanh') <= TOL_FP32
 
 
-@pytest.mark.parametrize('split', [2, 3, 7])
+@pytest.mark.parametrize('split', [2, 3, 7, 8, 12])   # up to 8: cluster reduction, above: global workspace
 def test_conv_split_k_is_exact_sum_of_partials(split):
     shape = (1, 160, 8, 8, 96, 3, 3, 1, 1, 1, 1, 1)
     rt.set_option('split_k', '1')
