@@ -70,6 +70,8 @@ IOS_API const char *ios_last_error(void);
  * key "precision": "tf32x3" (default; fp32 storage, every product formed from three TF32 tensor-core
  *                  products of value/residual operand pairs, fp32 accumulate: fp32-grade results),
  *                  "tf32" (one TF32 product per multiply: fastest, about 3e-4 relative error per layer),
+ *                  "bf16" (activations and weights stored as bfloat16, bf16 tensor-core products, fp32
+ *                  accumulate: half the memory traffic and twice the tensor rate, about 1e-2 relative error),
  *                  "fp32" (CUDA-core fp32 products, the slow exact path)
  * key "executor":  "graph" (default; a schedule is captured once into a CUDA graph),
  *                  "streams" (group j of every stage is launched on stream j, events between stages)
@@ -117,7 +119,7 @@ IOS_API int ios_engine_get_output(ios_engine *engine, float *output);
  *      src/ios/ios_runtime.cu:309-332, PoolOP::forward :563-566) ------------------------------ */
 /* y[n, cout, oh, ow] = act(conv(x[n, cin, h, w], w[cout, cin/groups, kh, kw]) + bias).
  * act: 0 identity, 1 relu, 2 sigmoid, 3 tanh.  impl: 0 auto, 1 direct (CUDA cores), 2 tensor cores with the
- * current precision option, 3 tensor cores single-pass TF32. */
+ * current precision option, 3 tensor cores single-pass TF32, 4 tensor cores bfloat16. */
 IOS_API int ios_conv2d(const float *x, const float *w, const float *bias, float *y, int n, int cin, int h,
                        int wdt, int cout, int kh, int kw, int sh, int sw, int ph, int pw, int groups,
                        int act, int impl);

@@ -9,6 +9,8 @@
 // (src/ios/ios_runtime.cu:313-331) for their shapes.
 #include "kernels.h"
 
+#include <cuda_bf16.h>
+
 #include <cstring>
 
 namespace ios {
@@ -34,10 +36,32 @@ __device__ __forceinline__ float finish_value(float v, int act, int round_out) {
     return round_out ? to_tf32(v) : v;
 }
 
+// ---- element access (activations are float32 or bfloat16; weights, bias and arithmetic float32) ----
+__device__ __forceinline__ float load1(const float *p) { return *p; }
+__device__ __forceinline__ float load1(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
+__device__ __forceinline__ void store1(float *p, float v) { *p = v; }
+__device__ __forceinline__ void store1(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
+__device__ __forceinline__ float4 load4(const float *p) { return *reinterpret_cast<const float4 *>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16 *p) {
+    const uint2 raw = *reinterpret_cast<const uint2 *>(p);
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.x));
+    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+__device__ __forceinline__ void store4(float *p, float4 v) { *reinterpret_cast<float4 *>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16 *p, float4 v) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const uint32_t *>(&lo);
+    raw.y = *reinterpret_cast<const uint32_t *>(&hi);
+    *reinterpret_cast<uint2 *>(p) = raw;
+}
+
 // One thread per (pixel, 4 consecutive output channels of one group); consecutive threads take
 // consecutive channel quads, so weight reads are coalesced and the activation read is a broadcast.
 constexpr int kCoPerThread = 4;
 
+template <typename T>
 __global__ void __launch_bounds__(128) conv_direct_kernel(const ConvDirectParams p) {
     const ConvGeom &g = p.g;
     const int cin_g = g.Cin / g.groups, cout_g = g.Cout / g.groups;
@@ -61,10 +85,10 @@ __global__ void __launch_bounds__(128) conv_direct_kernel(const ConvDirectParams
             for (int s = 0; s < g.kw; ++s) {
                 const int w = ow * g.sw - g.pw + s;
                 if (w < 0 || w >= g.W) continue;
-                const float *x = p.in.ptr + ((long(n) * g.H + h) * g.W + w) * p.in.pitch + grp * cin_g;
+                const T *x = p.in.as<const T>() + ((long(n) * g.H + h) * g.W + w) * p.in.pitch + grp * cin_g;
                 const float *wt = p.weight + (long(r * g.kw + s) * cin_g) * g.Cout;
                 for (int c = 0; c < cin_g; ++c) {
-                    float xv = x[c];
+                    float xv = load1(x + c);
                     if (g.pre_relu) xv = fmaxf(xv, 0.0f);
                     const float *wrow = wt + long(c) * g.Cout;
 #pragma unroll
@@ -73,14 +97,14 @@ __global__ void __launch_bounds__(128) conv_direct_kernel(const ConvDirectParams
                 }
             }
         }
-        float *y = p.out.ptr + ((long(n) * g.OH + oh) * g.OW + ow) * p.out.pitch;
+        T *y = p.out.as<T>() + ((long(n) * g.OH + oh) * g.OW + ow) * p.out.pitch;
 #pragma unroll
         for (int j = 0; j < kCoPerThread; ++j)
-            if (co0 + j < co_end) y[co0 + j] = act_apply(acc[j] + (p.bias ? p.bias[co0 + j] : 0.0f), g.act);
+            if (co0 + j < co_end) store1(y + co0 + j, act_apply(acc[j] + (p.bias ? p.bias[co0 + j] : 0.0f), g.act));
     }
 }
 
-template <bool kVec>
+template <typename T, bool kVec>
 __global__ void __launch_bounds__(256) conv_depthwise_kernel(const ConvDirectParams p) {
     const ConvGeom &g = p.g;
     const int lanes = kVec ? g.Cout / 4 : g.Cout;
@@ -99,10 +123,10 @@ __global__ void __launch_bounds__(256) conv_depthwise_kernel(const ConvDirectPar
             for (int s = 0; s < g.kw; ++s) {
                 const int w = ow * g.sw - g.pw + s;
                 if (w < 0 || w >= g.W) continue;
-                const float *x = p.in.ptr + ((long(n) * g.H + h) * g.W + w) * p.in.pitch;
+                const T *x = p.in.as<const T>() + ((long(n) * g.H + h) * g.W + w) * p.in.pitch;
                 const float *wt = p.weight + long(r * g.kw + s) * g.Cout;
                 if (kVec) {
-                    float4 xv = *reinterpret_cast<const float4 *>(x + 4 * c);
+                    float4 xv = load4(x + 4 * c);
                     const float4 wv = *reinterpret_cast<const float4 *>(wt + 4 * c);
                     if (g.pre_relu) {
                         xv.x = fmaxf(xv.x, 0.f); xv.y = fmaxf(xv.y, 0.f); xv.z = fmaxf(xv.z, 0.f); xv.w = fmaxf(xv.w, 0.f);
@@ -110,21 +134,21 @@ __global__ void __launch_bounds__(256) conv_depthwise_kernel(const ConvDirectPar
                     acc.x = fmaf(xv.x, wv.x, acc.x); acc.y = fmaf(xv.y, wv.y, acc.y);
                     acc.z = fmaf(xv.z, wv.z, acc.z); acc.w = fmaf(xv.w, wv.w, acc.w);
                 } else {
-                    float xv = x[c];
+                    float xv = load1(x + c);
                     if (g.pre_relu) xv = fmaxf(xv, 0.f);
                     acc.x = fmaf(xv, wt[c], acc.x);
                 }
             }
         }
-        float *y = p.out.ptr + ((long(n) * g.OH + oh) * g.OW + ow) * p.out.pitch;
+        T *y = p.out.as<T>() + ((long(n) * g.OH + oh) * g.OW + ow) * p.out.pitch;
         if (kVec) {
             float4 b = p.bias ? *reinterpret_cast<const float4 *>(p.bias + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
             float4 o;
             o.x = act_apply(acc.x + b.x, g.act); o.y = act_apply(acc.y + b.y, g.act);
             o.z = act_apply(acc.z + b.z, g.act); o.w = act_apply(acc.w + b.w, g.act);
-            *reinterpret_cast<float4 *>(y + 4 * c) = o;
+            store4(y + 4 * c, o);
         } else {
-            y[c] = act_apply(acc.x + (p.bias ? p.bias[c] : 0.f), g.act);
+            store1(y + c, act_apply(acc.x + (p.bias ? p.bias[c] : 0.f), g.act));
         }
     }
 }
@@ -142,7 +166,8 @@ void launch_conv_direct(const ConvDirectParams &p, cudaStream_t stream) {
     const ConvGeom &g = p.g;
     const int cout_g = g.Cout / g.groups;
     const long work = long(g.N) * g.OH * g.OW * ((cout_g + kCoPerThread - 1) / kCoPerThread) * g.groups;
-    conv_direct_kernel<<<blocks_for(work, 128), 128, 0, stream>>>(p);
+    if (p.in.esize == 2) conv_direct_kernel<__nv_bfloat16><<<blocks_for(work, 128), 128, 0, stream>>>(p);
+    else conv_direct_kernel<float><<<blocks_for(work, 128), 128, 0, stream>>>(p);
 }
 
 void launch_conv_depthwise(const ConvDirectParams &p, cudaStream_t stream) {
@@ -151,8 +176,13 @@ void launch_conv_depthwise(const ConvDirectParams &p, cudaStream_t stream) {
                      ((reinterpret_cast<uintptr_t>(p.weight) & 15) == 0) &&
                      (!p.bias || (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0);
     const long work = long(g.N) * g.OH * g.OW * (vec ? g.Cout / 4 : g.Cout);
-    if (vec) conv_depthwise_kernel<true><<<blocks_for(work, 256), 256, 0, stream>>>(p);
-    else conv_depthwise_kernel<false><<<blocks_for(work, 256), 256, 0, stream>>>(p);
+    if (p.in.esize == 2) {
+        if (vec) conv_depthwise_kernel<__nv_bfloat16, true><<<blocks_for(work, 256), 256, 0, stream>>>(p);
+        else conv_depthwise_kernel<__nv_bfloat16, false><<<blocks_for(work, 256), 256, 0, stream>>>(p);
+    } else {
+        if (vec) conv_depthwise_kernel<float, true><<<blocks_for(work, 256), 256, 0, stream>>>(p);
+        else conv_depthwise_kernel<float, false><<<blocks_for(work, 256), 256, 0, stream>>>(p);
+    }
 }
 
 void conv_direct_pack_weights(const float *oihw, const ConvGeom &g, float *packed) {

@@ -31,6 +31,7 @@
 #include "kernels.h"
 
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cstdio>
 #include <cstring>
 #include <cmath>
@@ -41,8 +42,9 @@ namespace ios {
 namespace {
 
 constexpr int kTileM = 128;          // TMEM lanes = pixel rows per CTA
-constexpr int kChunk = 32;           // floats of K per pipeline step = one 128-byte swizzle row
-constexpr int kATileBytes = kTileM * kChunk * 4;   // 16 KiB
+constexpr int kRowBytes = 128;       // K bytes per pipeline step = one 128-byte swizzle row (32 floats or 64 bf16)
+constexpr int kChunk = 32;           // float32 elements per row
+constexpr int kATileBytes = kTileM * kRowBytes;    // 16 KiB
 constexpr int kThreads = 192;
 constexpr uint64_t kWaitBudgetNs = 2000000000ull;  // 2 s per wait
 
@@ -57,6 +59,8 @@ struct TileGeom {
     int cout_pad;     // rows of one plane of the packed weight matrix
     int tma_store;    // 1: the epilogue stages the tile in shared memory and stores it with bulk tensor stores
     int cluster;      // 1: the split_k CTAs of a tile form a thread-block cluster and reduce through shared memory
+    int bf16;         // 1: bfloat16 operands / activations (kind::f16), 0: float32 storage (kind::tf32)
+    int chunk;        // elements of K per 128-byte row: 32 (float32) or 64 (bfloat16)
 };
 
 // ---- PTX wrappers ----------------------------------------------------------------------------
@@ -154,8 +158,31 @@ __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint
         ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// two 16-column loads in flight, one wait
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float *v) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float *v) {
     uint32_t r[16];
@@ -204,6 +231,48 @@ __device__ __forceinline__ uint32_t sw128_offset(int row, int c4) {
     return uint32_t(row) * 128u + (uint32_t(c4 ^ (row & 7)) << 4);
 }
 
+// Stage four finished values (tile channels cc..cc+3 of `row`) for the bulk store: the staging area
+// is [slab][row][128 B] with the TMA swizzle, a slab being 32 float32 or 64 bfloat16 channels.
+__device__ __forceinline__ void stage4(uint8_t *staging, int row, int cc, float4 o, int bf16) {
+    if (!bf16) {
+        *reinterpret_cast<float4 *>(staging + size_t(cc >> 5) * kATileBytes + sw128_offset(row, (cc & 31) >> 2)) = o;
+    } else {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(o.x, o.y), hi = __floats2bfloat162_rn(o.z, o.w);
+        uint2 raw;
+        raw.x = *reinterpret_cast<const uint32_t *>(&lo);
+        raw.y = *reinterpret_cast<const uint32_t *>(&hi);
+        *reinterpret_cast<uint2 *>(staging + size_t(cc >> 6) * kATileBytes + sw128_offset(row, (cc & 63) >> 3) + ((cc & 7) << 1)) = raw;
+    }
+}
+// Store up to four finished values straight to the output window at element offset `at`.
+__device__ __forceinline__ void store4_direct(void *out, int bf16, long at, float4 o, int count) {
+    if (!bf16) {
+        float *dst = static_cast<float *>(out) + at;
+        if (count >= 4 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+            *reinterpret_cast<float4 *>(dst) = o;
+        } else {
+            const float v[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (j < count) dst[j] = v[j];
+        }
+    } else {
+        __nv_bfloat16 *dst = static_cast<__nv_bfloat16 *>(out) + at;
+        if (count >= 4 && (reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(o.x, o.y), hi = __floats2bfloat162_rn(o.z, o.w);
+            uint2 raw;
+            raw.x = *reinterpret_cast<const uint32_t *>(&lo);
+            raw.y = *reinterpret_cast<const uint32_t *>(&hi);
+            *reinterpret_cast<uint2 *>(dst) = raw;
+        } else {
+            const float v[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (j < count) dst[j] = __float2bfloat16_rn(v[j]);
+        }
+    }
+}
+
 // ---- the kernel ------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kThreads, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -212,7 +281,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     __shared__ float bias_s[256];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
-    const int b_bytes = t.bn * kChunk * 4;
+    const int b_bytes = t.bn * kRowBytes;
     const int passes = t.x3 ? 2 : 1;                       // operand planes per stage: value (+ residual)
     const int stage_bytes = passes * (kATileBytes + b_bytes);
     // stage layout: A | A residual | B | B residual
@@ -247,13 +316,19 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int it_end = int(long(split + 1) * t.k_iters / t.split_k);
     const int n_it = it_end - it_begin;
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < t.stages; ++s) {
-            mbar_init(full0 + 8u * s, 1);
-            mbar_init(empty0 + 8u * s, 1);
-            mbar_init(ready0 + 8u * s, 128);
+    if (warp == 0) {
+        // one lane per pipeline stage initialises its three barriers; lane 31 fetches the tensor maps
+        if (lane < t.stages) {
+            mbar_init(full0 + 8u * lane, 1);
+            mbar_init(empty0 + 8u * lane, 1);
+            mbar_init(ready0 + 8u * lane, 128);
         }
-        mbar_init(accum_bar, 1);
+        if (lane == 30) mbar_init(accum_bar, 1);
+        if (lane == 31) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
+            if (t.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_c) : "memory");
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -273,8 +348,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     if (warp == 0) {
         if (lane == 0) {
             // ---------------- TMA producer ----------------
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
             asm volatile("griddepcontrol.wait;" ::: "memory");
             bool ok = true;
             int issued = 0;
@@ -289,10 +362,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 const uint32_t stage = smem_base + uint32_t(s) * stage_bytes;
                 const uint32_t bar = full0 + 8u * s;
                 mbar_expect_tx(bar, uint32_t(t.a_bytes + passes * b_bytes));
-                if (t.flat) tma_load_4d(stage, &tmap_a, bar, cc * kChunk, ow0, 0, 0);
-                else tma_load_4d(stage, &tmap_a, bar, cc * kChunk, ow0 * g.sw - g.pw + sx, oh0 * g.sh - g.ph + r, n0);
-                tma_load_2d(stage + b_off, &tmap_b, bar, it * kChunk, cout0);
-                if (t.x3) tma_load_2d(stage + b_lo_off, &tmap_b, bar, it * kChunk, t.cout_pad + cout0);
+                if (t.flat) tma_load_4d(stage, &tmap_a, bar, cc * t.chunk, ow0, 0, 0);
+                else tma_load_4d(stage, &tmap_a, bar, cc * t.chunk, ow0 * g.sw - g.pw + sx, oh0 * g.sh - g.ph + r, n0);
+                tma_load_2d(stage + b_off, &tmap_b, bar, it * t.chunk, cout0);
+                if (t.x3) tma_load_2d(stage + b_lo_off, &tmap_b, bar, it * t.chunk, t.cout_pad + cout0);
                 if (i == 0) STAMP(2);
                 issued = i + 1;
             }
@@ -306,7 +379,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     } else if (warp == 1) {
         if (lane == 0) {
             // ---------------- MMA issuer ----------------
-            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(t.bn >> 3) << 17) | (uint32_t(kTileM >> 4) << 24);
+            // instruction descriptor: fp32 accumulator, A/B format (2 = TF32, 1 = BF16), K-major, N, M
+            const uint32_t fmt = t.bf16 ? 1u : 2u;
+            const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(t.bn >> 3) << 17) | (uint32_t(kTileM >> 4) << 24);
             const uint32_t wait0 = t.x3 ? ready0 : full0;
             bool ok = true;
 #pragma unroll 1
@@ -322,14 +397,18 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     // a*w ~= a_lo*w_hi + a_hi*w_lo + a_hi*w_hi, small terms first
                     const uint64_t dal = smem_desc_sw128(stage + a_lo_off), dbl = smem_desc_sw128(stage + b_lo_off);
 #pragma unroll
-                    for (int k = 0; k < kChunk / 8; ++k) {
+                    for (int k = 0; k < kRowBytes / 32; ++k) {
                         umma_tf32(tmem_base, dal + uint64_t(k * 2), db + uint64_t(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
                         umma_tf32(tmem_base, da + uint64_t(k * 2), dbl + uint64_t(k * 2), idesc, 1u);
                         umma_tf32(tmem_base, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, 1u);
                     }
+                } else if (t.bf16) {
+#pragma unroll
+                    for (int k = 0; k < kRowBytes / 32; ++k)      // K = 16 bf16 = 32 bytes per instruction
+                        umma_f16(tmem_base, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
                 } else {
 #pragma unroll
-                    for (int k = 0; k < kChunk / 8; ++k)
+                    for (int k = 0; k < kRowBytes / 32; ++k)      // K = 8 tf32 = 32 bytes per instruction
                         umma_tf32(tmem_base, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
                 }
                 umma_commit(empty0 + 8u * s);   // frees the stage once these MMAs have read it
@@ -388,11 +467,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (ok) {
                 float *part = reinterpret_cast<float *>(generic_base) + size_t(row) * (t.bn + 4);
 #pragma unroll 1
-                for (int c = 0; c < t.bn; c += 16) {
-                    float v[16];
-                    tmem_ld16(taddr + c, v);
+                for (int c = 0; c < t.bn; c += 32) {
+                    float v[32];
+                    tmem_ld32(taddr + c, v);
 #pragma unroll
-                    for (int j = 0; j < 16; j += 4)
+                    for (int j = 0; j < 32; j += 4)
                         *reinterpret_cast<float4 *>(part + c + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
                 }
             }
@@ -433,11 +512,27 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     pix_off = ((long(n) * g.OH + oh) * g.OW + ow) * p.out.pitch;
             }
             const int valid = min(t.bn, g.Cout - cout0);
-            float *dst = p.out.ptr + (pix_off < 0 ? 0 : pix_off) + cout0;
-            const bool vec_ok = ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
             const float *ws_tile = p.workspace + size_t(tile_id) * t.split_k * size_t(t.bn) * kTileM;
             // (loops that run a handful of times are kept rolled: the code of a CTA runs once, so its
             // cost is dominated by instruction fetch, not by loop overhead)
+            if (t.split_k == 1 && t.tma_store) {
+                // common case: 32 channels = one 128-byte staging row per TMEM round trip
+#pragma unroll 1
+                for (int c = 0; c < t.bn; c += 32) {
+                    float v[32];
+                    tmem_ld32(taddr + c, v);
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        float o[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const float z = act_apply(v[j + u] + bias_s[c + j + u], g.act);
+                            o[u] = t.round_tf32 ? round_tf32(z) : z;
+                        }
+                        stage4(generic_base, row, c + j, make_float4(o[0], o[1], o[2], o[3]), t.bf16);
+                    }
+                }
+            } else
 #pragma unroll 1
             for (int c = 0; c < t.bn; c += 16) {
                 float v[16];
@@ -472,25 +567,19 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 }
                 if (c == 0 && threadIdx.x == 64) STAMP(14);
                 if (t.tma_store) {
-                    // stage the tile as [32-channel slab][row][128 B], swizzled like a TMA box, for the bulk store
-                    uint8_t *slab = generic_base + size_t(c >> 5) * kATileBytes;
-                    const int c4 = (c & 31) >> 2;
+                    // stage the tile as [slab][row][128 B], swizzled like a TMA box, for the bulk store
 #pragma unroll
                     for (int j = 0; j < 16; j += 4)
-                        *reinterpret_cast<float4 *>(slab + sw128_offset(row, c4 + (j >> 2))) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                        stage4(generic_base, row, c + j, make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]), t.bf16);
                     if (c == 0 && threadIdx.x == 64) STAMP(15);
                     continue;
                 }
                 if (pix_off < 0 || c >= valid) continue;
-                if (vec_ok && c + 16 <= valid) {
 #pragma unroll
-                    for (int j = 0; j < 16; j += 4)
-                        *reinterpret_cast<float4 *>(dst + c + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        if (c + j < valid) dst[c + j] = v[j];
-                }
+                for (int j = 0; j < 16; j += 4)
+                    if (c + j < valid)
+                        store4_direct(p.out.ptr, t.bf16, pix_off + cout0 + c + j, make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]),
+                                      valid - (c + j));
             }
             if (threadIdx.x == 64) STAMP(10);
             if (t.tma_store) {
@@ -498,9 +587,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (threadIdx.x == 64) {
                     STAMP(11);
-                    // one bulk tensor store per 32-channel slab; pixels and channels outside the tensor are clipped
-                    for (int c = 0; c < valid; c += 32) {
-                        const uint32_t src = smem_base + uint32_t(c >> 5) * kATileBytes;
+                    // one bulk tensor store per 128-byte slab; pixels and channels outside the tensor are clipped
+                    for (int c = 0; c < valid; c += t.chunk) {
+                        const uint32_t src = smem_base + uint32_t(c / t.chunk) * kATileBytes;
                         if (t.flat) tma_store_4d(&tmap_c, src, cout0 + c, ow0, 0, 0);
                         else tma_store_4d(&tmap_c, src, cout0 + c, ow0, oh0, n0);
                     }
@@ -563,14 +652,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     const float z = act_apply(o[j] + bias_s[c + j], g.act);
                     o[j] = t.round_tf32 ? round_tf32(z) : z;
                 }
-                float *dst = p.out.ptr + pix_off + cout0 + c;
-                if (c + 4 <= valid && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-                    *reinterpret_cast<float4 *>(dst) = make_float4(o[0], o[1], o[2], o[3]);
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        if (c + j < valid) dst[j] = o[j];
-                }
+                store4_direct(p.out.ptr, t.bf16, pix_off + cout0 + c, make_float4(o[0], o[1], o[2], o[3]), valid - c);
             }
             if (threadIdx.x == 64) STAMP(7);
         }
@@ -618,7 +700,7 @@ float tf32_round_host(float v) {
 
 bool conv_tc_supported(const TensorRef &in, const ConvGeom &g) {
     if (g.groups != 1 || g.pre_relu) return false;
-    if ((reinterpret_cast<uintptr_t>(in.ptr) & 15) != 0 || in.pitch % 4 != 0) return false;
+    if ((reinterpret_cast<uintptr_t>(in.ptr) & 15) != 0 || (size_t(in.pitch) * in.esize) % 16 != 0) return false;
     if (g.sw > 8 || g.sh > 8) return false;            // TMA element strides are at most 8
     if (g.kh * g.kw > 4096) return false;
     return true;
@@ -631,13 +713,17 @@ bool conv_tc_supported(const TensorRef &in, const ConvGeom &g) {
 //     time = waves * cta,  waves = ceil(ctas / how many fit at once)
 // over every pixel-tile shape, output-channel tile width and K split that the kernel supports.
 // It replaces the reference's run-time algorithm search (src/ios/ios_runtime.cu:150-205).
-void conv_tc_choose(const ConvGeom &g, int sm_count, int concurrency_hint, bool three_pass, ConvTcPlan *plan, int force_bn) {
+void conv_tc_choose(const ConvGeom &g, int sm_count, int concurrency_hint, bool three_pass, ConvTcPlan *plan, int force_bn,
+                    bool bf16) {
     ConvTcPlan &q = *plan;
-    q.x3 = three_pass ? 1 : 0;
+    q.bf16 = bf16 ? 1 : 0;
+    q.x3 = (three_pass && !bf16) ? 1 : 0;
     q.cluster = 1;
+    const int chunk = bf16 ? 64 : 32;            // K elements per 128-byte row
+    const int bn_step = bf16 ? 64 : 32;          // output channels per 128-byte row of the store staging
     const bool flat = g.kh == 1 && g.kw == 1 && g.sh == 1 && g.sw == 1 && g.ph == 0 && g.pw == 0;
     q.flat_1x1 = flat ? 1 : 0;
-    q.cchunks = ceil_div(g.Cin, kChunk);
+    q.cchunks = ceil_div(g.Cin, chunk);
     q.k_iters = g.kh * g.kw * q.cchunks;
 
     struct Shape { int box_w, box_h, box_n, tiles_w, tiles_h, tiles_n; };
@@ -668,7 +754,7 @@ void conv_tc_choose(const ConvGeom &g, int sm_count, int concurrency_hint, bool 
         }
     }
     const double kFixed = 3000.0, kFillBytesPerCycle = 20.0, kEpiloguePer16 = 400.0, kClusterOverhead = 500.0;
-    const int planes = three_pass ? 2 : 1;
+    const int planes = q.x3 ? 2 : 1;
     const int share = std::max(1, concurrency_hint);
     double best_cost = 1e30;
     Shape best_shape = shapes[0];
@@ -678,9 +764,9 @@ void conv_tc_choose(const ConvGeom &g, int sm_count, int concurrency_hint, bool 
         const int m_tiles = sh.tiles_w * sh.tiles_h * sh.tiles_n;
         const int rows = sh.box_w * sh.box_h * sh.box_n;
         int last_bn = 0;
-        for (int n_tiles = 1; n_tiles <= ceil_div(g.Cout, 32); ++n_tiles) {
-            int bn = std::min(256, ceil_div(ceil_div(g.Cout, n_tiles), 32) * 32);
-            if (force_bn > 0) bn = std::min(256, ceil_div(force_bn, 32) * 32);
+        for (int n_tiles = 1; n_tiles <= ceil_div(g.Cout, bn_step); ++n_tiles) {
+            int bn = std::min(256, ceil_div(ceil_div(g.Cout, n_tiles), bn_step) * bn_step);
+            if (force_bn > 0) bn = std::min(256, ceil_div(force_bn, bn_step) * bn_step);
             if (bn == last_bn) continue;
             last_bn = bn;
             const int nt = ceil_div(g.Cout, bn);
@@ -716,13 +802,14 @@ void conv_tc_set_split(ConvTcPlan *plan, int split) {
     split = std::max(1, std::min(split, q.k_iters));
     const int base = q.tiles_w * q.tiles_h * q.tiles_n * q.n_tiles;
     q.split_k = split;
-    const int stage_bytes = (q.x3 ? 2 : 1) * (kATileBytes + q.bn * kChunk * 4);
+    const int stage_bytes = (q.x3 ? 2 : 1) * (kATileBytes + q.bn * kRowBytes);
+    const int slab_channels = q.bf16 ? 64 : 32;
     const int per_split = ceil_div(q.k_iters, split);
     q.stages = std::max(2, std::min({8, per_split, (200 * 1024) / stage_bytes}));
     if (split > 8) q.cluster = 0;          // larger splits go through the global workspace
     // the store staging needs one 16 KiB slab per 32 output channels inside the pipeline buffers,
     // the cluster reduction one [128][bn + 4] float tile
-    while (q.stages * stage_bytes < (q.bn / 32) * kATileBytes) ++q.stages;
+    while (q.stages * stage_bytes < ceil_div(q.bn, slab_channels) * kATileBytes) ++q.stages;
     if (split > 1 && q.cluster)
         while (size_t(q.stages) * stage_bytes < size_t(kTileM) * (q.bn + 4) * sizeof(float)) ++q.stages;
     q.smem_bytes = size_t(q.stages) * stage_bytes + 24 * q.stages + 64 + 1024;
@@ -731,21 +818,37 @@ void conv_tc_set_split(ConvTcPlan *plan, int split) {
     q.counter_bytes = through_workspace ? size_t(base) * sizeof(unsigned int) : 0;
 }
 
-size_t conv_tc_packed_floats(const ConvGeom &g, const ConvTcPlan &plan) {
-    return size_t(plan.x3 ? 2 : 1) * plan.cout_pad * g.kh * g.kw * plan.cchunks * kChunk;
+static uint16_t bf16_round_host(float v) {
+    uint32_t u;
+    std::memcpy(&u, &v, 4);
+    if ((u & 0x7F800000u) == 0x7F800000u) return uint16_t(u >> 16);   // inf / nan
+    u += 0x00007FFFu + ((u >> 16) & 1u);                                // round to nearest even
+    return uint16_t(u >> 16);
 }
 
-void conv_tc_pack_weights(const float *oihw, const ConvGeom &g, const ConvTcPlan &plan, float *packed) {
+size_t conv_tc_packed_bytes(const ConvGeom &g, const ConvTcPlan &plan) {
+    const size_t elems = size_t(plan.x3 ? 2 : 1) * plan.cout_pad * g.kh * g.kw * plan.cchunks * (plan.bf16 ? 64 : 32);
+    return elems * (plan.bf16 ? 2 : 4);
+}
+
+void conv_tc_pack_weights(const float *oihw, const ConvGeom &g, const ConvTcPlan &plan, void *packed_out) {
     const int taps = g.kh * g.kw;
-    const size_t row = size_t(taps) * plan.cchunks * kChunk;
+    const int chunk = plan.bf16 ? 64 : 32;
+    const size_t row = size_t(taps) * plan.cchunks * chunk;
     const size_t plane = size_t(plan.cout_pad) * row;
-    std::memset(packed, 0, (plan.x3 ? 2 : 1) * plane * sizeof(float));
+    std::memset(packed_out, 0, conv_tc_packed_bytes(g, plan));
+    float *packed = static_cast<float *>(packed_out);
+    uint16_t *packed16 = static_cast<uint16_t *>(packed_out);
     for (int o = 0; o < g.Cout; ++o)
         for (int c = 0; c < g.Cin; ++c)
             for (int tp = 0; tp < taps; ++tp) {
                 const float w = oihw[(size_t(o) * g.Cin + c) * taps + tp];
+                const size_t at = size_t(o) * row + size_t(tp) * plan.cchunks * chunk + c;
+                if (plan.bf16) {
+                    packed16[at] = bf16_round_host(w);
+                    continue;
+                }
                 const float hi = tf32_round_host(w);
-                const size_t at = size_t(o) * row + size_t(tp) * plan.cchunks * kChunk + c;
                 packed[at] = hi;
                 if (plan.x3) packed[plane + at] = tf32_round_host(w - hi);   // residual plane
             }
@@ -757,6 +860,9 @@ const char *conv_tc_encode(const ConvTcParams &p, ConvTcPlan *plan) {
     const ConvGeom &g = p.g;
     ConvTcPlan &q = *plan;
     static thread_local char msg[160];
+    const CUtensorMapDataType dtype = q.bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    const cuuint64_t esize = q.bf16 ? 2 : 4;
+    const cuuint32_t chunk = q.bf16 ? 64 : 32;
     auto fail = [&](const char *what, CUresult r) {
         std::snprintf(msg, sizeof msg, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, int(r));
         return msg;
@@ -765,55 +871,56 @@ const char *conv_tc_encode(const ConvTcParams &p, ConvTcPlan *plan) {
         cuuint64_t dims[4];
         cuuint64_t strides[3];
         cuuint32_t box[4], estr[4];
-        const cuuint64_t pix_bytes = cuuint64_t(p.in.pitch) * 4;
+        const cuuint64_t pix_bytes = cuuint64_t(p.in.pitch) * esize;
         if (q.flat_1x1) {
             dims[0] = cuuint64_t(g.Cin); dims[1] = cuuint64_t(g.N) * g.H * g.W; dims[2] = 1; dims[3] = 1;
             strides[0] = pix_bytes; strides[1] = pix_bytes * dims[1]; strides[2] = strides[1];
-            box[0] = kChunk; box[1] = cuuint32_t(q.box_w); box[2] = 1; box[3] = 1;
+            box[0] = chunk; box[1] = cuuint32_t(q.box_w); box[2] = 1; box[3] = 1;
             estr[0] = estr[1] = estr[2] = estr[3] = 1;
         } else {
             dims[0] = cuuint64_t(g.Cin); dims[1] = cuuint64_t(g.W); dims[2] = cuuint64_t(g.H); dims[3] = cuuint64_t(g.N);
             strides[0] = pix_bytes; strides[1] = pix_bytes * g.W; strides[2] = pix_bytes * g.W * g.H;
-            box[0] = kChunk; box[1] = cuuint32_t(q.box_w * g.sw); box[2] = cuuint32_t(q.box_h * g.sh); box[3] = cuuint32_t(q.box_n);
+            box[0] = chunk; box[1] = cuuint32_t(q.box_w * g.sw); box[2] = cuuint32_t(q.box_h * g.sh); box[3] = cuuint32_t(q.box_n);
             estr[0] = 1; estr[1] = cuuint32_t(g.sw); estr[2] = cuuint32_t(g.sh); estr[3] = 1;
         }
-        CUresult r = encode(reinterpret_cast<CUtensorMap *>(q.tmap_a), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.in.ptr, dims,
+        CUresult r = encode(reinterpret_cast<CUtensorMap *>(q.tmap_a), dtype, 4, p.in.ptr, dims,
                             strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail("activations", r);
     }
     {
-        const cuuint64_t krow = cuuint64_t(g.kh) * g.kw * q.cchunks * kChunk;
+        const cuuint64_t krow = cuuint64_t(g.kh) * g.kw * q.cchunks * chunk;
         cuuint64_t dims[2] = {krow, cuuint64_t(q.cout_pad) * (q.x3 ? 2 : 1)};
-        cuuint64_t strides[1] = {krow * 4};
-        cuuint32_t box[2] = {kChunk, cuuint32_t(q.bn)};
+        cuuint64_t strides[1] = {krow * esize};
+        cuuint32_t box[2] = {chunk, cuuint32_t(q.bn)};
         cuuint32_t estr[2] = {1, 1};
-        CUresult r = encode(reinterpret_cast<CUtensorMap *>(q.tmap_b), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
-                            const_cast<float *>(p.weight_packed), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+        CUresult r = encode(reinterpret_cast<CUtensorMap *>(q.tmap_b), dtype, 2,
+                            const_cast<void *>(p.weight_packed), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail("weights", r);
     }
     // the output window: bulk tensor stores need a 16-byte aligned base
     // and a window whose end is 16-byte aligned too, so that clipping never lands inside a 16-byte unit
-    q.tma_store = ((reinterpret_cast<uintptr_t>(p.out.ptr) & 15) == 0 && p.out.pitch % 4 == 0 && g.Cout % 4 == 0) ? 1 : 0;
+    const int per16 = int(16 / esize);
+    q.tma_store = ((reinterpret_cast<uintptr_t>(p.out.ptr) & 15) == 0 && p.out.pitch % per16 == 0 && g.Cout % per16 == 0) ? 1 : 0;
     std::memcpy(q.tmap_c, q.tmap_a, sizeof q.tmap_c);
     if (q.tma_store) {
         cuuint64_t dims[4];
         cuuint64_t strides[3];
         cuuint32_t box[4];
         cuuint32_t estr[4] = {1, 1, 1, 1};
-        const cuuint64_t pix_bytes = cuuint64_t(p.out.pitch) * 4;
+        const cuuint64_t pix_bytes = cuuint64_t(p.out.pitch) * esize;
         if (q.flat_1x1) {
             dims[0] = cuuint64_t(g.Cout); dims[1] = cuuint64_t(g.N) * g.OH * g.OW; dims[2] = 1; dims[3] = 1;
             strides[0] = pix_bytes; strides[1] = pix_bytes * dims[1]; strides[2] = strides[1];
-            box[0] = kChunk; box[1] = cuuint32_t(q.box_w); box[2] = 1; box[3] = 1;
+            box[0] = chunk; box[1] = cuuint32_t(q.box_w); box[2] = 1; box[3] = 1;
         } else {
             dims[0] = cuuint64_t(g.Cout); dims[1] = cuuint64_t(g.OW); dims[2] = cuuint64_t(g.OH); dims[3] = cuuint64_t(g.N);
             strides[0] = pix_bytes; strides[1] = pix_bytes * g.OW; strides[2] = pix_bytes * g.OW * g.OH;
-            box[0] = kChunk; box[1] = cuuint32_t(q.box_w); box[2] = cuuint32_t(q.box_h); box[3] = cuuint32_t(q.box_n);
+            box[0] = chunk; box[1] = cuuint32_t(q.box_w); box[2] = cuuint32_t(q.box_h); box[3] = cuuint32_t(q.box_n);
         }
-        CUresult r = encode(reinterpret_cast<CUtensorMap *>(q.tmap_c), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.out.ptr, dims,
+        CUresult r = encode(reinterpret_cast<CUtensorMap *>(q.tmap_c), dtype, 4, p.out.ptr, dims,
                             strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                             CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail("output", r);
@@ -833,7 +940,7 @@ const char *conv_tc_encode_dense_weights(const ConvTcParams &p, ConvTcPlan *plan
     cuuint32_t box[2] = {kChunk, cuuint32_t(plan->bn)};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = encode(reinterpret_cast<CUtensorMap *>(plan->tmap_b), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
-                        const_cast<float *>(p.weight_packed), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        const_cast<void *>(p.weight_packed), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? nullptr : "cuTensorMapEncodeTiled(dense weights) failed";
 }
@@ -848,7 +955,9 @@ void launch_conv_tc(const ConvTcParams &p, const ConvTcPlan &q, cudaStream_t str
     t.tiles_w = q.tiles_w; t.tiles_h = q.tiles_h;
     t.bn = q.bn; t.cchunks = q.cchunks; t.k_iters = q.k_iters; t.split_k = q.split_k; t.stages = q.stages;
     t.flat = q.flat_1x1;
-    t.a_bytes = q.box_w * q.box_h * q.box_n * kChunk * 4;
+    t.a_bytes = q.box_w * q.box_h * q.box_n * kRowBytes;
+    t.bf16 = q.bf16;
+    t.chunk = q.bf16 ? 64 : 32;
     int cols = 32;
     while (cols < q.bn) cols *= 2;
     t.tmem_cols = cols;

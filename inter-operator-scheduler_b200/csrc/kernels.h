@@ -1,8 +1,9 @@
 // Device-side operator library: parameter blocks and host launchers.
 //
-// Activations live in HBM as NHWC float32 with a per-pixel pitch (floats) that is a multiple of 4,
-// so that a pixel row starts on a 16-byte boundary.  A TensorRef addresses a channel window of such
-// a buffer: element (n, h, w, c) is ptr[((n*H + h)*W + w)*pitch + c].  Channel slices, concat
+// Activations live in HBM as NHWC, float32 or (precision "bf16") bfloat16, with a per-pixel pitch
+// in elements that keeps every pixel row on a 16-byte boundary (a multiple of 4 floats / 8 bf16).
+// A TensorRef addresses a channel window of such a buffer: element (n, h, w, c) is
+// ptr[((n*H + h)*W + w)*pitch + c] in units of its element size.  Channel slices, concat
 // members and whole tensors are all TensorRefs, which is what lets a producer write straight into
 // its slot of a consumer's concat buffer and a consumer read a slice of a merged convolution
 // without the copy kernels of the reference (src/ios/ops.cu:6-24).
@@ -13,22 +14,35 @@
 namespace ios {
 
 struct TensorRef {
-    float *ptr = nullptr;
+    void *ptr = nullptr;
     int N = 0, H = 0, W = 0, C = 0;
-    int pitch = 0;   // floats between consecutive pixels
+    int pitch = 0;   // elements between consecutive pixels
+    int esize = 4;   // bytes per element: 4 = float32, 2 = bfloat16
 
     __host__ __device__ long pixels() const { return long(N) * H * W; }
-    bool vec4() const { return (C % 4 == 0) && (pitch % 4 == 0) && ((reinterpret_cast<uintptr_t>(ptr) & 15) == 0); }
+    // may the kernels move 4 elements per access?
+    bool vec4() const {
+        return (C % 4 == 0) && (pitch % 4 == 0) && ((reinterpret_cast<uintptr_t>(ptr) % size_t(4 * esize)) == 0);
+    }
+    // the same tensor seen from `channels` further along the channel axis
+    TensorRef shifted(int channels) const {
+        TensorRef t = *this;
+        t.ptr = static_cast<char *>(ptr) + size_t(channels) * esize;
+        return t;
+    }
+    template <class T>
+    __host__ __device__ T *as() const { return static_cast<T *>(ptr); }
 };
 
 constexpr int kMaxSumInputs = 8;
 
 // out = act(in_0 (+|*) in_1 ... in_{k-1}); k = 1 with act = identity is a strided copy.
 struct SumActParams {
-    const float *in[kMaxSumInputs];
+    const void *in[kMaxSumInputs];
     int in_pitch[kMaxSumInputs];
-    float *out;
+    void *out;
     int out_pitch;
+    int esize;       // element size of every operand (4 or 2)
     int k;
     int C;
     long pixels;
@@ -50,8 +64,9 @@ void launch_pool(const PoolParams &p, cudaStream_t stream);
 void launch_nchw_to_nhwc(const float *src, TensorRef dst, bool round_tf32, cudaStream_t stream);
 void launch_nhwc_to_nchw(TensorRef src, float *dst, cudaStream_t stream);
 
-// Deterministic pseudo-random fill in [-scale, scale] (synthetic weights / inputs for timing runs).
-void launch_fill(float *dst, long count, uint32_t seed, float scale, cudaStream_t stream);
+// Deterministic pseudo-random fill in [-scale, scale] (synthetic weights / inputs for timing runs);
+// esize 4 writes float32, esize 2 bfloat16.
+void launch_fill(void *dst, long count, uint32_t seed, float scale, cudaStream_t stream, int esize = 4);
 
 // ---- convolution ---------------------------------------------------------------------------
 struct ConvGeom {
@@ -76,8 +91,9 @@ void launch_conv_direct(const ConvDirectParams &p, cudaStream_t stream);
 void launch_conv_depthwise(const ConvDirectParams &p, cudaStream_t stream);
 
 // Tensor-core implicit-GEMM convolution (tcgen05 + TMEM + TMA), groups == 1.
-// Packed weights: [planes][Cout_pad][taps][cchunks*32] float32, zero padded; plane 0 holds the
-// weights rounded to TF32, plane 1 (three-pass mode only) the TF32-rounded residuals.
+// Packed weights: [planes][Cout_pad][taps][cchunks*chunk], zero padded, chunk = one 128-byte row
+// (32 float32 or 64 bfloat16); plane 0 holds the weights rounded to TF32 (or bfloat16), plane 1
+// (three-pass mode only) the TF32-rounded residuals.
 struct ConvTcPlan {
     // tile geometry chosen by conv_tc_plan()
     int box_w, box_h, box_n;       // output pixels covered by one M tile along W, H, batch
@@ -93,6 +109,7 @@ struct ConvTcPlan {
     int tma_store;                 // 1: the output window is 16-byte aligned, the epilogue uses bulk tensor stores
     int pdl;                       // 1: launch with programmatic stream serialization
     int cluster;                   // 1: a K split of up to 8 is reduced inside a thread-block cluster (no workspace)
+    int bf16;                      // 1: bfloat16 operands and activations (kind::f16), 0: float32 storage (kind::tf32)
     size_t smem_bytes;
     size_t workspace_bytes;        // split-K partial tiles (0 when split_k == 1)
     size_t counter_bytes;          // split-K arrival counters
@@ -103,7 +120,7 @@ struct ConvTcPlan {
 };
 struct ConvTcParams {
     TensorRef in, out;
-    const float *weight_packed;
+    const void *weight_packed;
     const float *bias;
     float *workspace;
     unsigned int *counters;
@@ -116,7 +133,7 @@ bool conv_tc_supported(const TensorRef &in, const ConvGeom &g);
 // Chooses the tiling; sm_count and concurrency_hint (groups running beside this one) steer bn and
 // split_k.  three_pass selects the fp32-grade 3xTF32 product.  Does not touch the device.
 void conv_tc_choose(const ConvGeom &g, int sm_count, int concurrency_hint, bool three_pass, ConvTcPlan *plan,
-                    int force_bn = 0);
+                    int force_bn = 0, bool bf16 = false);
 // Overrides the K split (recomputes pipeline depth, shared memory and workspace sizes).
 void conv_tc_set_split(ConvTcPlan *plan, int split);
 // Encodes the two tensor maps (needs final device addresses).  Returns a CUDA driver error text or nullptr.
@@ -127,9 +144,9 @@ const char *conv_tc_encode_dense_weights(const ConvTcParams &p, ConvTcPlan *plan
 // Raises the kernel's dynamic shared-memory limit; call once per device before the first launch.
 cudaError_t conv_tc_prepare();
 void launch_conv_tc(const ConvTcParams &p, const ConvTcPlan &plan, cudaStream_t stream);
-size_t conv_tc_packed_floats(const ConvGeom &g, const ConvTcPlan &plan);
-// Host-side packing of OIHW weights into the tensor-core layout (rounds to TF32, nearest even).
-void conv_tc_pack_weights(const float *oihw, const ConvGeom &g, const ConvTcPlan &plan, float *packed);
+size_t conv_tc_packed_bytes(const ConvGeom &g, const ConvTcPlan &plan);
+// Host-side packing of OIHW weights into the tensor-core layout (rounds to TF32 or bfloat16, nearest even).
+void conv_tc_pack_weights(const float *oihw, const ConvGeom &g, const ConvTcPlan &plan, void *packed);
 // Host-side packing for the CUDA-core kernels.
 void conv_direct_pack_weights(const float *oihw, const ConvGeom &g, float *packed);   // [tap][Cin/g][Cout]
 void conv_depthwise_pack_weights(const float *oihw, const ConvGeom &g, float *packed); // [tap][C]

@@ -96,6 +96,7 @@ extern "C" int ios_pointwise_conv_static_scratch(const float *x, const float *w,
 
     ConvTcParams p = {};
     p.in.ptr = const_cast<float *>(x);
+    p.in.esize = p.out.esize = 4;
     p.in.N = 1; p.in.H = 1; p.in.W = pixels; p.in.C = cin; p.in.pitch = cin;
     p.out.ptr = y;
     p.out.N = 1; p.out.H = 1; p.out.W = pixels; p.out.C = cout; p.out.pitch = cout;

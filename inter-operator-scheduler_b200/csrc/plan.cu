@@ -11,7 +11,7 @@ namespace {
 constexpr size_t kAlign = 256;
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
-int round4(int c) { return (c + 3) / 4 * 4; }
+int round_up(int c, int m) { return (c + m - 1) / m * m; }
 
 struct UserRef {
     int op;
@@ -39,6 +39,8 @@ public:
                 for (const ValueRef &v : term) users_[v.node].push_back({int(i), term.size() == 1});
 
         cursor_ = 0;
+        esize_ = plan_.options.bf16 ? 2 : 4;
+        per16_ = 16 / esize_;                      // elements per 16 bytes: pixel pitches are multiples of it
         plan_.error_flag_offset = alloc(kAlign);
         // split-K arrival counters: one zero-initialised region, size known from the dry pass
         plan_.zero_begin = alloc(dry_ ? 0 : plan_.zero_bytes);
@@ -49,8 +51,8 @@ public:
         size_t in_floats = 0;
         for (int idx : m_.placeholders) {
             const Op &op = m_.ops[idx];
-            const int pitch = round4(op.C);
-            const size_t off = alloc(size_t(m_.batch) * op.H * op.W * pitch * sizeof(float));
+            const int pitch = round_up(op.C, per16_);
+            const size_t off = alloc(size_t(m_.batch) * op.H * op.W * pitch * esize_);
             plan_.input_offsets.push_back(off);
             set_tensor(idx, window(off, op, pitch, 0, op.C));
             in_floats = std::max(in_floats, size_t(m_.batch) * op.C * op.H * op.W);
@@ -89,6 +91,7 @@ private:
     int sms_;
     size_t cursor_ = 0, counter_cursor_ = 0, counter_end_ = 0, counter_total_ = 0;
     int stage_ = 0, group_ = 0, width_ = 1;
+    int esize_ = 4, per16_ = 4;
     std::vector<bool> placed_, has_tensor_;
     std::vector<std::vector<UserRef>> users_;
     std::map<int, TensorRef> concat_in_;          // assembled-input buffer of multi-term Conv / Pool ops
@@ -105,7 +108,8 @@ private:
 
     TensorRef window(size_t off, const Op &op, int pitch, int c0, int c) const {
         TensorRef t;
-        t.ptr = at(off) + c0;
+        t.esize = esize_;
+        t.ptr = reinterpret_cast<char *>(at(off)) + size_t(c0) * esize_;
         t.N = m_.batch;
         t.H = op.H;
         t.W = op.W;
@@ -113,8 +117,8 @@ private:
         t.pitch = pitch;
         return t;
     }
-    static TensorRef slice(TensorRef t, int begin, int end) {
-        t.ptr += begin;
+    static TensorRef slice(const TensorRef &whole, int begin, int end) {
+        TensorRef t = whole.shifted(begin);
         t.C = end - begin;
         return t;
     }
@@ -123,21 +127,22 @@ private:
         has_tensor_[idx] = true;
     }
     TensorRef fresh(const Op &op, int channels) {
-        const int pitch = round4(channels);
-        const size_t off = alloc(size_t(m_.batch) * op.H * op.W * pitch * sizeof(float));
+        const int pitch = round_up(channels, per16_);
+        const size_t off = alloc(size_t(m_.batch) * op.H * op.W * pitch * esize_);
         return window(off, op, pitch, 0, channels);
     }
 
     // ---- which convolutions will run on the tensor cores (by geometry; view alignment is checked later)
     bool tc_candidate(const Op &op) const {
-        return op.kind == OpKind::Conv && op.groups == 1 && plan_.options.tf32 && plan_.options.allow_tc &&
+        return op.kind == OpKind::Conv && op.groups == 1 && (plan_.options.tf32 || plan_.options.bf16) && plan_.options.allow_tc &&
                op.sh <= 8 && op.sw <= 8;
     }
     // Round a tensor to TF32 when it is stored?  Only if every reader is a tensor-core convolution
     // that takes it unchanged, and it is not the tensor handed back to the caller.
     // Identity operators hand their single-value terms on unchanged, so the test looks through them.
     bool rounds_for_consumers(int idx) const {
-        if (!plan_.options.tf32 || plan_.options.three_pass || idx == m_.output || users_[idx].empty()) return false;
+        if (!plan_.options.tf32 || plan_.options.three_pass || plan_.options.bf16 || idx == m_.output || users_[idx].empty())
+            return false;
         for (const UserRef &u : users_[idx]) {
             const Op &c = m_.ops[u.op];
             if (!u.sole_value || !c.scheduled) return false;
@@ -188,7 +193,7 @@ private:
                     const ValueRef &v = term[0];
                     const Op &p = m_.ops[v.node];
                     const bool whole = v.begin == 0 && v.end == p.C;
-                    const bool aligned = (c_off % 4 == 0 && (reinterpret_cast<uintptr_t>(buf.ptr) & 15) == 0) ||
+                    const bool aligned = (c_off % per16_ == 0 && (reinterpret_cast<uintptr_t>(buf.ptr) & 15) == 0) ||
                                          users_[v.node].size() == 1;
                     if (whole && !has_tensor_[v.node] && placeable_producer(p) && aligned) {
                         set_tensor(v.node, slice(buf, c_off, c_off + tc));
@@ -240,6 +245,7 @@ private:
             p.k = k;
             p.out = dst.ptr;
             p.out_pitch = dst.pitch;
+            p.esize = esize_;
             p.C = dst.C;
             p.pixels = dst.pixels();
             p.act = last ? int(act) : 0;
@@ -380,18 +386,18 @@ private:
         const bool depthwise = op.groups > 1 && op.groups == op.inC && op.groups == op.C;
         if (depthwise) {
             slot.impl = StepKind::ConvDepthwise;
-            slot.weight_floats = size_t(op.kh) * op.kw * op.C;
+            slot.weight_bytes = size_t(op.kh) * op.kw * op.C * sizeof(float);
         } else if (tc_wanted && conv_tc_supported(in, g)) {
             slot.impl = StepKind::ConvTc;
-            conv_tc_choose(g, sms_, width_, plan_.options.three_pass, &slot.tcplan, plan_.options.force_bn);
+            conv_tc_choose(g, sms_, width_, plan_.options.three_pass, &slot.tcplan, plan_.options.force_bn, plan_.options.bf16);
             if (plan_.options.force_split_k > 0) conv_tc_set_split(&slot.tcplan, plan_.options.force_split_k);
             slot.tcplan.pdl = plan_.options.pdl ? 1 : 0;
-            slot.weight_floats = conv_tc_packed_floats(g, slot.tcplan);
+            slot.weight_bytes = conv_tc_packed_bytes(g, slot.tcplan);
         } else {
             slot.impl = StepKind::ConvDirect;
-            slot.weight_floats = size_t(op.kh) * op.kw * (op.inC / op.groups) * op.C;
+            slot.weight_bytes = size_t(op.kh) * op.kw * (op.inC / op.groups) * op.C * sizeof(float);
         }
-        slot.weight_offset = alloc(slot.weight_floats * sizeof(float));
+        slot.weight_offset = alloc(slot.weight_bytes);
         slot.bias_offset = alloc(size_t(op.C) * sizeof(float));
 
         Step &s = push(slot.impl, idx);

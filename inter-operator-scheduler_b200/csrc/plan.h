@@ -24,6 +24,7 @@ namespace ios {
 struct Options {
     bool tf32 = true;           // precision: tensor cores (tf32x3 / tf32) or CUDA cores (fp32)
     bool three_pass = true;     // tf32x3: operands split into TF32 value + residual, fp32-grade products
+    bool bf16 = false;          // precision "bf16": bfloat16 activations and weights, fp32 accumulation
     bool pdl = true;            // programmatic dependent launch between consecutive convolution kernels
     bool stage_barriers = true; // join all groups after every stage (the reference's semantics); false: data-flow edges
     bool use_graph = true;      // executor: CUDA graph or plain streams
@@ -52,7 +53,7 @@ struct ConvSlot {               // where a convolution's parameters live in the 
     StepKind impl;
     ConvGeom geom;
     ConvTcPlan tcplan;
-    size_t weight_offset, weight_floats;
+    size_t weight_offset, weight_bytes;
     size_t bias_offset;
 };
 

@@ -324,9 +324,11 @@ void load_parameters(const Plan &plan, char *base, const HostWeights *host, cuda
         float *w_dev = reinterpret_cast<float *>(base + slot.weight_offset);
         float *b_dev = reinterpret_cast<float *>(base + slot.bias_offset);
         const int fan_in = slot.geom.kh * slot.geom.kw * (slot.geom.Cin / slot.geom.groups);
+        const bool bf16_weights = slot.impl == StepKind::ConvTc && slot.tcplan.bf16;
         if (!host) {
             // timing run: bounded pseudo-random parameters keep the activations finite
-            launch_fill(w_dev, long(slot.weight_floats), seed++, std::sqrt(3.0f / float(fan_in)), stream);
+            launch_fill(w_dev, long(slot.weight_bytes / (bf16_weights ? 2 : 4)), seed++, std::sqrt(3.0f / float(fan_in)), stream,
+                        bf16_weights ? 2 : 4);
             launch_fill(b_dev, slot.geom.Cout, seed++, 0.05f, stream);
             continue;
         }
@@ -338,13 +340,13 @@ void load_parameters(const Plan &plan, char *base, const HostWeights *host, cuda
             }
         if (found < 0 || !host->filters[found] || !host->biases[found])
             throw MissingWeights("convolution '" + op.name + "' was given no weight or bias");
-        packed.resize(slot.weight_floats);
+        packed.resize((slot.weight_bytes + 3) / 4);
         switch (slot.impl) {
             case StepKind::ConvTc: conv_tc_pack_weights(host->filters[found], slot.geom, slot.tcplan, packed.data()); break;
             case StepKind::ConvDepthwise: conv_depthwise_pack_weights(host->filters[found], slot.geom, packed.data()); break;
             default: conv_direct_pack_weights(host->filters[found], slot.geom, packed.data()); break;
         }
-        CUDA_OK(cudaMemcpyAsync(w_dev, packed.data(), slot.weight_floats * sizeof(float), cudaMemcpyHostToDevice, stream));
+        CUDA_OK(cudaMemcpyAsync(w_dev, packed.data(), slot.weight_bytes, cudaMemcpyHostToDevice, stream));
         CUDA_OK(cudaStreamSynchronize(stream));   // `packed` is reused for the next convolution
         CUDA_OK(cudaMemcpyAsync(b_dev, host->biases[found], size_t(slot.geom.Cout) * sizeof(float), cudaMemcpyHostToDevice, stream));
     }
@@ -367,7 +369,7 @@ void fill_inputs(DeviceContext &ctx, const Plan &plan, char *base) {
     uint32_t seed = 1000;
     for (size_t i = 0; i < plan.model.placeholders.size(); ++i) {
         const TensorRef &t = plan.tensors[plan.model.placeholders[i]];
-        launch_fill(reinterpret_cast<float *>(base + plan.input_offsets[i]), t.pixels() * t.pitch, seed++, 1.0f, ctx.streams[0]);
+        launch_fill(base + plan.input_offsets[i], t.pixels() * t.pitch, seed++, 1.0f, ctx.streams[0], t.esize);
     }
 }
 
@@ -637,8 +639,9 @@ int ios_set_option(const char *key, const char *value) {
         if (!key || !value) throw ArgumentError("key and value must not be NULL");
         std::lock_guard<std::mutex> lock(g_mutex);
         const std::string k = key, v = value;
-        if (k == "precision" && (v == "tf32x3" || v == "tf32" || v == "fp32")) {
-            g_options.tf32 = v != "fp32";
+        if (k == "precision" && (v == "tf32x3" || v == "tf32" || v == "fp32" || v == "bf16")) {
+            g_options.bf16 = v == "bf16";
+            g_options.tf32 = v == "tf32x3" || v == "tf32";
             g_options.three_pass = v == "tf32x3";
         } else if (k == "pdl" && (v == "0" || v == "1")) g_options.pdl = v == "1";
         else if (k == "executor" && (v == "graph" || v == "streams")) g_options.use_graph = v == "graph";
@@ -656,7 +659,7 @@ int ios_get_option(const char *key, char *value, int capacity) {
         if (!key || !value || capacity <= 0) throw ArgumentError("key and value must not be NULL");
         const std::string k = key;
         std::string v;
-        if (k == "precision") v = !g_options.tf32 ? "fp32" : g_options.three_pass ? "tf32x3" : "tf32";
+        if (k == "precision") v = g_options.bf16 ? "bf16" : !g_options.tf32 ? "fp32" : g_options.three_pass ? "tf32x3" : "tf32";
         else if (k == "pdl") v = g_options.pdl ? "1" : "0";
         else if (k == "stage_barriers") v = g_options.stage_barriers ? "1" : "0";
         else if (k == "executor") v = g_options.use_graph ? "graph" : "streams";
@@ -866,15 +869,15 @@ int ios_engine_profile(ios_engine *engine, int iters, int capacity, int *count, 
             step_kind[i] = int(s.kind);
             switch (s.kind) {
                 case StepKind::SumAct:
-                    step_work[i] = double(s.sum.k + 1) * double(s.sum.pixels) * s.sum.C * 4.0;
+                    step_work[i] = double(s.sum.k + 1) * double(s.sum.pixels) * s.sum.C * double(s.sum.esize);
                     break;
                 case StepKind::Pool:
-                    step_work[i] = (double(s.pool.in.pixels()) + double(s.pool.out.pixels())) * s.pool.in.C * 4.0;
+                    step_work[i] = (double(s.pool.in.pixels()) + double(s.pool.out.pixels())) * s.pool.in.C * double(s.pool.in.esize);
                     break;
                 case StepKind::ConvDepthwise: {
                     const ConvGeom &g = s.direct.g;
-                    step_work[i] = (double(g.N) * g.H * g.W * g.Cin + double(g.N) * g.OH * g.OW * g.Cout +
-                                    double(g.kh) * g.kw * g.Cout) * 4.0;
+                    step_work[i] = (double(g.N) * g.H * g.W * g.Cin + double(g.N) * g.OH * g.OW * g.Cout) * double(s.direct.in.esize) +
+                                   double(g.kh) * g.kw * g.Cout * 4.0;
                     break;
                 }
                 default: {
@@ -903,7 +906,7 @@ int ios_engine_describe(ios_engine *engine, char *text, int capacity) {
             }
         }
         size_t weight_bytes = 0;
-        for (const ConvSlot &c : p.convs) weight_bytes += (c.weight_floats + c.geom.Cout) * sizeof(float);
+        for (const ConvSlot &c : p.convs) weight_bytes += c.weight_bytes + c.geom.Cout * sizeof(float);
         const Op &out = p.model.ops[p.model.output];
         std::snprintf(text, size_t(capacity),
                       "{\"launches\": %d, \"conv_tc\": %d, \"conv_tc_split_k\": %d, \"conv_direct\": %d, \"conv_depthwise\": %d, "
@@ -913,7 +916,7 @@ int ios_engine_describe(ios_engine *engine, char *text, int capacity) {
                       p.launches_per_forward, n_tc, n_split, n_direct, n_dw, n_sum, n_pool, p.model.stages.size(), e.bytes,
                       p.workspace_bytes, weight_bytes, p.model.conv_flops(), p.model.batch, out.C, out.H, out.W,
                       p.options.use_graph ? "graph" : "streams",
-                      !p.options.tf32 ? "fp32" : p.options.three_pass ? "tf32x3" : "tf32");
+                      p.options.bf16 ? "bf16" : !p.options.tf32 ? "fp32" : p.options.three_pass ? "tf32x3" : "tf32");
     });
 }
 
@@ -921,7 +924,7 @@ int ios_conv2d(const float *x, const float *w, const float *bias, float *y, int 
                int kh, int kw, int sh, int sw, int ph, int pw, int groups, int act, int impl) {
     return guarded([&]() {
         if (!x || !w || !y) throw ArgumentError("x, w and y must not be NULL");
-        if (n <= 0 || cin <= 0 || h <= 0 || wdt <= 0 || cout <= 0 || groups <= 0 || act < 0 || act > 3 || impl < 0 || impl > 3)
+        if (n <= 0 || cin <= 0 || h <= 0 || wdt <= 0 || cout <= 0 || groups <= 0 || act < 0 || act > 3 || impl < 0 || impl > 4)
             throw ArgumentError("bad convolution arguments");
         // a one-operator graph drives exactly the code path a scheduled convolution takes
         static const char *acts[] = {"identity", "relu", "sigmoid", "tanh"};
@@ -945,8 +948,9 @@ int ios_conv2d(const float *x, const float *w, const float *bias, float *y, int 
             std::lock_guard<std::mutex> lock(g_mutex);
             saved = g_options;
             if (impl == 1) g_options.allow_tc = false;
-            if (impl == 2) { g_options.allow_tc = true; g_options.tf32 = true; }
-            if (impl == 3) { g_options.allow_tc = true; g_options.tf32 = true; g_options.three_pass = false; }
+            if (impl == 2) { g_options.allow_tc = true; if (!g_options.bf16) g_options.tf32 = true; }
+            if (impl == 3) { g_options.allow_tc = true; g_options.tf32 = true; g_options.three_pass = false; g_options.bf16 = false; }
+            if (impl == 4) { g_options.allow_tc = true; g_options.bf16 = true; g_options.tf32 = false; }
         }
         try {
             run_inference(model, x, hw, y);

@@ -88,7 +88,7 @@ def _check(status):
 
 
 def set_option(key: str, value: str):
-    """Run-time switches: precision tf32x3|tf32|fp32, executor graph|streams, conv auto|direct, pdl 0|1."""
+    """Run-time switches: precision tf32x3|tf32|bf16|fp32, executor graph|streams, conv auto|direct, pdl 0|1."""
     _check(_library().ios_set_option(key.encode(), str(value).encode()))
 
 
@@ -190,7 +190,7 @@ def conv2d(x: np.ndarray, weight: np.ndarray, bias=None, stride=(1, 1), padding=
     """
     One convolution through the runtime (testing aid).  x: NCHW, weight: OIHW.  impl: 'auto',
     'direct' (CUDA cores), 'tensor' (tensor cores, current precision option), 'tensor1' (tensor
-    cores, single-pass TF32).
+    cores, single-pass TF32), 'bf16' (tensor cores, bfloat16 operands and activations).
     """
     x = np.ascontiguousarray(x, dtype=np.float32)
     weight = np.ascontiguousarray(weight, dtype=np.float32)
@@ -204,7 +204,7 @@ def conv2d(x: np.ndarray, weight: np.ndarray, bias=None, stride=(1, 1), padding=
         x.ctypes.data_as(ctypes.c_void_p), weight.ctypes.data_as(ctypes.c_void_p),
         None if b is None else b.ctypes.data_as(ctypes.c_void_p), y.ctypes.data_as(ctypes.c_void_p),
         n, cin, h, w, cout, kh, kw, stride[0], stride[1], padding[0], padding[1], groups,
-        ['identity', 'relu', 'sigmoid', 'tanh'].index(act), ['auto', 'direct', 'tensor', 'tensor1'].index(impl)))
+        ['identity', 'relu', 'sigmoid', 'tanh'].index(act), ['auto', 'direct', 'tensor', 'tensor1', 'bf16'].index(impl)))
     return y
 
 

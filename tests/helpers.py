@@ -14,6 +14,7 @@ GOLDEN_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), 'golden')
 # tolerances of the parity contract: max|y - ref| / max|ref|
 TOL_TF32 = 1e-3     # TF32 products, fp32 accumulate
 TOL_FP32 = 2e-5     # CUDA-core fp32 path against an fp32/fp64 oracle
+TOL_BF16 = 2e-2     # bfloat16 storage and products, fp32 accumulate
 
 
 class Golden:

@@ -17,7 +17,7 @@ import pytest
 import ios
 import ios_oracle as oracle
 from ios.contrib import ios_runtime as rt
-from helpers import (GOLDEN_DIR, TOL_FP32, TOL_TF32, load_ref_schedule, sample_block, seeded, set_weights,
+from helpers import (GOLDEN_DIR, TOL_BF16, TOL_FP32, TOL_TF32, load_ref_schedule, sample_block, seeded, set_weights,
                      weights_of)
 
 pytestmark = pytest.mark.gpu
@@ -68,6 +68,7 @@ TC_SHAPES = [
 def test_conv_tensor_core_vs_oracle(shape):
     assert _conv_case(shape, 'tensor') <= TOL_FP32          # three-pass TF32: fp32-grade
     assert _conv_case(shape, 'tensor1') <= TOL_TF32         # single-pass TF32
+    assert _conv_case(shape, 'bf16') <= TOL_BF16            # bfloat16 operands
 
 
 @pytest.mark.parametrize('shape', TC_SHAPES[:6] + [
@@ -138,6 +139,29 @@ def test_networks_match_reference_outputs(golden, case, model, law, wseed, xseed
     x = oracle.normal_input(config, batch, xseed)
     y = rt.graph_inference(graph, batch, x)
     golden.expect(case, y, TOL_TF32)
+
+
+@pytest.mark.parametrize('case,model,batch,law,wseed,xseed', [
+    ('sample_block', 'sample_block', 1, 'he', 0, 0), ('inception_v3', 'inception_v3', 1, 'he', 0, 0),
+    ('inception_v3_uniform_b2', 'inception_v3', 2, 'uniform', 1, 1), ('squeezenet', 'squeezenet', 1, 'he', 0, 0),
+    ('randwire_small', 'randwire_small', 1, 'he', 0, 0)])
+def test_networks_in_bfloat16(golden, case, model, batch, law, wseed, xseed):
+    """precision=bf16: bfloat16 storage and products, fp32 accumulation; the bar is 2e-2."""
+    rt.set_option('precision', 'bf16')
+    graph = sample_block() if model == 'sample_block' else getattr(ios.models, model)()
+    graph.sequential_schedule()
+    config, weights = seeded(graph, wseed, law)
+    y = rt.graph_inference(graph, batch, oracle.normal_input(config, batch, xseed))
+    golden.expect(case, y, TOL_BF16)
+
+
+def test_all_operator_types_in_bfloat16(golden):
+    with open(os.path.join(GOLDEN_DIR, 'all_ops.json')) as fh:
+        config = json.load(fh)
+    graph = ios.Graph.from_config(config)
+    set_weights(graph, oracle.uniform_weights(graph.export_config(), 3))
+    rt.set_option('precision', 'bf16')
+    golden.expect('all_ops_b3', rt.graph_inference(graph, 3, oracle.normal_input(config, 3, 4)), TOL_BF16)
 
 
 def test_single_pass_tf32_error_growth(golden):
