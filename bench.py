@@ -281,12 +281,19 @@ def run_ours(args):
         slot['work'] += work
     total_ms = sum(v['ms'] for v in by_kind.values())
     conv = by_kind.get('conv_tc', {'launches': 0, 'ms': 0.0, 'work': 0.0})
-    tf32_peak = peaks['bf16_tflops'] / 2.0
+    precision = rt.get_option('precision')
+    if precision == 'bf16':
+        tensor_peak = peaks['bf16_tflops']
+        peak_note = f'{peak_kind} bf16 burst (cuBLAS bf16 GEMM)'
+    else:
+        tensor_peak = peaks['bf16_tflops'] / 2.0
+        peak_note = f'{peak_kind} bf16 burst / 2 (dense TF32 is half the bf16 rate; not measured separately)'
+    tf32_peak = tensor_peak
     achieved = conv['work'] / (conv['ms'] * 1e-3) / 1e12 if conv['ms'] > 0 else 0.0
     roofline = {
         'bound': 'tensor', 'kernel': 'conv_tc_kernel', 'achieved': round(achieved, 3), 'peak': tf32_peak,
         'unit': 'TFLOP/s', 'frac': round(achieved / tf32_peak, 5),
-        'peak_source': f'{peak_kind} bf16 burst / 2 (dense TF32 is half the bf16 rate; not measured separately)',
+        'peak_source': peak_note,
         'traffic': None,
         'launches_per_step': conv['launches'], 'avg_launch_us': round(1e3 * conv['ms'] / max(1, conv['launches']), 3),
         'flops_per_step': conv['work'],
@@ -308,11 +315,16 @@ def run_ours(args):
     line = {
         'metric': METRIC, 'value': round(value, 2), 'unit': 'images/s', 'n_gpus': ranks.world, 'steps': args.steps,
         'warmup': args.warmup, 'ms_per_step': round(ms_per_step, 5), 'higher_is_better': True, 'scaling': 'weak',
-        'vs_baseline': None, 'dtype': 'tf32 (fp32 storage and accumulate)', 'data': 'synthetic',
+        'vs_baseline': None, 'data': 'synthetic',
+        'dtype': {'tf32x3': 'tf32 (fp32 storage, three TF32 products per multiply, fp32 accumulate)',
+                  'tf32': 'tf32 (fp32 storage, fp32 accumulate)', 'bf16': 'bf16 (fp32 accumulate)',
+                  'fp32': 'fp32 (CUDA cores)'}[precision],
         'config': {'workload': f'{args.model} batch {args.batch} per GPU, schedule {args.schedule} '
                                f'({info["stages"]} stages, {info["launches"]} launches)',
                    'global_batch': images, 'input': list(x.shape[1:]), 'parallelism':
-                       'single GPU' if ranks.world == 1 else f'{ranks.world} independent replicas (batch 1 does not shard)',
+                       'single GPU' if ranks.world == 1 else
+                       (f'{ranks.world} independent replicas (batch 1 does not shard)' if args.batch == 1 else
+                        f'global batch {images} sharded evenly, {args.batch} images per GPU, no collective on the data path'),
                    'l2': 'flushed between steps by a 256 MiB write', 'schedule_search_s': round(search_s, 1)},
         'e2e': {'value': round(e2e_value, 2), 'unit': 'images/s', 'ms_per_step': round(e2e_ms, 5),
                 'h2d_bytes_per_step': int(x.nbytes), 'd2h_bytes_per_step': int(y.nbytes)},
@@ -322,6 +334,9 @@ def run_ours(args):
         'clocks': clocks, 'roofline': roofline,
     }
 
+    if ranks.world == 1 and args.sweep and args.model == 'inception_v3' and args.batch == 1:
+        line['throughput_sweep'] = throughput_sweep(graph, peaks, peak_kind)
+
     if ranks.rank == 0:
         ref = oracle.run_config(base_config, weights, x)
         line['parity_max_rel_err'] = float(f'{oracle.max_rel_err(y, ref):.3e}')
@@ -330,6 +345,33 @@ def run_ours(args):
         print(json.dumps(line), flush=True)
     engine.close()
     ranks.finish()
+
+
+def throughput_sweep(graph, peaks, peak_kind):
+    """
+    Images/s of the same network at batch 16 / 64 / 256 on one GPU (greedy schedule, device-resident,
+    CUDA events over back-to-back replays; the activations alone exceed L2 from batch 16 on), for the
+    default precision and for bf16, each with its fraction of the measured tensor peak.
+    """
+    from ios.contrib import ios_runtime as rt
+    saved = rt.get_option('precision')
+    flops_per_image = 2.0 * sum(c.output_shape[0] * c.output_shape[1] * c.output_shape[2] * c.kernel[0] * c.kernel[1] *
+                                (c.input_shape[0] // c.groups) for c in graph.convs())
+    graph.greedy_schedule()
+    out = []
+    for precision in (saved, 'bf16'):
+        rt.set_option('precision', precision)
+        peak = peaks['bf16_tflops'] if precision == 'bf16' else peaks['bf16_tflops'] / 2.0
+        for batch in (16, 64, 256):
+            engine = rt.Engine(graph, batch, synthetic_weights=True)
+            engine.time(2)
+            ms = engine.time(5)
+            engine.close()
+            tflops = flops_per_image * batch / (ms * 1e-3) / 1e12
+            out.append({'precision': precision, 'batch': batch, 'ms': round(ms, 3), 'images_per_s': round(batch / ms * 1e3, 1),
+                        'conv_tflops': round(tflops, 1), 'frac_of_tensor_peak': round(tflops / peak, 4)})
+    rt.set_option('precision', saved)
+    return {'schedule': 'greedy', 'peak_source': f'{peak_kind} bf16 burst (bf16) or half of it (tf32)', 'points': out}
 
 
 def cpu_baseline(config, weights, x, batch, budget_s=15.0):
@@ -433,6 +475,8 @@ def main():
     ap.add_argument('--batch', type=int, default=1, help='images per GPU per step')
     ap.add_argument('--schedule', default='dp', choices=['dp', 'sequential', 'greedy'])
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--no-sweep', dest='sweep', action='store_false',
+                    help='skip the batch 16/64/256 throughput sweep that the default single-GPU run appends')
     ap.add_argument('--executor', default='graph', choices=['graph', 'streams'],
                     help='streams: plain launches instead of a CUDA graph (used for kernel-level profiling)')
     ap.add_argument('--precision', default=None, help='runtime precision option (default: the library default)')

@@ -806,6 +806,13 @@ void conv_tc_set_split(ConvTcPlan *plan, int split) {
     const int slab_channels = q.bf16 ? 64 : 32;
     const int per_split = ceil_div(q.k_iters, split);
     q.stages = std::max(2, std::min({8, per_split, (200 * 1024) / stage_bytes}));
+    // A grid of several waves runs faster with two CTAs per SM (one CTA's set-up and epilogue hide
+    // behind the other's K loop) than with one CTA and a deeper pipeline: keep such CTAs under half
+    // of an SM's shared memory, three stages if they fit.
+    if (long(base) * split > 148) {
+        const int fit = (108 * 1024) / stage_bytes;
+        q.stages = std::max(2, std::min(q.stages, std::max(fit, 2)));
+    }
     if (split > 8) q.cluster = 0;          // larger splits go through the global workspace
     // the store staging needs one 16 KiB slab per 32 output channels inside the pipeline buffers,
     // the cluster reduction one [128][bn + 4] float tile

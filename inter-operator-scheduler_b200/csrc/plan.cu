@@ -392,6 +392,15 @@ private:
             conv_tc_choose(g, sms_, width_, plan_.options.three_pass, &slot.tcplan, plan_.options.force_bn, plan_.options.bf16);
             if (plan_.options.force_split_k > 0) conv_tc_set_split(&slot.tcplan, plan_.options.force_split_k);
             slot.tcplan.pdl = plan_.options.pdl ? 1 : 0;
+            if (plan_.options.force_stages > 0) {           // testing aid: shallower pipeline
+                ConvTcPlan &q = slot.tcplan;
+                const size_t stage_bytes = (q.smem_bytes - 24 * q.stages - 64 - 1024) / q.stages;
+                const int stages = std::max(2, std::min(q.stages, plan_.options.force_stages));
+                if (size_t(stages) * stage_bytes >= size_t(128) * (q.bn + 4) * 4 && size_t(stages) * stage_bytes >= size_t(q.bn / 32) * 16384) {
+                    q.stages = stages;
+                    q.smem_bytes = size_t(stages) * stage_bytes + 24 * stages + 64 + 1024;
+                }
+            }
             slot.weight_bytes = conv_tc_packed_bytes(g, slot.tcplan);
         } else {
             slot.impl = StepKind::ConvDirect;

@@ -31,6 +31,7 @@ struct Options {
     bool allow_tc = true;       // conv: auto or direct
     int force_split_k = 0;      // testing aid: > 0 overrides the split-K choice
     int force_bn = 0;           // testing aid: > 0 overrides the output-channel tile width
+    int force_stages = 0;       // testing aid: > 0 caps the depth of the shared-memory pipeline
     bool timeline = false;      // diagnostics: the tensor-core kernel stamps its phases (see conv_tc.cu)
 };
 
