@@ -118,8 +118,10 @@ struct DeviceContext {
                 CUDA_OK(cudaMalloc(&arena, want));
             }
             arena_capacity = want;
-            // padding lanes of the NHWC buffers are never written: keep them finite
+            // padding lanes of the NHWC buffers are never written: keep them finite.  The memset runs on
+            // the legacy default stream, which the (non-blocking) working streams do not wait for.
             CUDA_OK(cudaMemset(arena, 0, want));
+            CUDA_OK(cudaDeviceSynchronize());
         }
         return arena;
     }
@@ -706,6 +708,7 @@ int ios_engine_create(const char *graph_json, int batch_size, int num_convs, cha
         e.bytes = e.plan.arena_bytes;
         CUDA_OK(cudaMalloc(&e.base, e.bytes));
         CUDA_OK(cudaMemset(e.base, 0, e.bytes));
+        CUDA_OK(cudaDeviceSynchronize());      // the working streams do not wait for the default stream
         bind_plan(ctx, &e.plan, e.base);
         cudaStream_t spine = ctx.streams[0];
         if (filter_data && bias_data && conv_names) {

@@ -217,6 +217,26 @@ def test_batched_inference_equals_per_image_inference():
     assert oracle.max_rel_err(y0, y[2:3]) <= 1e-4      # same function per image; tiling and K split differ with the batch
 
 
+def test_growing_the_arena_between_calls_keeps_results_correct():
+    """A later, larger plan re-allocates the process-wide arena; nothing of the new plan may be lost to its clearing."""
+    small = sample_block()
+    small.sequential_schedule()
+    config, weights = seeded(small, 0)
+    rt.graph_inference(small, 1, oracle.normal_input(config, 1, 0))
+    graph = ios.models.squeezenet()
+    graph.sequential_schedule()
+    config, weights = seeded(graph, 0)
+    for batch in (24, 96):                       # each one larger than anything this process has planned so far
+        x = oracle.normal_input(config, batch, 2)
+        y = rt.graph_inference(graph, batch, x)
+        assert oracle.max_rel_err(y, oracle.run_config(config, weights, x)) <= TOL_TF32
+        engine = rt.Engine(graph, batch)
+        try:
+            assert np.array_equal(engine.run(x), y)
+        finally:
+            engine.close()
+
+
 def test_results_are_deterministic_across_runs_and_executors():
     graph = sample_block()
     config, weights = seeded(graph, 0)
