@@ -46,6 +46,14 @@ __device__ __forceinline__ float4 load4(const __nv_bfloat16 *p) {
     const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.y));
     return make_float4(lo.x, lo.y, hi.x, hi.y);
 }
+// store the first `count` (1..4) of four values
+template <typename T>
+__device__ __forceinline__ void store_some(T *p, float4 v, int count) {
+    const float a[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        if (j < count) store1(p + j, a[j]);
+}
 __device__ __forceinline__ void store4(float *p, float4 v) { *reinterpret_cast<float4 *>(p) = v; }
 __device__ __forceinline__ void store4(__nv_bfloat16 *p, float4 v) {
     const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
@@ -65,7 +73,7 @@ inline int grid_for(long work, int threads, int max_blocks = 148 * 32) {
 // ---------------------------------------------------------------------------------------------
 template <typename T, bool kVec>
 __global__ void __launch_bounds__(kThreads) sum_act_kernel(const SumActParams p) {
-    const int lanes = kVec ? p.C / 4 : p.C;            // work items per pixel
+    const int lanes = kVec ? (p.C + 3) / 4 : p.C;      // work items per pixel
     const long total = p.pixels * lanes;
     T *out = static_cast<T *>(p.out);
     for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < total; i += long(gridDim.x) * blockDim.x) {
@@ -91,7 +99,8 @@ __global__ void __launch_bounds__(kThreads) sum_act_kernel(const SumActParams p)
             if (p.round_out) {
                 acc.x = to_tf32(acc.x); acc.y = to_tf32(acc.y); acc.z = to_tf32(acc.z); acc.w = to_tf32(acc.w);
             }
-            store4(out + pix * p.out_pitch + 4 * c, acc);
+            if (4 * c + 4 <= p.C) store4(out + pix * p.out_pitch + 4 * c, acc);
+            else store_some(out + pix * p.out_pitch + 4 * c, acc, p.C - 4 * c);
         } else {
             float acc = load1(static_cast<const T *>(p.in[0]) + pix * p.in_pitch[0] + c);
 #pragma unroll
@@ -110,7 +119,7 @@ __global__ void __launch_bounds__(kThreads) sum_act_kernel(const SumActParams p)
 // ---------------------------------------------------------------------------------------------
 template <typename T, bool kVec>
 __global__ void __launch_bounds__(kThreads) pool_kernel(const PoolParams p) {
-    const int lanes = kVec ? p.in.C / 4 : p.in.C;
+    const int lanes = kVec ? (p.in.C + 3) / 4 : p.in.C;
     const long total = p.out.pixels() * lanes;
     const float inv_window = 1.0f / float(p.kh * p.kw);   // padding counts (CUDNN_POOLING_AVERAGE_COUNT_INCLUDE_PADDING)
     const T *in = p.in.as<const T>();
@@ -152,8 +161,9 @@ __global__ void __launch_bounds__(kThreads) pool_kernel(const PoolParams p) {
             acc.x = to_tf32(acc.x); acc.y = to_tf32(acc.y); acc.z = to_tf32(acc.z); acc.w = to_tf32(acc.w);
         }
         T *dst = out + ((long(n) * p.out.H + oh) * p.out.W + ow) * p.out.pitch;
-        if (kVec) store4(dst + 4 * c, acc);
-        else store1(dst + c, acc.x);
+        if (!kVec) store1(dst + c, acc.x);
+        else if (4 * c + 4 <= p.in.C) store4(dst + 4 * c, acc);
+        else store_some(dst + 4 * c, acc, p.in.C - 4 * c);
     }
 }
 
@@ -238,7 +248,7 @@ __global__ void __launch_bounds__(kThreads) fill_kernel(T *dst, long count, uint
 
 void launch_sum_act(const SumActParams &p, bool vec4, cudaStream_t stream) {
     if (p.pixels <= 0 || p.C <= 0) return;
-    const int grid = grid_for(p.pixels * (vec4 ? p.C / 4 : p.C), kThreads);
+    const int grid = grid_for(p.pixels * (vec4 ? (p.C + 3) / 4 : p.C), kThreads);
     if (p.esize == 2) {
         if (vec4) sum_act_kernel<__nv_bfloat16, true><<<grid, kThreads, 0, stream>>>(p);
         else sum_act_kernel<__nv_bfloat16, false><<<grid, kThreads, 0, stream>>>(p);
@@ -258,7 +268,7 @@ void launch_pool(const PoolParams &p, cudaStream_t stream) {
         return;
     }
     const bool vec = p.in.vec4() && p.out.vec4();
-    const int grid = grid_for(p.out.pixels() * (vec ? p.in.C / 4 : p.in.C), kThreads);
+    const int grid = grid_for(p.out.pixels() * (vec ? (p.in.C + 3) / 4 : p.in.C), kThreads);
     if (bf16) {
         if (vec) pool_kernel<__nv_bfloat16, true><<<grid, kThreads, 0, stream>>>(p);
         else pool_kernel<__nv_bfloat16, false><<<grid, kThreads, 0, stream>>>(p);

@@ -107,7 +107,8 @@ __global__ void __launch_bounds__(128) conv_direct_kernel(const ConvDirectParams
 template <typename T, bool kVec>
 __global__ void __launch_bounds__(256) conv_depthwise_kernel(const ConvDirectParams p) {
     const ConvGeom &g = p.g;
-    const int lanes = kVec ? g.Cout / 4 : g.Cout;
+    const int lanes = kVec ? (g.Cout + 3) / 4 : g.Cout;   // the last group may be partial: stored element by element
+    const int wrow = (g.Cout + 3) / 4 * 4;                // packed weight rows are padded to a multiple of 4
     const long total = long(g.N) * g.OH * g.OW * lanes;
     for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < total; i += long(gridDim.x) * blockDim.x) {
         long pix = i / lanes;
@@ -124,7 +125,7 @@ __global__ void __launch_bounds__(256) conv_depthwise_kernel(const ConvDirectPar
                 const int w = ow * g.sw - g.pw + s;
                 if (w < 0 || w >= g.W) continue;
                 const T *x = p.in.as<const T>() + ((long(n) * g.H + h) * g.W + w) * p.in.pitch;
-                const float *wt = p.weight + long(r * g.kw + s) * g.Cout;
+                const float *wt = p.weight + long(r * g.kw + s) * wrow;
                 if (kVec) {
                     float4 xv = load4(x + 4 * c);
                     const float4 wv = *reinterpret_cast<const float4 *>(wt + 4 * c);
@@ -146,7 +147,14 @@ __global__ void __launch_bounds__(256) conv_depthwise_kernel(const ConvDirectPar
             float4 o;
             o.x = act_apply(acc.x + b.x, g.act); o.y = act_apply(acc.y + b.y, g.act);
             o.z = act_apply(acc.z + b.z, g.act); o.w = act_apply(acc.w + b.w, g.act);
-            store4(y + 4 * c, o);
+            if (4 * c + 4 <= g.Cout) {
+                store4(y + 4 * c, o);
+            } else {
+                const float a[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (4 * c + j < g.Cout) store1(y + 4 * c + j, a[j]);
+            }
         } else {
             store1(y + c, act_apply(acc.x + (p.bias ? p.bias[c] : 0.f), g.act));
         }
@@ -172,10 +180,10 @@ void launch_conv_direct(const ConvDirectParams &p, cudaStream_t stream) {
 
 void launch_conv_depthwise(const ConvDirectParams &p, cudaStream_t stream) {
     const ConvGeom &g = p.g;
-    const bool vec = p.in.vec4() && p.out.vec4() && (g.Cout % 4 == 0) &&
+    const bool vec = p.in.vec4() && p.out.vec4() &&
                      ((reinterpret_cast<uintptr_t>(p.weight) & 15) == 0) &&
                      (!p.bias || (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0);
-    const long work = long(g.N) * g.OH * g.OW * (vec ? g.Cout / 4 : g.Cout);
+    const long work = long(g.N) * g.OH * g.OW * (vec ? (g.Cout + 3) / 4 : g.Cout);
     if (p.in.esize == 2) {
         if (vec) conv_depthwise_kernel<__nv_bfloat16, true><<<blocks_for(work, 256), 256, 0, stream>>>(p);
         else conv_depthwise_kernel<__nv_bfloat16, false><<<blocks_for(work, 256), 256, 0, stream>>>(p);
@@ -195,8 +203,10 @@ void conv_direct_pack_weights(const float *oihw, const ConvGeom &g, float *packe
 
 void conv_depthwise_pack_weights(const float *oihw, const ConvGeom &g, float *packed) {
     const int taps = g.kh * g.kw;
+    const int wrow = (g.Cout + 3) / 4 * 4;
+    std::memset(packed, 0, size_t(taps) * wrow * sizeof(float));
     for (int o = 0; o < g.Cout; ++o)
-        for (int t = 0; t < taps; ++t) packed[size_t(t) * g.Cout + o] = oihw[size_t(o) * taps + t];
+        for (int t = 0; t < taps; ++t) packed[size_t(t) * wrow + o] = oihw[size_t(o) * taps + t];
 }
 
 }  // namespace ios

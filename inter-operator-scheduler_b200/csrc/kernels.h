@@ -20,9 +20,10 @@ struct TensorRef {
     int esize = 4;   // bytes per element: 4 = float32, 2 = bfloat16
 
     __host__ __device__ long pixels() const { return long(N) * H * W; }
-    // may the kernels move 4 elements per access?
+    // May the kernels move 4 elements per access?  C need not be a multiple of 4: the last group of a
+    // pixel is loaded whole (the bytes past the window belong to the same arena) and stored element by element.
     bool vec4() const {
-        return (C % 4 == 0) && (pitch % 4 == 0) && ((reinterpret_cast<uintptr_t>(ptr) % size_t(4 * esize)) == 0);
+        return (pitch % 4 == 0) && ((reinterpret_cast<uintptr_t>(ptr) % size_t(4 * esize)) == 0);
     }
     // the same tensor seen from `channels` further along the channel axis
     TensorRef shifted(int channels) const {
@@ -87,7 +88,7 @@ struct ConvDirectParams {
     ConvGeom g;
 };
 void launch_conv_direct(const ConvDirectParams &p, cudaStream_t stream);
-// Depthwise (groups == Cin == Cout).  Weights: [tap][C] float32.
+// Depthwise (groups == Cin == Cout).  Weights: [tap][C rounded up to 4] float32, zero padded.
 void launch_conv_depthwise(const ConvDirectParams &p, cudaStream_t stream);
 
 // Tensor-core implicit-GEMM convolution (tcgen05 + TMEM + TMA), groups == 1.
@@ -149,6 +150,6 @@ size_t conv_tc_packed_bytes(const ConvGeom &g, const ConvTcPlan &plan);
 void conv_tc_pack_weights(const float *oihw, const ConvGeom &g, const ConvTcPlan &plan, void *packed);
 // Host-side packing for the CUDA-core kernels.
 void conv_direct_pack_weights(const float *oihw, const ConvGeom &g, float *packed);   // [tap][Cin/g][Cout]
-void conv_depthwise_pack_weights(const float *oihw, const ConvGeom &g, float *packed); // [tap][C]
+void conv_depthwise_pack_weights(const float *oihw, const ConvGeom &g, float *packed); // [tap][C rounded up to 4]
 
 }  // namespace ios

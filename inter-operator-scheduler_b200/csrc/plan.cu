@@ -386,7 +386,7 @@ private:
         const bool depthwise = op.groups > 1 && op.groups == op.inC && op.groups == op.C;
         if (depthwise) {
             slot.impl = StepKind::ConvDepthwise;
-            slot.weight_bytes = size_t(op.kh) * op.kw * op.C * sizeof(float);
+            slot.weight_bytes = size_t(op.kh) * op.kw * ((op.C + 3) / 4 * 4) * sizeof(float);   // rows padded to 4
         } else if (tc_wanted && conv_tc_supported(in, g)) {
             slot.impl = StepKind::ConvTc;
             conv_tc_choose(g, sms_, width_, plan_.options.three_pass, &slot.tcplan, plan_.options.force_bn, plan_.options.bf16);
