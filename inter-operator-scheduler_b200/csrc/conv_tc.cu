@@ -348,31 +348,48 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     if (warp == 0) {
         if (lane == 0) {
             // ---------------- TMA producer ----------------
+            // Weights never depend on the previous kernel: the weight tiles of the first `stages` K steps
+            // are requested before the grid dependency is waited for, so that under programmatic dependent
+            // launch their latency hides behind the predecessor's tail.  Activations follow after the wait.
+            const int early = min(n_it, t.stages);
+#pragma unroll 1
+            for (int i = 0; i < early; ++i) {
+                const uint32_t stage = smem_base + uint32_t(i) * stage_bytes;
+                const uint32_t bar = full0 + 8u * i;
+                mbar_expect_tx(bar, uint32_t(t.a_bytes + passes * b_bytes));
+                tma_load_2d(stage + b_off, &tmap_b, bar, (it_begin + i) * t.chunk, cout0);
+                if (t.x3) tma_load_2d(stage + b_lo_off, &tmap_b, bar, (it_begin + i) * t.chunk, t.cout_pad + cout0);
+            }
             asm volatile("griddepcontrol.wait;" ::: "memory");
             bool ok = true;
             int issued = 0;
 #pragma unroll 1
             for (int i = 0; i < n_it && ok; ++i) {
                 const int s = i % t.stages;
-                if (i >= t.stages) ok = mbar_wait(empty0 + 8u * s, uint32_t((i / t.stages - 1) & 1), p.error_flag);
-                if (!ok) break;
                 const int it = it_begin + i;
-                const int tap = it / t.cchunks, cc = it - tap * t.cchunks;
-                const int r = tap / g.kw, sx = tap - r * g.kw;
                 const uint32_t stage = smem_base + uint32_t(s) * stage_bytes;
                 const uint32_t bar = full0 + 8u * s;
-                mbar_expect_tx(bar, uint32_t(t.a_bytes + passes * b_bytes));
+                if (i >= t.stages) {
+                    ok = mbar_wait(empty0 + 8u * s, uint32_t((i / t.stages - 1) & 1), p.error_flag);
+                    if (!ok) break;
+                    mbar_expect_tx(bar, uint32_t(t.a_bytes + passes * b_bytes));
+                    tma_load_2d(stage + b_off, &tmap_b, bar, it * t.chunk, cout0);
+                    if (t.x3) tma_load_2d(stage + b_lo_off, &tmap_b, bar, it * t.chunk, t.cout_pad + cout0);
+                }
+                const int tap = it / t.cchunks, cc = it - tap * t.cchunks;
+                const int r = tap / g.kw, sx = tap - r * g.kw;
                 if (t.flat) tma_load_4d(stage, &tmap_a, bar, cc * t.chunk, ow0, 0, 0);
                 else tma_load_4d(stage, &tmap_a, bar, cc * t.chunk, ow0 * g.sw - g.pw + sx, oh0 * g.sh - g.ph + r, n0);
-                tma_load_2d(stage + b_off, &tmap_b, bar, it * t.chunk, cout0);
-                if (t.x3) tma_load_2d(stage + b_lo_off, &tmap_b, bar, it * t.chunk, t.cout_pad + cout0);
                 if (i == 0) STAMP(2);
                 issued = i + 1;
             }
             if (!ok) {
                 atomicExch(p.error_flag, 1);
-                // drain: the loads already issued still land in this CTA's shared memory
-                for (int i = max(0, issued - t.stages); i < issued; ++i)
+                // drain: the loads already issued still land in this CTA's shared memory; a stage whose
+                // activation tile was never requested is completed by hand so that its barrier can fire
+                for (int i = issued; i < min(n_it, max(issued, early)); ++i)
+                    asm volatile("mbarrier.complete_tx.shared::cta.relaxed.cta.b64 [%0], %1;" ::"r"(full0 + 8u * (i % t.stages)), "r"(uint32_t(t.a_bytes)) : "memory");
+                for (int i = max(0, issued - t.stages); i < max(issued, early); ++i)
                     mbar_wait(full0 + 8u * (i % t.stages), uint32_t((i / t.stages) & 1), nullptr);
             }
         }
@@ -720,6 +737,7 @@ void conv_tc_choose(const ConvGeom &g, int sm_count, int concurrency_hint, bool 
                     bool bf16) {
     ConvTcPlan &q = *plan;
     q.bf16 = bf16 ? 1 : 0;
+    q.sm_count = sm_count;
     q.x3 = (three_pass && !bf16) ? 1 : 0;
     q.cluster = 1;
     const int chunk = bf16 ? 64 : 32;            // K elements per 128-byte row
@@ -812,7 +830,7 @@ void conv_tc_set_split(ConvTcPlan *plan, int split) {
     // A grid of several waves runs faster with two CTAs per SM (one CTA's set-up and epilogue hide
     // behind the other's K loop) than with one CTA and a deeper pipeline: keep such CTAs under half
     // of an SM's shared memory, three stages if they fit.
-    if (long(base) * split > 148) {
+    if (long(base) * split > (q.sm_count > 0 ? q.sm_count : 148)) {
         const int fit = (108 * 1024) / stage_bytes;
         q.stages = std::max(2, std::min(q.stages, std::max(fit, 2)));
     }

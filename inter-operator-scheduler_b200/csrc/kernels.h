@@ -111,6 +111,7 @@ struct ConvTcPlan {
     int pdl;                       // 1: launch with programmatic stream serialization
     int cluster;                   // 1: a K split of up to 8 is reduced inside a thread-block cluster (no workspace)
     int bf16;                      // 1: bfloat16 operands and activations (kind::f16), 0: float32 storage (kind::tf32)
+    int sm_count;                  // SMs of the device the tiling was chosen for
     size_t smem_bytes;
     size_t workspace_bytes;        // split-K partial tiles (0 when split_k == 1)
     size_t counter_bytes;          // split-K arrival counters

@@ -125,21 +125,6 @@ struct DeviceContext {
         }
         return arena;
     }
-    void release() {
-        if (device < 0) return;
-        cudaSetDevice(device);
-        for (cudaStream_t s : streams) cudaStreamDestroy(s);
-        for (cudaEvent_t e : events) cudaEventDestroy(e);
-        if (t_start) cudaEventDestroy(t_start);
-        if (t_end) cudaEventDestroy(t_end);
-        if (arena) cudaFree(arena);
-        streams.clear();
-        events.clear();
-        t_start = t_end = nullptr;
-        arena = nullptr;
-        arena_capacity = 0;
-        device = -1;
-    }
 };
 
 std::map<int, DeviceContext> g_contexts;   // one per device this process has used
