@@ -433,6 +433,7 @@ private:
             if (!dry_) {
                 const char *err = conv_tc_encode(s.tc, &slot.tcplan);
                 if (err) throw std::runtime_error(err);
+                if (plan_.options.no_bulk_store) slot.tcplan.tma_store = 0;   // testing aid
             }
             s.tcplan = slot.tcplan;
         } else {
