@@ -77,6 +77,13 @@ IOS_API const char *ios_last_error(void);
  *                  "streams" (group j of every stage is launched on stream j, events between stages)
  * key "conv":      "auto" (default), "direct" (never use the tensor-core kernel)
  * key "pdl":       "1" (default; consecutive convolution kernels use programmatic dependent launch), "0"
+ * key "stage_barriers": "1" (default; every stage joins all its groups, as the reference does), "0" (a group
+ *                  waits only for the groups that produced its inputs)
+ * Testing aids (each switches one mechanism of the tensor-core convolution off or pins one choice):
+ * "im2col" "1"/"0" (pixel tiles over the flattened pixel axis by im2col-mode loads / boxes of the image),
+ * "bulk_store" "1"/"0" (results leave through a bulk tensor store / straight from registers),
+ * "split_k", "bn", "stages" (a positive number overrides the K split, the output-channel tile width, the
+ * depth of the shared-memory pipeline; "0" = automatic), "timeline" "1"/"0" (phase stamps of one CTA).
  * Options apply to plans built afterwards on the calling process. */
 IOS_API int ios_set_option(const char *key, const char *value);
 IOS_API int ios_get_option(const char *key, char *value, int capacity);

@@ -51,7 +51,9 @@ constexpr uint64_t kWaitBudgetNs = 2000000000ull;  // 2 s per wait
 struct TileGeom {
     int box_w, box_h, box_n;
     int tiles_w, tiles_h;
-    int bn, cchunks, k_iters, split_k, stages, flat;
+    int bn, cchunks, k_iters, split_k, stages;
+    int flat;         // 1: a tile is box_w consecutive pixels of the flattened (n, oh, ow) axis
+    int im2col;       // 1: (flat only) the window has taps, padding or strides: im2col-mode loads
     int a_bytes;      // bytes one A load delivers
     int tmem_cols;
     int round_tf32;   // round the stored result to TF32 (the consumer is a single-pass tensor-core convolution)
@@ -106,6 +108,16 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void *tmap, uint
     asm volatile(
         "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
         ::"r"(dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+// im2col mode: the box is `pixels per column` consecutive positions of the filter window's corner,
+// walked along w, then h, then n inside the bounding box of the tensor map, starting at (w, h, n);
+// (off_w, off_h) selects the filter tap.  Positions outside the image read zeros (the padding).
+__device__ __forceinline__ void tma_load_im2col(uint32_t dst, const void *tmap, uint32_t bar, int c, int w, int h, int n,
+                                                uint32_t off_w, uint32_t off_h) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+        ::"r"(dst), "l"(tmap), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(uint16_t(off_w)), "h"(uint16_t(off_h))
         : "memory");
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void *tmap, uint32_t bar, int c0, int c1) {
@@ -301,9 +313,18 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
     // tile coordinates
     const int m_tile = blockIdx.x, n_tile = blockIdx.y, split = blockIdx.z;
-    int ow0 = 0, oh0 = 0, n0 = 0;
+    int ow0 = 0, oh0 = 0, n0 = 0, im_w = 0, im_h = 0;
     if (t.flat) {
         ow0 = m_tile * t.box_w;
+        if (t.im2col) {
+            // the tile's first pixel, as the corner of its filter window in input coordinates
+            const int per_image = g.OH * g.OW;
+            n0 = ow0 / per_image;
+            const int rem = ow0 - n0 * per_image;
+            oh0 = rem / g.OW;
+            im_w = (rem - oh0 * g.OW) * g.sw - g.pw;
+            im_h = oh0 * g.sh - g.ph;
+        }
     } else {
         const int tw = m_tile % t.tiles_w;
         const int rest = m_tile / t.tiles_w;
@@ -378,7 +399,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 }
                 const int tap = it / t.cchunks, cc = it - tap * t.cchunks;
                 const int r = tap / g.kw, sx = tap - r * g.kw;
-                if (t.flat) tma_load_4d(stage, &tmap_a, bar, cc * t.chunk, ow0, 0, 0);
+                if (t.im2col) tma_load_im2col(stage, &tmap_a, bar, cc * t.chunk, im_w, im_h, n0, uint32_t(sx), uint32_t(r));
+                else if (t.flat) tma_load_4d(stage, &tmap_a, bar, cc * t.chunk, ow0, 0, 0);
                 else tma_load_4d(stage, &tmap_a, bar, cc * t.chunk, ow0 * g.sw - g.pw + sx, oh0 * g.sh - g.ph + r, n0);
                 if (i == 0) STAMP(2);
                 issued = i + 1;
@@ -703,7 +725,30 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
+typedef CUresult (*EncodeIm2colFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const int *, const int *, cuuint32_t, cuuint32_t, const cuuint32_t *,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeIm2colFn encode_im2col_fn() {
+    static EncodeIm2colFn fn = nullptr;
+    if (fn) return fn;
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+        return nullptr;
+    fn = reinterpret_cast<EncodeIm2colFn>(sym);
+    return fn;
+}
+
 int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// Corners of the im2col bounding box along one axis: the filter window's first corner sits at -pad,
+// its last at (out - 1) * stride - pad, given relative to the last input element.
+void im2col_corners(int in, int out, int stride, int pad, int *lower, int *upper) {
+    *lower = -pad;
+    *upper = (out - 1) * stride - pad - (in - 1);
+}
 
 float tf32_round_host(float v) {
     uint32_t u;
@@ -734,7 +779,7 @@ bool conv_tc_supported(const TensorRef &in, const ConvGeom &g) {
 // over every pixel-tile shape, output-channel tile width and K split that the kernel supports.
 // It replaces the reference's run-time algorithm search (src/ios/ios_runtime.cu:150-205).
 void conv_tc_choose(const ConvGeom &g, int sm_count, int concurrency_hint, bool three_pass, ConvTcPlan *plan, int force_bn,
-                    bool bf16) {
+                    bool bf16, bool allow_im2col) {
     ConvTcPlan &q = *plan;
     q.bf16 = bf16 ? 1 : 0;
     q.sm_count = sm_count;
@@ -747,9 +792,19 @@ void conv_tc_choose(const ConvGeom &g, int sm_count, int concurrency_hint, bool 
     q.cchunks = ceil_div(g.Cin, chunk);
     q.k_iters = g.kh * g.kw * q.cchunks;
 
-    struct Shape { int box_w, box_h, box_n, tiles_w, tiles_h, tiles_n; };
+    struct Shape { int box_w, box_h, box_n, tiles_w, tiles_h, tiles_n, im2col; };
     std::vector<Shape> shapes;
-    if (flat) {
+    // A window with taps, padding or strides still tiles the flattened pixel axis when the TMA unit
+    // walks it in im2col mode; its bounding-box corners are 8-bit signed offsets.
+    bool im2col = allow_im2col && !flat && long(g.N) * g.OH * g.OW < (1l << 31) - kTileM;
+    if (im2col) {
+        int lo_w, up_w, lo_h, up_h;
+        im2col_corners(g.W, g.OW, g.sw, g.pw, &lo_w, &up_w);
+        im2col_corners(g.H, g.OH, g.sh, g.ph, &lo_h, &up_h);
+        for (int v : {lo_w, up_w, lo_h, up_h}) im2col = im2col && v >= -128 && v <= 127;
+        im2col = im2col && g.kw <= 65535 && g.kh <= 65535;
+    }
+    if (flat || im2col) {
         const long pixels = long(g.N) * g.OH * g.OW;
         const long tiles = (pixels + kTileM - 1) / kTileM;
         Shape sh;
@@ -757,6 +812,7 @@ void conv_tc_choose(const ConvGeom &g, int sm_count, int concurrency_hint, bool 
         sh.box_h = sh.box_n = 1;
         sh.tiles_w = int((pixels + sh.box_w - 1) / sh.box_w);
         sh.tiles_h = sh.tiles_n = 1;
+        sh.im2col = im2col ? 1 : 0;
         shapes.push_back(sh);
     } else {
         const int max_w = std::min(kTileM, 256 / g.sw);
@@ -771,6 +827,7 @@ void conv_tc_choose(const ConvGeom &g, int sm_count, int concurrency_hint, bool 
             const bool whole_image = sh.tiles_w == 1 && sh.box_h == g.OH;
             sh.box_n = whole_image ? std::min(g.N, std::max(1, kTileM / (g.OH * g.OW))) : 1;
             sh.tiles_n = ceil_div(g.N, sh.box_n);
+            sh.im2col = 0;
             shapes.push_back(sh);
         }
     }
@@ -812,6 +869,7 @@ void conv_tc_choose(const ConvGeom &g, int sm_count, int concurrency_hint, bool 
     }
     q.box_w = best_shape.box_w; q.box_h = best_shape.box_h; q.box_n = best_shape.box_n;
     q.tiles_w = best_shape.tiles_w; q.tiles_h = best_shape.tiles_h; q.tiles_n = best_shape.tiles_n;
+    q.im2col = best_shape.im2col;
     q.bn = best_bn;
     q.n_tiles = ceil_div(g.Cout, q.bn);
     q.cout_pad = q.n_tiles * q.bn;
@@ -905,16 +963,32 @@ const char *conv_tc_encode(const ConvTcParams &p, ConvTcPlan *plan) {
             strides[0] = pix_bytes; strides[1] = pix_bytes * dims[1]; strides[2] = strides[1];
             box[0] = chunk; box[1] = cuuint32_t(q.box_w); box[2] = 1; box[3] = 1;
             estr[0] = estr[1] = estr[2] = estr[3] = 1;
+        } else if (q.im2col) {
+            EncodeIm2colFn encode_im2col = encode_im2col_fn();
+            if (!encode_im2col) return "cuTensorMapEncodeIm2col is not available from the driver";
+            dims[0] = cuuint64_t(g.Cin); dims[1] = cuuint64_t(g.W); dims[2] = cuuint64_t(g.H); dims[3] = cuuint64_t(g.N);
+            strides[0] = pix_bytes; strides[1] = pix_bytes * g.W; strides[2] = pix_bytes * g.W * g.H;
+            estr[0] = 1; estr[1] = cuuint32_t(g.sw); estr[2] = cuuint32_t(g.sh); estr[3] = 1;
+            int lower[2], upper[2];                      // w, h
+            im2col_corners(g.W, g.OW, g.sw, g.pw, &lower[0], &upper[0]);
+            im2col_corners(g.H, g.OH, g.sh, g.ph, &lower[1], &upper[1]);
+            CUresult r = encode_im2col(reinterpret_cast<CUtensorMap *>(q.tmap_a), dtype, 4, p.in.ptr, dims, strides, lower,
+                                       upper, chunk, cuuint32_t(q.box_w), estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return fail("activations, im2col", r);
         } else {
             dims[0] = cuuint64_t(g.Cin); dims[1] = cuuint64_t(g.W); dims[2] = cuuint64_t(g.H); dims[3] = cuuint64_t(g.N);
             strides[0] = pix_bytes; strides[1] = pix_bytes * g.W; strides[2] = pix_bytes * g.W * g.H;
             box[0] = chunk; box[1] = cuuint32_t(q.box_w * g.sw); box[2] = cuuint32_t(q.box_h * g.sh); box[3] = cuuint32_t(q.box_n);
             estr[0] = 1; estr[1] = cuuint32_t(g.sw); estr[2] = cuuint32_t(g.sh); estr[3] = 1;
         }
-        CUresult r = encode(reinterpret_cast<CUtensorMap *>(q.tmap_a), dtype, 4, p.in.ptr, dims,
-                            strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) return fail("activations", r);
+        if (!q.im2col) {
+            CUresult r = encode(reinterpret_cast<CUtensorMap *>(q.tmap_a), dtype, 4, p.in.ptr, dims,
+                                strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return fail("activations", r);
+        }
     }
     {
         const cuuint64_t krow = cuuint64_t(g.kh) * g.kw * q.cchunks * chunk;
@@ -939,7 +1013,7 @@ const char *conv_tc_encode(const ConvTcParams &p, ConvTcPlan *plan) {
         cuuint32_t box[4];
         cuuint32_t estr[4] = {1, 1, 1, 1};
         const cuuint64_t pix_bytes = cuuint64_t(p.out.pitch) * esize;
-        if (q.flat_1x1) {
+        if (q.flat_1x1 || q.im2col) {
             dims[0] = cuuint64_t(g.Cout); dims[1] = cuuint64_t(g.N) * g.OH * g.OW; dims[2] = 1; dims[3] = 1;
             strides[0] = pix_bytes; strides[1] = pix_bytes * dims[1]; strides[2] = strides[1];
             box[0] = chunk; box[1] = cuuint32_t(q.box_w); box[2] = 1; box[3] = 1;
@@ -982,7 +1056,8 @@ void launch_conv_tc(const ConvTcParams &p, const ConvTcPlan &q, cudaStream_t str
     t.box_w = q.box_w; t.box_h = q.box_h; t.box_n = q.box_n;
     t.tiles_w = q.tiles_w; t.tiles_h = q.tiles_h;
     t.bn = q.bn; t.cchunks = q.cchunks; t.k_iters = q.k_iters; t.split_k = q.split_k; t.stages = q.stages;
-    t.flat = q.flat_1x1;
+    t.flat = (q.flat_1x1 || q.im2col) ? 1 : 0;
+    t.im2col = q.im2col;
     t.a_bytes = q.box_w * q.box_h * q.box_n * kRowBytes;
     t.bf16 = q.bf16;
     t.chunk = q.bf16 ? 64 : 32;

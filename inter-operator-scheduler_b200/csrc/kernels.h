@@ -106,6 +106,7 @@ struct ConvTcPlan {
     int split_k;                   // CTAs sharing one output tile
     int stages;                    // smem pipeline depth
     int flat_1x1;                  // 1: pixels flattened into one axis (1x1, stride 1, no padding)
+    int im2col;                    // 1: pixels flattened into one axis, activations fetched by im2col-mode TMA
     int x3;                        // 1: three-pass TF32 (operands split into value + residual)
     int tma_store;                 // 1: the output window is 16-byte aligned, the epilogue uses bulk tensor stores
     int pdl;                       // 1: launch with programmatic stream serialization
@@ -135,7 +136,7 @@ bool conv_tc_supported(const TensorRef &in, const ConvGeom &g);
 // Chooses the tiling; sm_count and concurrency_hint (groups running beside this one) steer bn and
 // split_k.  three_pass selects the fp32-grade 3xTF32 product.  Does not touch the device.
 void conv_tc_choose(const ConvGeom &g, int sm_count, int concurrency_hint, bool three_pass, ConvTcPlan *plan,
-                    int force_bn = 0, bool bf16 = false);
+                    int force_bn = 0, bool bf16 = false, bool allow_im2col = true);
 // Overrides the K split (recomputes pipeline depth, shared memory and workspace sizes).
 void conv_tc_set_split(ConvTcPlan *plan, int split);
 // Encodes the two tensor maps (needs final device addresses).  Returns a CUDA driver error text or nullptr.

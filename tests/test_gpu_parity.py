@@ -30,6 +30,7 @@ def default_options():
     rt.set_option('executor', 'graph')
     rt.set_option('conv', 'auto')
     rt.set_option('split_k', '0')
+    rt.set_option('im2col', '1')
     yield
 
 
@@ -61,11 +62,19 @@ TC_SHAPES = [
     (3, 24, 9, 9, 40, 3, 3, 1, 1, 1, 1, 1),        # batch 3, several images per tile
     (5, 20, 4, 4, 300, 1, 1, 1, 1, 0, 0, 1),       # batch 5 flat, Cout > 256
     (2, 36, 8, 8, 130, 3, 1, 1, 1, 1, 0, 1),       # 3x1, ragged Cout
+    (1, 16, 36, 36, 24, 3, 3, 2, 2, 0, 0, 1),      # stride 2 that leaves an unused last row and column
+    (3, 24, 17, 17, 40, 3, 3, 2, 2, 1, 1, 1),      # stride 2 with padding, pixel tiles that span two images
+    (3, 32, 17, 17, 48, 1, 7, 1, 1, 0, 3, 1),      # 867 pixels: the last pixel tile runs past the last image
+    (2, 32, 11, 13, 32, 1, 1, 2, 2, 0, 0, 1),      # 1x1 with stride 2
+    (1, 32, 10, 10, 32, 3, 3, 1, 1, 2, 2, 1),      # padding wider than the filter needs: output larger than input
 ]
 
 
+# windows with taps tile the flattened pixel axis (im2col-mode loads, the default) or boxes of the image
+@pytest.mark.parametrize('im2col', ['1', '0'])
 @pytest.mark.parametrize('shape', TC_SHAPES)
-def test_conv_tensor_core_vs_oracle(shape):
+def test_conv_tensor_core_vs_oracle(shape, im2col):
+    rt.set_option('im2col', im2col)
     assert _conv_case(shape, 'tensor') <= TOL_FP32          # three-pass TF32: fp32-grade
     assert _conv_case(shape, 'tensor1') <= TOL_TF32         # single-pass TF32
     assert _conv_case(shape, 'bf16') <= TOL_BF16            # bfloat16 operands
