@@ -82,8 +82,8 @@ IOS_API const char *ios_last_error(void);
  * Testing aids (each switches one mechanism of the tensor-core convolution off or pins one choice):
  * "im2col" "1"/"0" (pixel tiles over the flattened pixel axis by im2col-mode loads / boxes of the image),
  * "bulk_store" "1"/"0" (results leave through a bulk tensor store / straight from registers),
- * "split_k", "bn", "stages" (a positive number overrides the K split, the output-channel tile width, the
- * depth of the shared-memory pipeline; "0" = automatic), "timeline" "1"/"0" (phase stamps of one CTA).
+ * "split_k", "bn", "stages", "producers" (a positive number overrides the K split, the output-channel tile
+ * width, the depth of the shared-memory pipeline, the lanes that issue TMA loads; "0" = automatic), "timeline" "1"/"0" (phase stamps of one CTA).
  * Options apply to plans built afterwards on the calling process. */
 IOS_API int ios_set_option(const char *key, const char *value);
 IOS_API int ios_get_option(const char *key, char *value, int capacity);

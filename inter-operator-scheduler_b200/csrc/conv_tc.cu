@@ -63,6 +63,9 @@ struct TileGeom {
     int cluster;      // 1: the split_k CTAs of a tile form a thread-block cluster and reduce through shared memory
     int bf16;         // 1: bfloat16 operands / activations (kind::f16), 0: float32 storage (kind::tf32)
     int chunk;        // elements of K per 128-byte row: 32 (float32) or 64 (bfloat16)
+    int producers;    // lanes of warp 0 that issue TMA loads; divides `stages`
+    int wide;         // 1: (three-pass mode, bn <= 128) one instruction of width 2 bn covers the weight tile and its
+                      //    residual; the residual's products accumulate in columns [bn, 2 bn)
 };
 
 // ---- PTX wrappers ----------------------------------------------------------------------------
@@ -207,6 +210,26 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float *v) {
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
+// Accumulator columns [c, c + N) of this thread's lane; in three-pass mode the products with the weight
+// residual accumulate in a second column range `pair` columns further on and are added here.
+__device__ __forceinline__ void acc_ld32(uint32_t taddr, uint32_t pair, float *v) {
+    tmem_ld32(taddr, v);
+    if (pair) {
+        float w[32];
+        tmem_ld32(taddr + pair, w);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] += w[i];
+    }
+}
+__device__ __forceinline__ void acc_ld16(uint32_t taddr, uint32_t pair, float *v) {
+    tmem_ld16(taddr, v);
+    if (pair) {
+        float w[16];
+        tmem_ld16(taddr + pair, w);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] += w[i];
+    }
+}
 // K-major operand tile with 128-byte swizzle: rows are 128 bytes, groups of 8 rows are 1024 bytes apart.
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
     uint64_t d = 0;
@@ -285,6 +308,45 @@ __device__ __forceinline__ void store4_direct(void *out, int bf16, long at, floa
     }
 }
 
+// The MMA issuer's K loop, one copy per operand mode (0: TF32, 1: three-pass TF32, 2: BF16) so that the
+// (3: three-pass TF32 with the weight tile and its residual under one instruction of twice the width)
+// loop body carries no mode tests: wait for the stage, issue its instructions, hand the stage back.
+template <int MODE>
+__device__ __forceinline__ bool mma_loop(int n_it, int stages, uint32_t wait0, uint32_t empty0, uint64_t da0, uint64_t db0,
+                                         uint64_t dal0, uint64_t dbl0, uint64_t dstep, uint32_t tmem_base, uint32_t idesc, uint32_t idesc_wide,
+                                         const ConvTcParams &p) {
+    uint64_t da = da0, db = db0, dal = dal0, dbl = dbl0;
+    uint32_t s = 0, phase = 0;
+#pragma unroll 1
+    for (int i = 0; i < n_it; ++i) {
+        if (!mbar_wait(wait0 + 8u * s, phase, p.error_flag)) return false;
+        if (i == 0) STAMP(3);
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < kRowBytes / 32; ++k) {       // 32 bytes of K per instruction: 8 TF32 or 16 BF16
+            const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+            if (MODE == 3) {
+                // a*w ~= a_hi*[w_hi | w_lo] + a_lo*w_hi
+                umma_tf32(tmem_base, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc_wide, acc);
+                umma_tf32(tmem_base, dal + uint64_t(k * 2), db + uint64_t(k * 2), idesc, 1u);
+            } else if (MODE == 1) {
+                // a*w ~= a_lo*w_hi + a_hi*w_lo + a_hi*w_hi, small terms first
+                umma_tf32(tmem_base, dal + uint64_t(k * 2), db + uint64_t(k * 2), idesc, acc);
+                umma_tf32(tmem_base, da + uint64_t(k * 2), dbl + uint64_t(k * 2), idesc, 1u);
+                umma_tf32(tmem_base, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, 1u);
+            } else if (MODE == 2) {
+                umma_f16(tmem_base, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, acc);
+            } else {
+                umma_tf32(tmem_base, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, acc);
+            }
+        }
+        umma_commit(empty0 + 8u * s);   // frees the stage once these MMAs have read it
+        da += dstep; db += dstep; dal += dstep; dbl += dstep;
+        if (++s == uint32_t(stages)) { s = 0; phase ^= 1u; da = da0; db = db0; dal = dal0; dbl = dbl0; }
+    }
+    return true;
+}
+
 // ---- the kernel ------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kThreads, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -353,7 +415,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == 1) {
+    if (warp == 2) {
         tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), uint32_t(t.tmem_cols));
         tmem_relinquish();
     }
@@ -365,16 +427,24 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // Everything above touches no global memory, so under programmatic dependent launch it overlaps
     // the tail of the previous kernel; the next kernel may start its own prologue from here on.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // Warps 0 and 1 work through a few lanes only.  Their other lanes leave now: a lane that spins on a
+    // barrier pays about 50 cycles per wait while the rest of its warp is parked at the reconvergence point.
+    // (Not in a cluster: there every thread takes part in the cluster barriers below.)
+    if (!t.cluster && ((warp == 0 && lane >= t.producers) || (warp == 1 && lane != 0))) return;
 
     if (warp == 0) {
-        if (lane == 0) {
-            // ---------------- TMA producer ----------------
+        if (lane < t.producers) {
+            // ---------------- TMA producers ----------------
+            // One thread gets through wait -> arm -> issue about once per 600-800 cycles, whatever the
+            // tiles' size, so `producers` lanes share the K steps: lane l serves steps l, l + P, ... and,
+            // P dividing the pipeline depth, owns stages l, l + P, ... for itself.
             // Weights never depend on the previous kernel: the weight tiles of the first `stages` K steps
             // are requested before the grid dependency is waited for, so that under programmatic dependent
             // launch their latency hides behind the predecessor's tail.  Activations follow after the wait.
+            const int P = t.producers;
             const int early = min(n_it, t.stages);
 #pragma unroll 1
-            for (int i = 0; i < early; ++i) {
+            for (int i = lane; i < early; i += P) {
                 const uint32_t stage = smem_base + uint32_t(i) * stage_bytes;
                 const uint32_t bar = full0 + 8u * i;
                 mbar_expect_tx(bar, uint32_t(t.a_bytes + passes * b_bytes));
@@ -383,36 +453,55 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             }
             asm volatile("griddepcontrol.wait;" ::: "memory");
             bool ok = true;
-            int issued = 0;
+            int next = lane;            // this lane's first K step whose activation tile is not requested yet
+            // running position of this lane (divisions cost more than the loads they would steer):
+            // stage s and its phase, channel chunk cc and filter tap (r, sx) of K step it_begin + i
+            int s = lane, phase = 1;
+            int cc, r, sx;
+            {
+                const int it = it_begin + lane;
+                const int tap = it / t.cchunks;
+                cc = it - tap * t.cchunks;
+                r = tap / g.kw;
+                sx = tap - r * g.kw;
+            }
 #pragma unroll 1
-            for (int i = 0; i < n_it && ok; ++i) {
-                const int s = i % t.stages;
-                const int it = it_begin + i;
+            for (int i = lane; i < n_it; i += P) {
                 const uint32_t stage = smem_base + uint32_t(s) * stage_bytes;
                 const uint32_t bar = full0 + 8u * s;
                 if (i >= t.stages) {
-                    ok = mbar_wait(empty0 + 8u * s, uint32_t((i / t.stages - 1) & 1), p.error_flag);
+                    ok = mbar_wait(empty0 + 8u * s, uint32_t(phase), p.error_flag);
                     if (!ok) break;
+                    const int kcol = (it_begin + i) * t.chunk;
                     mbar_expect_tx(bar, uint32_t(t.a_bytes + passes * b_bytes));
-                    tma_load_2d(stage + b_off, &tmap_b, bar, it * t.chunk, cout0);
-                    if (t.x3) tma_load_2d(stage + b_lo_off, &tmap_b, bar, it * t.chunk, t.cout_pad + cout0);
+                    tma_load_2d(stage + b_off, &tmap_b, bar, kcol, cout0);
+                    if (t.x3) tma_load_2d(stage + b_lo_off, &tmap_b, bar, kcol, t.cout_pad + cout0);
                 }
-                const int tap = it / t.cchunks, cc = it - tap * t.cchunks;
-                const int r = tap / g.kw, sx = tap - r * g.kw;
                 if (t.im2col) tma_load_im2col(stage, &tmap_a, bar, cc * t.chunk, im_w, im_h, n0, uint32_t(sx), uint32_t(r));
                 else if (t.flat) tma_load_4d(stage, &tmap_a, bar, cc * t.chunk, ow0, 0, 0);
                 else tma_load_4d(stage, &tmap_a, bar, cc * t.chunk, ow0 * g.sw - g.pw + sx, oh0 * g.sh - g.ph + r, n0);
                 if (i == 0) STAMP(2);
-                issued = i + 1;
+                next = i + P;
+                s += P;
+                if (s >= t.stages) { s -= t.stages; phase ^= 1; }
+                cc += P;
+                while (cc >= t.cchunks) {
+                    cc -= t.cchunks;
+                    if (++sx == g.kw) { sx = 0; ++r; }
+                }
             }
             if (!ok) {
                 atomicExch(p.error_flag, 1);
                 // drain: the loads already issued still land in this CTA's shared memory; a stage whose
-                // activation tile was never requested is completed by hand so that its barrier can fire
-                for (int i = issued; i < min(n_it, max(issued, early)); ++i)
-                    asm volatile("mbarrier.complete_tx.shared::cta.relaxed.cta.b64 [%0], %1;" ::"r"(full0 + 8u * (i % t.stages)), "r"(uint32_t(t.a_bytes)) : "memory");
-                for (int i = max(0, issued - t.stages); i < max(issued, early); ++i)
-                    mbar_wait(full0 + 8u * (i % t.stages), uint32_t((i / t.stages) & 1), nullptr);
+                // activation tile was never requested is completed by hand so that its barrier can fire;
+                // then the latest armed step of each stage this lane owns is waited for
+                int last = next - P;
+                for (int j = next; j < early; j += P) {
+                    asm volatile("mbarrier.complete_tx.shared::cta.relaxed.cta.b64 [%0], %1;" ::"r"(full0 + 8u * (j % t.stages)), "r"(uint32_t(t.a_bytes)) : "memory");
+                    last = j;
+                }
+                for (int j = last, k = 0; j >= 0 && k < t.stages; j -= P, k += P)
+                    mbar_wait(full0 + 8u * (j % t.stages), uint32_t((j / t.stages) & 1), nullptr);
             }
         }
     } else if (warp == 1) {
@@ -421,37 +510,17 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             // instruction descriptor: fp32 accumulator, A/B format (2 = TF32, 1 = BF16), K-major, N, M
             const uint32_t fmt = t.bf16 ? 1u : 2u;
             const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(t.bn >> 3) << 17) | (uint32_t(kTileM >> 4) << 24);
-            const uint32_t wait0 = t.x3 ? ready0 : full0;
-            bool ok = true;
-#pragma unroll 1
-            for (int i = 0; i < n_it; ++i) {
-                const int s = i % t.stages;
-                ok = mbar_wait(wait0 + 8u * s, uint32_t((i / t.stages) & 1), p.error_flag);
-                if (!ok) break;
-                if (i == 0) STAMP(3);
-                tc_fence_after();
-                const uint32_t stage = smem_base + uint32_t(s) * stage_bytes;
-                const uint64_t da = smem_desc_sw128(stage), db = smem_desc_sw128(stage + b_off);
-                if (t.x3) {
-                    // a*w ~= a_lo*w_hi + a_hi*w_lo + a_hi*w_hi, small terms first
-                    const uint64_t dal = smem_desc_sw128(stage + a_lo_off), dbl = smem_desc_sw128(stage + b_lo_off);
-#pragma unroll
-                    for (int k = 0; k < kRowBytes / 32; ++k) {
-                        umma_tf32(tmem_base, dal + uint64_t(k * 2), db + uint64_t(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
-                        umma_tf32(tmem_base, da + uint64_t(k * 2), dbl + uint64_t(k * 2), idesc, 1u);
-                        umma_tf32(tmem_base, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, 1u);
-                    }
-                } else if (t.bf16) {
-#pragma unroll
-                    for (int k = 0; k < kRowBytes / 32; ++k)      // K = 16 bf16 = 32 bytes per instruction
-                        umma_f16(tmem_base, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
-                } else {
-#pragma unroll
-                    for (int k = 0; k < kRowBytes / 32; ++k)      // K = 8 tf32 = 32 bytes per instruction
-                        umma_tf32(tmem_base, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
-                }
-                umma_commit(empty0 + 8u * s);   // frees the stage once these MMAs have read it
-            }
+            // three-pass mode: the weight tile and its residual lie behind one another, so one instruction
+            // of twice the width forms a_hi*w_hi (columns [0, bn)) and a_hi*w_lo (columns [bn, 2 bn))
+            const uint32_t idesc_wide = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(t.bn >> 2) << 17) | (uint32_t(kTileM >> 4) << 24);
+            const uint64_t da0 = smem_desc_sw128(smem_base), db0 = smem_desc_sw128(smem_base + b_off);
+            const uint64_t dal0 = smem_desc_sw128(smem_base + a_lo_off);
+            const uint64_t dstep = uint64_t(stage_bytes >> 4);      // descriptors hold the address in 16-byte units
+            const uint64_t dbl0 = smem_desc_sw128(smem_base + b_lo_off);
+#define IOS_MMA_LOOP(MODE, WAIT) mma_loop<MODE>(n_it, t.stages, WAIT, empty0, da0, db0, dal0, dbl0, dstep, tmem_base, idesc, idesc_wide, p)
+            const bool ok = t.x3 ? (t.wide ? IOS_MMA_LOOP(3, ready0) : IOS_MMA_LOOP(1, ready0))
+                                 : (t.bf16 ? IOS_MMA_LOOP(2, full0) : IOS_MMA_LOOP(0, full0));
+#undef IOS_MMA_LOOP
             if (ok) umma_commit(accum_bar);
             else atomicExch(p.error_flag, 2);
             STAMP(4);
@@ -471,10 +540,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             // tile here.  (Weights are split on the host into two planes; deriving their residual here too
             // was measured 7-15 % slower: this step sits on the latency chain TMA -> split -> MMA.)
             const int n_vec = t.a_bytes >> 4;
+            int s = 0;
+            uint32_t phase = 0;
 #pragma unroll 1
             for (int i = 0; i < n_it && ok; ++i) {
-                const int s = i % t.stages;
-                ok = mbar_wait(full0 + 8u * s, uint32_t((i / t.stages) & 1), p.error_flag);
+                ok = mbar_wait(full0 + 8u * s, phase, p.error_flag);
                 if (!ok) break;
                 uint8_t *stage = generic_base + size_t(s) * stage_bytes;
                 const float4 *hi = reinterpret_cast<const float4 *>(stage);
@@ -491,6 +561,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(ready0 + 8u * s) : "memory");
+                if (++s == t.stages) { s = 0; phase ^= 1u; }
             }
         }
         if (ok) ok = mbar_wait(accum_bar, 0, p.error_flag);
@@ -501,6 +572,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         asm volatile("bar.sync 1, 128;" ::: "memory");          // bias_s is complete
         if (threadIdx.x == 64) STAMP(9);
         const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16);
+        const uint32_t pair = t.wide ? uint32_t(t.bn) : 0u;
         const int tile_id = m_tile * gridDim.y + n_tile;
         bool finisher = true;
         if (t.split_k > 1 && t.cluster) {
@@ -511,7 +583,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll 1
                 for (int c = 0; c < t.bn; c += 32) {
                     float v[32];
-                    tmem_ld32(taddr + c, v);
+                    acc_ld32(taddr + c, pair, v);
 #pragma unroll
                     for (int j = 0; j < 32; j += 4)
                         *reinterpret_cast<float4 *>(part + c + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
@@ -524,7 +596,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll 1
             for (int c = 0; c < t.bn; c += 16) {
                 float v[16];
-                tmem_ld16(taddr + c, v);
+                acc_ld16(taddr + c, pair, v);
 #pragma unroll
                 for (int j = 0; j < 16; ++j) ws[size_t(c + j) * kTileM + row] = v[j];
             }
@@ -562,7 +634,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll 1
                 for (int c = 0; c < t.bn; c += 32) {
                     float v[32];
-                    tmem_ld32(taddr + c, v);
+                    acc_ld32(taddr + c, pair, v);
 #pragma unroll
                     for (int j = 0; j < 32; j += 4) {
                         float o[4];
@@ -579,7 +651,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             for (int c = 0; c < t.bn; c += 16) {
                 float v[16];
                 if (t.split_k == 1) {
-                    tmem_ld16(taddr + c, v);
+                    acc_ld16(taddr + c, pair, v);
                     if (c == 0 && threadIdx.x == 64) STAMP(13);
                 } else {
 #pragma unroll
@@ -649,9 +721,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         // Every thread of every CTA of the cluster passes both barriers, whatever happened before.
         cluster_sync_all();                                   // all partial tiles are parked
         if (warp >= 2) {
-            // CTA r of the cluster finishes rows [r*128/S, (r+1)*128/S) of the tile: it adds the S partial
-            // tiles in split order (so the result does not depend on timing), applies bias and activation
-            // and writes its rows; consecutive threads take consecutive 16-byte columns of a row.
             const int tid = threadIdx.x - 64;
             const uint32_t rank = cluster_cta_rank();
             const int r0 = int(rank) * kTileM / t.split_k, r1 = int(rank + 1) * kTileM / t.split_k;
@@ -700,8 +769,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         cluster_sync_all();                                   // nobody leaves while its tile may still be read
     }
-    __syncthreads();
-    if (warp == 1) {
+    if (warp < 2) return;       // the producer lanes and the MMA issuer have nothing left to do
+    // warps 0 and 1 are gone by now or on their way out; the warps that read the accumulator free it
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (warp == 2) {
         tc_fence_after();
         tmem_dealloc(tmem_base, uint32_t(t.tmem_cols));
         if (lane == 0) STAMP(8);
@@ -771,10 +842,12 @@ bool conv_tc_supported(const TensorRef &in, const ConvGeom &g) {
     return true;
 }
 
-// Tile selection.  At batch 1 a layer is a few dozen CTAs whose cost is fixed overhead plus a K loop
-// that runs at the per-SM rate at which TMA can fill shared memory, so the choice is made with a
-// small cost model (cycles, fitted to a sweep over the 43 distinct Inception-v3 layers on B200):
-//     cta  = fixed + k_steps_per_cta * stage_bytes / fill_rate + epilogue(bn) + cluster_overhead
+// Tile selection.  A CTA costs a fixed overhead plus a K loop whose steps are bound by the slowest of
+// three things -- the wait/issue chain of its single-thread roles (about 450 cycles per step, 700 in
+// three-pass mode, whatever the tile's size), the tensor pipe, the TMA unit -- so the choice is made
+// with a small cost model (cycles, fitted to a sweep over the 43 distinct Inception-v3 layers on B200):
+//     step = max(issue chain of one CTA, tensor time of the resident CTAs, bytes loaded by them / TMA fill rate)
+//     cta  = fixed + k_steps_per_cta * step + epilogue(bn) + cluster_overhead
 //     time = waves * cta,  waves = ceil(ctas / how many fit at once)
 // over every pixel-tile shape, output-channel tile width and K split that the kernel supports.
 // It replaces the reference's run-time algorithm search (src/ios/ios_runtime.cu:150-205).
@@ -831,31 +904,42 @@ void conv_tc_choose(const ConvGeom &g, int sm_count, int concurrency_hint, bool 
             shapes.push_back(sh);
         }
     }
-    const double kFixed = 3000.0, kFillBytesPerCycle = 20.0, kEpiloguePer16 = 400.0, kClusterOverhead = 500.0;
+    // cycles; fitted to a sweep of tile width x split over the 43 distinct Inception-v3 layers at batch 1 and 64
+    const double kFixed = 3000.0, kIssue = 450.0, kIssueThreePass = 700.0, kFillBytesPerCycle = 60.0, kEpiloguePerColumn = 36.0,
+                 kClusterOverhead = 2000.0, kTensorPerColumn = 2.1 * 1.15;
     const int planes = q.x3 ? 2 : 1;
     const int share = std::max(1, concurrency_hint);
     double best_cost = 1e30;
     Shape best_shape = shapes[0];
     int best_bn = 32, best_split = 1;
-    static const int splits[] = {1, 2, 3, 4, 6, 8};
+    static const int splits[] = {1, 2, 4, 8};
     for (const Shape &sh : shapes) {
         const int m_tiles = sh.tiles_w * sh.tiles_h * sh.tiles_n;
         const int rows = sh.box_w * sh.box_h * sh.box_n;
         int last_bn = 0;
         for (int n_tiles = 1; n_tiles <= ceil_div(g.Cout, bn_step); ++n_tiles) {
-            int bn = std::min(256, ceil_div(ceil_div(g.Cout, n_tiles), bn_step) * bn_step);
-            if (force_bn > 0) bn = std::min(256, ceil_div(force_bn, bn_step) * bn_step);
+            const int bn_max = 256;
+            int bn = std::min(bn_max, ceil_div(ceil_div(g.Cout, n_tiles), bn_step) * bn_step);
+            if (force_bn > 0) bn = std::min(bn_max, ceil_div(force_bn, bn_step) * bn_step);
             if (bn == last_bn) continue;
             last_bn = bn;
             const int nt = ceil_div(g.Cout, bn);
-            const double stage_bytes = rows * 128.0 + double(planes) * bn * 128.0;
+            const double load_bytes = rows * 128.0 + double(planes) * bn * 128.0;
+            const double stage_bytes = double(planes) * (kATileBytes + bn * 128.0);
+            const bool wide = q.x3 && bn <= 128;
+            const double tensor = bn * kTensorPerColumn * (q.x3 ? 3.0 : 1.0);
+            const double epilogue = bn * kEpiloguePerColumn * (wide ? 1.3 : 1.0);
             for (int split : splits) {
                 if (split > 1 && split * 2 > q.k_iters) break;
                 const long ctas = long(m_tiles) * nt * split;
-                const int fit = std::max(1, (split == 1 ? sm_count : 8 * (16 / split) * split) / share);
+                // a grid of several waves keeps two CTAs on an SM when two stages of each fit (conv_tc_set_split)
+                const int resident = (split == 1 && ctas > sm_count && 2.0 * stage_bytes <= 108.0 * 1024) ? 2 : 1;
+                const int fit = std::max(1, (split == 1 ? sm_count * resident : 8 * (16 / split) * split) / share);
                 const double waves = double((ctas + fit - 1) / fit);
-                const double cta = kFixed + ceil_div(q.k_iters, split) * stage_bytes / kFillBytesPerCycle +
-                                   (bn / 16) * kEpiloguePer16 + (split > 1 ? kClusterOverhead : 0.0);
+                // a K step costs what its slowest part costs: the issue chain of one CTA, or the SM's tensor
+                // pipe and TMA unit shared by the resident CTAs
+                const double step = std::max({q.x3 ? kIssueThreePass : kIssue, resident * tensor, resident * load_bytes / kFillBytesPerCycle});
+                const double cta = kFixed + ceil_div(q.k_iters, split) * step + epilogue + (split > 1 ? kClusterOverhead : 0.0);
                 const double cost = waves * cta;
                 if (cost < best_cost) {
                     best_cost = cost;
@@ -892,6 +976,7 @@ void conv_tc_set_split(ConvTcPlan *plan, int split) {
         const int fit = (108 * 1024) / stage_bytes;
         q.stages = std::max(2, std::min(q.stages, std::max(fit, 2)));
     }
+    if (q.stages == 5 || q.stages == 7) --q.stages;    // a depth that 2, 3 or 4 producer lanes can share evenly
     if (split > 8) q.cluster = 0;          // larger splits go through the global workspace
     // the store staging needs one 16 KiB slab per 32 output channels inside the pipeline buffers,
     // the cluster reduction one [128][bn + 4] float tile
@@ -1056,13 +1141,21 @@ void launch_conv_tc(const ConvTcParams &p, const ConvTcPlan &q, cudaStream_t str
     t.box_w = q.box_w; t.box_h = q.box_h; t.box_n = q.box_n;
     t.tiles_w = q.tiles_w; t.tiles_h = q.tiles_h;
     t.bn = q.bn; t.cchunks = q.cchunks; t.k_iters = q.k_iters; t.split_k = q.split_k; t.stages = q.stages;
+    t.producers = 1;
+    // lanes run in lockstep, so every lane's stage must be free before any of them refills: at most half
+    // of the stages are refilled together
+    // (measured: two lanes pay off from six stages on; never in three-pass mode, whose stages pass through
+    // the residual split on their way to the tensor core and are few)
+    for (int cand = 2; cand <= (q.max_producers > 0 ? q.max_producers : 4) && cand <= 8 && cand * 3 <= q.stages && !q.x3; ++cand)
+        if (q.stages % cand == 0) t.producers = cand;
     t.flat = (q.flat_1x1 || q.im2col) ? 1 : 0;
     t.im2col = q.im2col;
     t.a_bytes = q.box_w * q.box_h * q.box_n * kRowBytes;
     t.bf16 = q.bf16;
     t.chunk = q.bf16 ? 64 : 32;
+    t.wide = (q.x3 && q.bn <= 128) ? 1 : 0;
     int cols = 32;
-    while (cols < q.bn) cols *= 2;
+    while (cols < (t.wide ? 2 : 1) * q.bn) cols *= 2;   // the wide form keeps a second accumulator range
     t.tmem_cols = cols;
     t.round_tf32 = p.g.round_out;
     t.x3 = q.x3;

@@ -106,6 +106,7 @@ struct ConvTcPlan {
     int split_k;                   // CTAs sharing one output tile
     int stages;                    // smem pipeline depth
     int flat_1x1;                  // 1: pixels flattened into one axis (1x1, stride 1, no padding)
+    int max_producers;             // testing aid: cap on the lanes that issue TMA loads (0: the default, 4)
     int im2col;                    // 1: pixels flattened into one axis, activations fetched by im2col-mode TMA
     int x3;                        // 1: three-pass TF32 (operands split into value + residual)
     int tma_store;                 // 1: the output window is 16-byte aligned, the epilogue uses bulk tensor stores

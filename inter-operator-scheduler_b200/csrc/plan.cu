@@ -393,6 +393,7 @@ private:
                            !plan_.options.no_im2col);
             if (plan_.options.force_split_k > 0) conv_tc_set_split(&slot.tcplan, plan_.options.force_split_k);
             slot.tcplan.pdl = plan_.options.pdl ? 1 : 0;
+            slot.tcplan.max_producers = plan_.options.producers;
             if (plan_.options.force_stages > 0) {           // testing aid: shallower pipeline
                 ConvTcPlan &q = slot.tcplan;
                 const size_t stage_bytes = (q.smem_bytes - 24 * q.stages - 64 - 1024) / q.stages;

@@ -636,6 +636,7 @@ int ios_set_option(const char *key, const char *value) {
         else if (k == "split_k") g_options.force_split_k = std::atoi(value);
         else if (k == "bn") g_options.force_bn = std::atoi(value);
         else if (k == "stages") g_options.force_stages = std::atoi(value);
+        else if (k == "producers") g_options.producers = std::atoi(value);
         else if (k == "bulk_store" && (v == "0" || v == "1")) g_options.no_bulk_store = v == "0";
         else if (k == "im2col" && (v == "0" || v == "1")) g_options.no_im2col = v == "0";
         else if (k == "timeline") g_options.timeline = v == "1";
