@@ -167,6 +167,162 @@ __global__ void __launch_bounds__(kThreads) pool_kernel(const PoolParams p) {
     }
 }
 
+// ---- 3x3 windows: a thread walks down a column of output pixels ------------------------------
+// V consecutive channels as float: one 16-byte access of float32 (V = 4) or bfloat16 (V = 8), or 8 bytes of bfloat16 (V = 4).
+template <typename T, int V> struct VecIo;
+template <> struct VecIo<float, 4> {
+    typedef float4 Raw;
+    static __device__ __forceinline__ void unpack(const Raw &x, float (&v)[4]) { v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w; }
+    static __device__ __forceinline__ void load(const float *p, float (&v)[4]) {
+        const float4 x = *reinterpret_cast<const float4 *>(p);
+        v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+    }
+    static __device__ __forceinline__ void store(float *p, const float (&v)[4]) {
+        *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+template <> struct VecIo<__nv_bfloat16, 4> {
+    typedef uint2 Raw;
+    static __device__ __forceinline__ void unpack(const Raw &raw, float (&v)[4]) {
+        const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.x));
+        const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.y));
+        v[0] = lo.x; v[1] = lo.y; v[2] = hi.x; v[3] = hi.y;
+    }
+    static __device__ __forceinline__ void load(const __nv_bfloat16 *p, float (&v)[4]) {
+        const float4 x = load4(p);
+        v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16 *p, const float (&v)[4]) { store4(p, make_float4(v[0], v[1], v[2], v[3])); }
+};
+template <> struct VecIo<__nv_bfloat16, 8> {
+    typedef uint4 Raw;
+    static __device__ __forceinline__ void unpack(const Raw &raw, float (&v)[8]) {
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&w[j]));
+            v[2 * j] = f.x; v[2 * j + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ void load(const __nv_bfloat16 *p, float (&v)[8]) {
+        const uint4 raw = *reinterpret_cast<const uint4 *>(p);
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&w[j]));
+            v[2 * j] = f.x; v[2 * j + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16 *p, const float (&v)[8]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+            w[j] = *reinterpret_cast<const uint32_t *>(&h);
+        }
+        *reinterpret_cast<uint4 *>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+};
+
+// A thread owns V channels of one output column and walks `rows_per_thread` output rows down it.  It
+// reads every input row of its span once: the three pixels of the window's width (the pixels its
+// neighbours in the warp read at the same moment, so two of three come from L1) are reduced to one
+// value per row, the last three rows' values sit in registers, and an output row is emitted whenever
+// the window is complete -- 3 loads per output for a stride-1 window instead of 9, 6 for stride 2.
+// Rows are fetched four at a time (12 independent 16-byte loads in flight per thread): a thread's rows
+// depend on one another only through registers, so the memory latency is paid once per four rows.
+// Average pooling divides by 9 whatever the padding (CUDNN_POOLING_AVERAGE_COUNT_INCLUDE_PADDING,
+// the reference's mode, src/ios/ios_runtime.cu:546-553).
+template <typename T, int V, bool kMax>
+__global__ void __launch_bounds__(kThreads) pool3x3_kernel(const PoolParams p, int rows_per_thread) {
+    typedef typename VecIo<T, V>::Raw Raw;
+    constexpr int kRows = 4;
+    // grid: x covers (output column, channel group), y the row segments, z the images -- no 64-bit index arithmetic
+    const int groups = (p.in.C + V - 1) / V;
+    const int idx = blockIdx.x * kThreads + threadIdx.x;
+    if (idx >= p.out.W * groups) return;
+    const int ow = idx / groups;
+    const int c = (idx - ow * groups) * V;
+    const int n = blockIdx.z;
+    const int oh_begin = blockIdx.y * rows_per_thread, oh_end = min(p.out.H, oh_begin + rows_per_thread);
+    const float identity = kMax ? -FLT_MAX : 0.0f;
+    const int w0 = ow * p.sw - p.pw;
+    const bool w_ok[3] = {w0 >= 0 && w0 < p.in.W, w0 + 1 >= 0 && w0 + 1 < p.in.W, w0 + 2 >= 0 && w0 + 2 < p.in.W};
+    const size_t row_pitch = size_t(p.in.W) * p.in.pitch;
+    const T *image = p.in.as<const T>() + size_t(n) * p.in.H * row_pitch + size_t(max(w0, 0)) * p.in.pitch + c;
+    const int first = w0 < 0 ? -w0 : 0;          // window column that `image` points at
+    T *dst = p.out.as<T>() + ((size_t(n) * p.out.H + oh_begin) * p.out.W + ow) * p.out.pitch + c;
+    const size_t dst_step = size_t(p.out.W) * p.out.pitch;
+    const bool whole = c + V <= p.in.C;
+
+    const int h_first = oh_begin * p.sh - p.ph, h_last = (oh_end - 1) * p.sh - p.ph + 2;
+    int next_emit = h_first + 2;                 // the input row that completes the next output row
+    float r1[V], r2[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) r1[j] = r2[j] = identity;
+    for (int hb = h_first; hb <= h_last; hb += kRows) {
+        Raw raw[kRows][3];
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            const int h = hb + r;
+            const bool row_ok = h >= 0 && h < p.in.H && h <= h_last;
+            const T *src = image + size_t(max(h, 0)) * row_pitch;
+#pragma unroll
+            for (int s = 0; s < 3; ++s)
+                if (row_ok && w_ok[s]) raw[r][s] = *reinterpret_cast<const Raw *>(src + (s - first) * p.in.pitch);
+        }
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            const int h = hb + r;
+            if (h > h_last) break;
+            const bool row_ok = h >= 0 && h < p.in.H;
+            float acc[V];
+#pragma unroll
+            for (int j = 0; j < V; ++j) acc[j] = identity;
+#pragma unroll
+            for (int s = 0; s < 3; ++s) {
+                if (!(row_ok && w_ok[s])) continue;
+                float v[V];
+                VecIo<T, V>::unpack(raw[r][s], v);
+#pragma unroll
+                for (int j = 0; j < V; ++j) acc[j] = kMax ? fmaxf(acc[j], v[j]) : acc[j] + v[j];
+            }
+            if (h == next_emit) {
+                float o[V];
+#pragma unroll
+                for (int j = 0; j < V; ++j) {
+                    const float z = kMax ? fmaxf(fmaxf(r1[j], r2[j]), acc[j]) : (r1[j] + r2[j] + acc[j]) * (1.0f / 9.0f);
+                    o[j] = p.round_out ? to_tf32(z) : z;
+                }
+                if (whole) {
+                    VecIo<T, V>::store(dst, o);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < V; ++j)
+                        if (c + j < p.in.C) store1(dst + j, o[j]);
+                }
+                dst += dst_step;
+                next_emit += p.sh;
+            }
+#pragma unroll
+            for (int j = 0; j < V; ++j) { r1[j] = r2[j]; r2[j] = acc[j]; }
+        }
+    }
+}
+
+template <typename T, int V>
+void launch_pool3x3(const PoolParams &p, cudaStream_t stream) {
+    const int groups = (p.in.C + V - 1) / V;
+    // long columns reuse the most rows; short ones give a small batch enough threads to fill the GPU
+    int rows = p.out.H;
+    auto threads_for = [&](int r) { return long(p.out.N) * ((p.out.H + r - 1) / r) * p.out.W * groups; };
+    while (rows > 4 && threads_for(rows) < 148L * 1024) rows = (rows + 1) / 2;
+    const int segments = (p.out.H + rows - 1) / rows;
+    const dim3 grid((p.out.W * groups + kThreads - 1) / kThreads, segments, p.out.N);
+    if (p.is_max) pool3x3_kernel<T, V, true><<<grid, kThreads, 0, stream>>>(p, rows);
+    else pool3x3_kernel<T, V, false><<<grid, kThreads, 0, stream>>>(p, rows);
+}
+
 // One block per (image, 32-channel slab): 8 warps stride over the pixels, lanes over channels, so
 // each warp reads one contiguous span per pixel; partial results meet in shared memory.
 template <typename T>
@@ -268,6 +424,14 @@ void launch_pool(const PoolParams &p, cudaStream_t stream) {
         return;
     }
     const bool vec = p.in.vec4() && p.out.vec4();
+    if (vec && p.kh == 3 && p.kw == 3 && p.out.N <= 65535) {
+        const bool wide = bf16 && p.in.pitch % 8 == 0 && p.out.pitch % 8 == 0 &&
+                          (reinterpret_cast<uintptr_t>(p.in.ptr) | reinterpret_cast<uintptr_t>(p.out.ptr)) % 16 == 0;
+        if (!bf16) launch_pool3x3<float, 4>(p, stream);
+        else if (wide) launch_pool3x3<__nv_bfloat16, 8>(p, stream);
+        else launch_pool3x3<__nv_bfloat16, 4>(p, stream);
+        return;
+    }
     const int grid = grid_for(p.out.pixels() * (vec ? (p.in.C + 3) / 4 : p.in.C), kThreads);
     if (bf16) {
         if (vec) pool_kernel<__nv_bfloat16, true><<<grid, kThreads, 0, stream>>>(p);
