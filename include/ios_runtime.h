@@ -81,6 +81,7 @@ IOS_API const char *ios_last_error(void);
  *                  waits only for the groups that produced its inputs)
  * Testing aids (each switches one mechanism of the tensor-core convolution off or pins one choice):
  * "im2col" "1"/"0" (pixel tiles over the flattened pixel axis by im2col-mode loads / boxes of the image),
+ * "persistent" "1"/"0" (grids of several waves run as resident CTAs that walk the tiles / one CTA per tile),
  * "bulk_store" "1"/"0" (results leave through a bulk tensor store / straight from registers),
  * "split_k", "bn", "stages", "producers" (a positive number overrides the K split, the output-channel tile
  * width, the depth of the shared-memory pipeline, the lanes that issue TMA loads; "0" = automatic), "timeline" "1"/"0" (phase stamps of one CTA).

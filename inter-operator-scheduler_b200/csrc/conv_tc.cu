@@ -311,38 +311,55 @@ __device__ __forceinline__ void store4_direct(void *out, int bf16, long at, floa
 // The MMA issuer's K loop, one copy per operand mode (0: TF32, 1: three-pass TF32, 2: BF16) so that the
 // (3: three-pass TF32 with the weight tile and its residual under one instruction of twice the width)
 // loop body carries no mode tests: wait for the stage, issue its instructions, hand the stage back.
+// Position of the MMA issuer in the ring of pipeline stages (it outlives a tile in the persistent kernel).
+struct MmaRing {
+    uint64_t da0, db0, dal0, dbl0, dstep;   // descriptors of stage 0 and their step per stage (16-byte units)
+    uint64_t da, db, dal, dbl;
+    uint32_t s, phase;
+    __device__ __forceinline__ void start(uint32_t smem_base, uint32_t a_lo_off, uint32_t b_off, uint32_t b_lo_off, int stage_bytes) {
+        da0 = smem_desc_sw128(smem_base);
+        db0 = smem_desc_sw128(smem_base + b_off);
+        dal0 = smem_desc_sw128(smem_base + a_lo_off);
+        dbl0 = smem_desc_sw128(smem_base + b_lo_off);
+        dstep = uint64_t(stage_bytes >> 4);
+        da = da0; db = db0; dal = dal0; dbl = dbl0;
+        s = 0; phase = 0;
+    }
+};
+
 template <int MODE>
-__device__ __forceinline__ bool mma_loop(int n_it, int stages, uint32_t wait0, uint32_t empty0, uint64_t da0, uint64_t db0,
-                                         uint64_t dal0, uint64_t dbl0, uint64_t dstep, uint32_t tmem_base, uint32_t idesc, uint32_t idesc_wide,
-                                         const ConvTcParams &p) {
-    uint64_t da = da0, db = db0, dal = dal0, dbl = dbl0;
-    uint32_t s = 0, phase = 0;
+__device__ __forceinline__ bool mma_loop(int n_it, int stages, uint32_t wait0, uint32_t empty0, MmaRing &ring, uint32_t tmem_d,
+                                         uint32_t idesc, uint32_t idesc_wide, const ConvTcParams &p) {
 #pragma unroll 1
     for (int i = 0; i < n_it; ++i) {
-        if (!mbar_wait(wait0 + 8u * s, phase, p.error_flag)) return false;
+        if (!mbar_wait(wait0 + 8u * ring.s, ring.phase, p.error_flag)) return false;
         if (i == 0) STAMP(3);
         tc_fence_after();
+        const uint64_t da = ring.da, db = ring.db, dal = ring.dal, dbl = ring.dbl;
 #pragma unroll
         for (int k = 0; k < kRowBytes / 32; ++k) {       // 32 bytes of K per instruction: 8 TF32 or 16 BF16
             const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
             if (MODE == 3) {
                 // a*w ~= a_hi*[w_hi | w_lo] + a_lo*w_hi
-                umma_tf32(tmem_base, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc_wide, acc);
-                umma_tf32(tmem_base, dal + uint64_t(k * 2), db + uint64_t(k * 2), idesc, 1u);
+                umma_tf32(tmem_d, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc_wide, acc);
+                umma_tf32(tmem_d, dal + uint64_t(k * 2), db + uint64_t(k * 2), idesc, 1u);
             } else if (MODE == 1) {
                 // a*w ~= a_lo*w_hi + a_hi*w_lo + a_hi*w_hi, small terms first
-                umma_tf32(tmem_base, dal + uint64_t(k * 2), db + uint64_t(k * 2), idesc, acc);
-                umma_tf32(tmem_base, da + uint64_t(k * 2), dbl + uint64_t(k * 2), idesc, 1u);
-                umma_tf32(tmem_base, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, 1u);
+                umma_tf32(tmem_d, dal + uint64_t(k * 2), db + uint64_t(k * 2), idesc, acc);
+                umma_tf32(tmem_d, da + uint64_t(k * 2), dbl + uint64_t(k * 2), idesc, 1u);
+                umma_tf32(tmem_d, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, 1u);
             } else if (MODE == 2) {
-                umma_f16(tmem_base, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, acc);
+                umma_f16(tmem_d, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, acc);
             } else {
-                umma_tf32(tmem_base, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, acc);
+                umma_tf32(tmem_d, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, acc);
             }
         }
-        umma_commit(empty0 + 8u * s);   // frees the stage once these MMAs have read it
-        da += dstep; db += dstep; dal += dstep; dbl += dstep;
-        if (++s == uint32_t(stages)) { s = 0; phase ^= 1u; da = da0; db = db0; dal = dal0; dbl = dbl0; }
+        umma_commit(empty0 + 8u * ring.s);   // frees the stage once these MMAs have read it
+        ring.da += ring.dstep; ring.db += ring.dstep; ring.dal += ring.dstep; ring.dbl += ring.dstep;
+        if (++ring.s == uint32_t(stages)) {
+            ring.s = 0; ring.phase ^= 1u;
+            ring.da = ring.da0; ring.db = ring.db0; ring.dal = ring.dal0; ring.dbl = ring.dbl0;
+        }
     }
     return true;
 }
@@ -513,11 +530,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             // three-pass mode: the weight tile and its residual lie behind one another, so one instruction
             // of twice the width forms a_hi*w_hi (columns [0, bn)) and a_hi*w_lo (columns [bn, 2 bn))
             const uint32_t idesc_wide = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(t.bn >> 2) << 17) | (uint32_t(kTileM >> 4) << 24);
-            const uint64_t da0 = smem_desc_sw128(smem_base), db0 = smem_desc_sw128(smem_base + b_off);
-            const uint64_t dal0 = smem_desc_sw128(smem_base + a_lo_off);
-            const uint64_t dstep = uint64_t(stage_bytes >> 4);      // descriptors hold the address in 16-byte units
-            const uint64_t dbl0 = smem_desc_sw128(smem_base + b_lo_off);
-#define IOS_MMA_LOOP(MODE, WAIT) mma_loop<MODE>(n_it, t.stages, WAIT, empty0, da0, db0, dal0, dbl0, dstep, tmem_base, idesc, idesc_wide, p)
+            MmaRing ring;
+            ring.start(smem_base, a_lo_off, b_off, b_lo_off, stage_bytes);
+#define IOS_MMA_LOOP(MODE, WAIT) mma_loop<MODE>(n_it, t.stages, WAIT, empty0, ring, tmem_base, idesc, idesc_wide, p)
             const bool ok = t.x3 ? (t.wide ? IOS_MMA_LOOP(3, ready0) : IOS_MMA_LOOP(1, ready0))
                                  : (t.bf16 ? IOS_MMA_LOOP(2, full0) : IOS_MMA_LOOP(0, full0));
 #undef IOS_MMA_LOOP
@@ -779,6 +794,312 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
 }
 
+// ---- the persistent kernel -------------------------------------------------------------------
+// A grid of several waves spends most of its time outside the K loop when K is short (a 1x1
+// convolution over 192 bfloat16 channels is three K steps): set-up and epilogue of a tile cost more
+// than its tensor work.  Here a CTA stays on its SM and walks tiles blockIdx.x, blockIdx.x + gridDim.x,
+// ...; barriers, tensor maps and TMEM are set up once, the accumulator is double-buffered in TMEM, and
+// the epilogue warps finish tile i while the producer and the MMA issuer are already in tile i + 1.
+//   warp 0     TMA producer lanes (ring of pipeline stages, running across tiles)
+//   warp 1     MMA issuer: waits for a free accumulator, runs the tile's K loop, commits to acc_full
+//   warps 2-9  epilogue: two warps per TMEM lane quarter, each half of the tile's columns
+//              (three-pass mode: warps 2-5 are the epilogue, warps 6-9 compute the activation residual)
+constexpr int kPersistThreads = 320;
+
+struct PersistGeom {
+    int n_tiles;        // output-channel tiles
+    int total_tiles;    // pixel tiles * output-channel tiles, output-channel tile fastest
+    int staging_off;    // byte offset of the store staging area (behind the pipeline stages)
+    int acc_stride;     // TMEM columns from one accumulator to the other
+};
+
+struct TileCoord {
+    int cout0, ow0, oh0, n0, im_w, im_h;
+};
+
+__device__ __forceinline__ TileCoord tile_coord(int tile, const TileGeom &t, const PersistGeom &pg, const ConvGeom &g) {
+    TileCoord c;
+    const int m_tile = tile / pg.n_tiles;
+    c.cout0 = (tile - m_tile * pg.n_tiles) * t.bn;
+    c.ow0 = c.oh0 = c.n0 = c.im_w = c.im_h = 0;
+    if (t.flat) {
+        c.ow0 = m_tile * t.box_w;
+        if (t.im2col) {
+            const int per_image = g.OH * g.OW;
+            c.n0 = c.ow0 / per_image;
+            const int rem = c.ow0 - c.n0 * per_image;
+            c.oh0 = rem / g.OW;
+            c.im_w = (rem - c.oh0 * g.OW) * g.sw - g.pw;
+            c.im_h = c.oh0 * g.sh - g.ph;
+        }
+    } else {
+        const int tw = m_tile % t.tiles_w;
+        const int rest = m_tile / t.tiles_w;
+        c.ow0 = tw * t.box_w;
+        c.oh0 = (rest % t.tiles_h) * t.box_h;
+        c.n0 = (rest / t.tiles_h) * t.box_n;
+    }
+    return c;
+}
+
+__global__ void __launch_bounds__(kPersistThreads, 1)
+conv_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                          const __grid_constant__ CUtensorMap tmap_c, const ConvTcParams p, const TileGeom t,
+                          const PersistGeom pg) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ float bias_s[2][256];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
+    const int b_bytes = t.bn * kRowBytes;
+    const int passes = t.x3 ? 2 : 1;
+    const int stage_bytes = passes * (kATileBytes + b_bytes);
+    const uint32_t a_lo_off = kATileBytes;
+    const uint32_t b_off = uint32_t(passes) * kATileBytes;
+    const uint32_t b_lo_off = b_off + uint32_t(b_bytes);
+    const int slabs = (t.bn + t.chunk - 1) / t.chunk;
+    const uint32_t bars = smem_base + uint32_t(pg.staging_off) + (t.tma_store ? uint32_t(slabs) * kATileBytes : 0u);
+    const uint32_t full0 = bars, empty0 = bars + 8u * t.stages, ready0 = bars + 16u * t.stages;
+    const uint32_t acc_full0 = bars + 24u * t.stages, acc_empty0 = acc_full0 + 16u;
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(generic_base + (bars - smem_base) + 24 * t.stages + 32);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const ConvGeom &g = p.g;
+    const int epi_warps = t.x3 ? 4 : 8;
+    const int my_tiles = (pg.total_tiles - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x);
+
+    if (warp == 0) {
+        if (lane < t.stages) {
+            mbar_init(full0 + 8u * lane, 1);
+            mbar_init(empty0 + 8u * lane, 1);
+            mbar_init(ready0 + 8u * lane, 128);
+        }
+        if (lane >= 28) {
+            const int a = lane & 1;
+            if (lane < 30) mbar_init(acc_full0 + 8u * a, 1);
+            else mbar_init(acc_empty0 + 8u * a, uint32_t(epi_warps));
+        }
+        if (lane == 27) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
+            if (t.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_c) : "memory");
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 2) {
+        tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), uint32_t(t.tmem_cols));
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if ((warp == 0 && lane >= t.producers) || (warp == 1 && lane != 0)) return;
+
+    if (warp == 0) {
+        // ---------------- TMA producer lanes ----------------
+        // Lane l serves K steps l, l + P, ... of the CTA's whole sequence of (tile, K step) pairs and owns
+        // stages l, l + P, ... of the ring.  A fresh barrier lets a wait for parity 1 pass at once.
+        const int P = t.producers;
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        int tile = blockIdx.x, it = lane;
+        while (it >= t.k_iters && tile < pg.total_tiles) { it -= t.k_iters; tile += gridDim.x; }
+        int s = lane, phase = 1, armed = 0;
+        bool ok = true;
+#pragma unroll 1
+        while (ok && tile < pg.total_tiles) {
+            const TileCoord tc = tile_coord(tile, t, pg, g);
+            int cc, r, sx;
+            {
+                const int tap = it / t.cchunks;
+                cc = it - tap * t.cchunks;
+                r = tap / g.kw;
+                sx = tap - r * g.kw;
+            }
+#pragma unroll 1
+            while (it < t.k_iters) {
+                ok = mbar_wait(empty0 + 8u * s, uint32_t(phase), p.error_flag);
+                if (!ok) break;
+                const uint32_t stage = smem_base + uint32_t(s) * stage_bytes;
+                const uint32_t bar = full0 + 8u * s;
+                mbar_expect_tx(bar, uint32_t(t.a_bytes + passes * b_bytes));
+                tma_load_2d(stage + b_off, &tmap_b, bar, it * t.chunk, tc.cout0);
+                if (t.x3) tma_load_2d(stage + b_lo_off, &tmap_b, bar, it * t.chunk, t.cout_pad + tc.cout0);
+                if (t.im2col) tma_load_im2col(stage, &tmap_a, bar, cc * t.chunk, tc.im_w, tc.im_h, tc.n0, uint32_t(sx), uint32_t(r));
+                else if (t.flat) tma_load_4d(stage, &tmap_a, bar, cc * t.chunk, tc.ow0, 0, 0);
+                else tma_load_4d(stage, &tmap_a, bar, cc * t.chunk, tc.ow0 * g.sw - g.pw + sx, tc.oh0 * g.sh - g.ph + r, tc.n0);
+                ++armed;
+                s += P;
+                if (s >= t.stages) { s -= t.stages; phase ^= 1; }
+                it += P;
+                cc += P;
+                while (cc >= t.cchunks) {
+                    cc -= t.cchunks;
+                    if (++sx == g.kw) { sx = 0; ++r; }
+                }
+            }
+            it -= t.k_iters;
+            tile += gridDim.x;
+            while (it >= t.k_iters && tile < pg.total_tiles) { it -= t.k_iters; tile += gridDim.x; }
+        }
+        if (!ok) {
+            atomicExch(p.error_flag, 1);
+            // drain: the loads this lane has issued still land in shared memory; wait for the latest
+            // one of each stage it owns before the CTA may go
+            const int owned = t.stages / P;
+            for (int j = armed - 1, k = 0; j >= 0 && k < owned; --j, ++k)
+                mbar_wait(full0 + 8u * (lane + (j % owned) * P), uint32_t((j / owned) & 1), nullptr);
+        }
+        return;
+    }
+    if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        const uint32_t fmt = t.bf16 ? 1u : 2u;
+        const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(t.bn >> 3) << 17) | (uint32_t(kTileM >> 4) << 24);
+        const uint32_t idesc_wide = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(t.bn >> 2) << 17) | (uint32_t(kTileM >> 4) << 24);
+        MmaRing ring;
+        ring.start(smem_base, a_lo_off, b_off, b_lo_off, stage_bytes);
+        bool ok = true;
+#pragma unroll 1
+        for (int ti = 0; ti < my_tiles && ok; ++ti) {
+            const uint32_t a = uint32_t(ti) & 1u;
+            // the epilogue must have emptied this accumulator (tiles 0 and 1 find it fresh: parity 1 passes)
+            ok = mbar_wait(acc_empty0 + 8u * a, ((uint32_t(ti) >> 1) & 1u) ^ 1u, p.error_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t tmem_d = tmem_base + a * uint32_t(pg.acc_stride);
+#define IOS_MMA_LOOP(MODE, WAIT) mma_loop<MODE>(t.k_iters, t.stages, WAIT, empty0, ring, tmem_d, idesc, idesc_wide, p)
+            ok = t.x3 ? (t.wide ? IOS_MMA_LOOP(3, ready0) : IOS_MMA_LOOP(1, ready0))
+                      : (t.bf16 ? IOS_MMA_LOOP(2, full0) : IOS_MMA_LOOP(0, full0));
+#undef IOS_MMA_LOOP
+            if (ok) umma_commit(acc_full0 + 8u * a);
+        }
+        if (!ok) atomicExch(p.error_flag, 2);
+        return;
+    }
+    if (t.x3 && warp >= 6) {
+        // ---------------- warps 6..9 (three-pass mode): residual of every landed activation tile ----------------
+        const int tid = threadIdx.x - 192;
+        const int n_vec = t.a_bytes >> 4;
+        const long steps = long(my_tiles) * t.k_iters;
+        int s = 0;
+        uint32_t phase = 0;
+#pragma unroll 1
+        for (long i = 0; i < steps; ++i) {
+            if (!mbar_wait(full0 + 8u * s, phase, p.error_flag)) {
+                atomicExch(p.error_flag, 4);
+                break;
+            }
+            uint8_t *stage = generic_base + size_t(s) * stage_bytes;
+            const float4 *hi = reinterpret_cast<const float4 *>(stage);
+            float4 *lo = reinterpret_cast<float4 *>(stage + a_lo_off);
+#pragma unroll 2
+            for (int v = tid; v < n_vec; v += 128) {
+                const float4 x = hi[v];
+                float4 l;
+                l.x = x.x - __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u);
+                l.y = x.y - __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u);
+                l.z = x.z - __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u);
+                l.w = x.w - __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u);
+                lo[v] = l;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(ready0 + 8u * s) : "memory");
+            if (++s == t.stages) { s = 0; phase ^= 1u; }
+        }
+        return;
+    }
+    // ---------------- epilogue warps ----------------
+    const int e = warp - 2;                           // 0 .. epi_warps - 1
+    const int etid = threadIdx.x - 64;                // 0 .. epi_warps * 32 - 1
+    const int epi_threads = epi_warps * 32;
+    const int quad = warp & 3;                        // TMEM lane quarter this warp may read
+    const int row = quad * 32 + lane;
+    const int cols_per_warp = epi_warps == 8 ? t.bn / 2 : t.bn;
+    const int c_begin = (e >> 2) * cols_per_warp, c_end = c_begin + cols_per_warp;
+    const uint32_t pair = t.wide ? uint32_t(t.bn) : 0u;
+    uint8_t *staging = generic_base + pg.staging_off;
+    const long total_pixels = long(g.N) * g.OH * g.OW;
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // the output window may still be read by the previous kernel
+#pragma unroll 1
+    for (int ti = 0; ti < my_tiles; ++ti) {
+        const int tile = int(blockIdx.x) + ti * int(gridDim.x);
+        const TileCoord tc = tile_coord(tile, t, pg, g);
+        const uint32_t a = uint32_t(ti) & 1u;
+        float *bias = bias_s[a];
+        for (int j = etid; j < t.bn; j += epi_threads) bias[j] = (p.bias && tc.cout0 + j < g.Cout) ? p.bias[tc.cout0 + j] : 0.0f;
+        bool ok = mbar_wait(acc_full0 + 8u * a, (uint32_t(ti) >> 1) & 1u, p.error_flag);
+        ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
+        if (!ok && lane == 0) atomicExch(p.error_flag, 3);
+        tc_fence_after();
+        // the bulk store of the previous tile must have read the staging area before it is written again
+        if (t.tma_store && etid == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"r"(epi_threads) : "memory");      // bias complete, staging free
+        const int valid = min(t.bn, g.Cout - tc.cout0);
+        if (ok) {
+            long pix_off = -1;
+            if (t.flat) {
+                const long pix = long(tc.ow0) + row;
+                if (row < t.box_w && pix < total_pixels) pix_off = pix * p.out.pitch;
+            } else {
+                const int ww = row % t.box_w;
+                const int hh = (row / t.box_w) % t.box_h;
+                const int im = row / (t.box_w * t.box_h);
+                const int ow = tc.ow0 + ww, oh = tc.oh0 + hh, n = tc.n0 + im;
+                if (im < t.box_n && ow < g.OW && oh < g.OH && n < g.N)
+                    pix_off = ((long(n) * g.OH + oh) * g.OW + ow) * p.out.pitch;
+            }
+            const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + a * uint32_t(pg.acc_stride);
+#pragma unroll 1
+            for (int c = c_begin; c < c_end; c += 16) {
+                float v[16];
+                acc_ld16(taddr + c, pair, v);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float z = act_apply(v[j] + bias[c + j], g.act);
+                    v[j] = t.round_tf32 ? round_tf32(z) : z;
+                }
+                if (t.tma_store) {
+#pragma unroll
+                    for (int j = 0; j < 16; j += 4)
+                        stage4(staging, row, c + j, make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]), t.bf16);
+                } else if (pix_off >= 0 && c < valid) {
+#pragma unroll
+                    for (int j = 0; j < 16; j += 4)
+                        if (c + j < valid)
+                            store4_direct(p.out.ptr, t.bf16, pix_off + tc.cout0 + c + j, make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]),
+                                          valid - (c + j));
+                }
+            }
+        }
+        // hand the accumulator back to the MMA issuer: one arrival per epilogue warp
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty0 + 8u * a) : "memory");
+        if (t.tma_store) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("bar.sync 1, %0;" ::"r"(epi_threads) : "memory");  // the tile is staged
+            if (ok && etid == 0) {
+                for (int c = 0; c < valid; c += t.chunk) {
+                    const uint32_t src = smem_base + uint32_t(pg.staging_off) + uint32_t(c / t.chunk) * kATileBytes;
+                    if (t.flat) tma_store_4d(&tmap_c, src, tc.cout0 + c, tc.ow0, 0, 0);
+                    else tma_store_4d(&tmap_c, src, tc.cout0 + c, tc.ow0, tc.oh0, tc.n0);
+                }
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+        }
+    }
+    if (t.tma_store && etid == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    tc_fence_before();
+    asm volatile("bar.sync 1, %0;" ::"r"(epi_threads) : "memory");
+    if (warp == 2) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, uint32_t(t.tmem_cols));
+    }
+}
+
+
 // ---- host side -------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -984,6 +1305,28 @@ void conv_tc_set_split(ConvTcPlan *plan, int split) {
     if (split > 1 && q.cluster)
         while (size_t(q.stages) * stage_bytes < size_t(kTileM) * (q.bn + 4) * sizeof(float)) ++q.stages;
     q.smem_bytes = size_t(q.stages) * stage_bytes + 24 * q.stages + 64 + 1024;
+    // More tiles than CTAs that fit at once: persistent CTAs with two accumulators in TMEM, the store
+    // staging in an area of its own behind the pipeline stages.
+    q.persistent = 0;
+    q.grid_ctas = base * split;
+    const int sms = q.sm_count > 0 ? q.sm_count : 148;
+    const int acc_cols = ((q.x3 && q.bn <= 128) ? 2 : 1) * ceil_div(q.bn, 32) * 32;
+    if (split == 1 && !q.no_persistent && 2 * acc_cols <= 512) {
+        const int staging = ceil_div(q.bn, slab_channels) * kATileBytes;
+        const int fixed = staging + 24 * 8 + 64 + 1024;
+        const int resident = (4 * acc_cols <= 512 && 2 * stage_bytes + fixed <= 110 * 1024) ? 2 : 1;
+        if (base > sms * resident && 2 * stage_bytes + fixed <= 210 * 1024) {
+            q.persistent = 1;
+            q.grid_ctas = sms * resident;
+            const int budget = (resident == 2 ? 110 : 210) * 1024;
+            q.stages = std::max(2, std::min(8, (budget - fixed) / stage_bytes));
+            if (q.stages == 5 || q.stages == 7) --q.stages;
+            q.smem_bytes = size_t(q.stages) * stage_bytes + fixed;
+            // a CTA that must have the SM's TMEM to itself also takes more than half of its shared memory,
+            // so that no second CTA can be placed beside it only to wait for TMEM
+            if (resident == 1) q.smem_bytes = std::max(q.smem_bytes, size_t(120 * 1024));
+        }
+    }
     const bool through_workspace = split > 1 && !q.cluster;
     q.workspace_bytes = through_workspace ? size_t(base) * split * q.bn * kTileM * sizeof(float) : 0;
     q.counter_bytes = through_workspace ? size_t(base) * sizeof(unsigned int) : 0;
@@ -1133,7 +1476,9 @@ const char *conv_tc_encode_dense_weights(const ConvTcParams &p, ConvTcPlan *plan
 }
 
 cudaError_t conv_tc_prepare() {
-    return cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024);
+    cudaError_t err = cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024);
+    if (err != cudaSuccess) return err;
+    return cudaFuncSetAttribute(conv_tc_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024);
 }
 
 void launch_conv_tc(const ConvTcParams &p, const ConvTcPlan &q, cudaStream_t stream) {
@@ -1163,8 +1508,21 @@ void launch_conv_tc(const ConvTcParams &p, const ConvTcPlan &q, cudaStream_t str
     t.tma_store = q.tma_store;
     t.cluster = (q.split_k > 1 && q.cluster) ? 1 : 0;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(q.tiles_w * q.tiles_h * q.tiles_n, q.n_tiles, q.split_k);
-    cfg.blockDim = dim3(kThreads);
+    PersistGeom pg = {};
+    if (q.persistent) {
+        pg.n_tiles = q.n_tiles;
+        pg.total_tiles = q.tiles_w * q.tiles_h * q.tiles_n * q.n_tiles;
+        pg.staging_off = q.stages * (q.x3 ? 2 : 1) * (kATileBytes + q.bn * kRowBytes);
+        pg.acc_stride = (t.wide ? 2 : 1) * ceil_div(q.bn, 32) * 32;
+        cols = 32;
+        while (cols < 2 * pg.acc_stride) cols *= 2;
+        t.tmem_cols = cols;
+        cfg.gridDim = dim3(std::min(q.grid_ctas, pg.total_tiles));
+        cfg.blockDim = dim3(kPersistThreads);
+    } else {
+        cfg.gridDim = dim3(q.tiles_w * q.tiles_h * q.tiles_n, q.n_tiles, q.split_k);
+        cfg.blockDim = dim3(kThreads);
+    }
     cfg.dynamicSmemBytes = q.smem_bytes;
     cfg.stream = stream;
     // programmatic dependent launch: this kernel's prologue may overlap the tail of its predecessor
@@ -1184,6 +1542,11 @@ void launch_conv_tc(const ConvTcParams &p, const ConvTcPlan &q, cudaStream_t str
     }
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
+    if (q.persistent) {
+        cudaLaunchKernelEx(&cfg, conv_tc_persistent_kernel, *reinterpret_cast<const CUtensorMap *>(q.tmap_a),
+                           *reinterpret_cast<const CUtensorMap *>(q.tmap_b), *reinterpret_cast<const CUtensorMap *>(q.tmap_c), p, t, pg);
+        return;
+    }
     cudaLaunchKernelEx(&cfg, conv_tc_kernel, *reinterpret_cast<const CUtensorMap *>(q.tmap_a),
                        *reinterpret_cast<const CUtensorMap *>(q.tmap_b), *reinterpret_cast<const CUtensorMap *>(q.tmap_c), p, t);
 }

@@ -106,6 +106,9 @@ struct ConvTcPlan {
     int split_k;                   // CTAs sharing one output tile
     int stages;                    // smem pipeline depth
     int flat_1x1;                  // 1: pixels flattened into one axis (1x1, stride 1, no padding)
+    int persistent;                // 1: CTAs stay resident and walk the tiles (grids of several waves, split_k == 1)
+    int grid_ctas;                 // CTAs launched
+    int no_persistent;             // testing aid: never use the persistent kernel
     int max_producers;             // testing aid: cap on the lanes that issue TMA loads (0: the default, 4)
     int im2col;                    // 1: pixels flattened into one axis, activations fetched by im2col-mode TMA
     int x3;                        // 1: three-pass TF32 (operands split into value + residual)

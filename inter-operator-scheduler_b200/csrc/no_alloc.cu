@@ -111,6 +111,7 @@ extern "C" int ios_pointwise_conv_static_scratch(const float *x, const float *w,
     g.round_out = 0;
 
     ConvTcPlan plan = {};
+    plan.no_persistent = 1;                             // this entry point exists for the kernel that uses the scratch
     conv_tc_choose(g, dev->sm_count, 1, /*three_pass=*/false, &plan);
     plan.cluster = 0;                                   // reduce through the (static) workspace, not a cluster
     conv_tc_set_split(&plan, split_k > 0 ? split_k : plan.split_k);

@@ -389,12 +389,13 @@ private:
             slot.weight_bytes = size_t(op.kh) * op.kw * ((op.C + 3) / 4 * 4) * sizeof(float);   // rows padded to 4
         } else if (tc_wanted && conv_tc_supported(in, g)) {
             slot.impl = StepKind::ConvTc;
+            slot.tcplan.no_persistent = plan_.options.no_persistent ? 1 : 0;
             conv_tc_choose(g, sms_, width_, plan_.options.three_pass, &slot.tcplan, plan_.options.force_bn, plan_.options.bf16,
                            !plan_.options.no_im2col);
             if (plan_.options.force_split_k > 0) conv_tc_set_split(&slot.tcplan, plan_.options.force_split_k);
             slot.tcplan.pdl = plan_.options.pdl ? 1 : 0;
             slot.tcplan.max_producers = plan_.options.producers;
-            if (plan_.options.force_stages > 0) {           // testing aid: shallower pipeline
+            if (plan_.options.force_stages > 0 && !slot.tcplan.persistent) {   // testing aid: shallower pipeline
                 ConvTcPlan &q = slot.tcplan;
                 const size_t stage_bytes = (q.smem_bytes - 24 * q.stages - 64 - 1024) / q.stages;
                 const int stages = std::max(2, std::min(q.stages, plan_.options.force_stages));

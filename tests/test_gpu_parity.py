@@ -31,6 +31,7 @@ def default_options():
     rt.set_option('conv', 'auto')
     rt.set_option('split_k', '0')
     rt.set_option('im2col', '1')
+    rt.set_option('persistent', '1')
     yield
 
 
@@ -78,6 +79,26 @@ def test_conv_tensor_core_vs_oracle(shape, im2col):
     assert _conv_case(shape, 'tensor') <= TOL_FP32          # three-pass TF32: fp32-grade
     assert _conv_case(shape, 'tensor1') <= TOL_TF32         # single-pass TF32
     assert _conv_case(shape, 'bf16') <= TOL_BF16            # bfloat16 operands
+
+
+# more pixel tiles than CTAs fit at once: resident CTAs walk the tiles, two accumulators in TMEM
+PERSISTENT_SHAPES = [
+    (4, 32, 150, 150, 32, 3, 3, 1, 1, 0, 0, 1),     # 685 tiles of 9 (bf16: 9) K steps
+    (16, 32, 57, 57, 16, 1, 1, 1, 1, 0, 0, 1),      # one K step per tile: fewer steps than producer lanes
+    (8, 64, 35, 35, 200, 1, 1, 1, 1, 0, 0, 1),      # several output-channel tiles, 16-byte aligned ragged Cout
+    (8, 40, 35, 35, 90, 3, 3, 2, 2, 1, 1, 1),       # Cout not a multiple of 4: results leave through plain stores
+    (40, 96, 17, 17, 256, 1, 7, 1, 1, 0, 3, 1),     # wide tiles (one CTA per SM where they need all of TMEM)
+    (2, 3, 299, 299, 32, 3, 3, 2, 2, 0, 0, 1),      # Inception stem
+]
+
+
+@pytest.mark.parametrize('persistent', ['1', '0'])
+@pytest.mark.parametrize('shape', PERSISTENT_SHAPES)
+def test_conv_many_tiles_vs_oracle(shape, persistent):
+    rt.set_option('persistent', persistent)
+    assert _conv_case(shape, 'tensor') <= TOL_FP32
+    assert _conv_case(shape, 'tensor1') <= TOL_TF32
+    assert _conv_case(shape, 'bf16') <= TOL_BF16
 
 
 @pytest.mark.parametrize('shape', TC_SHAPES[:6] + [
