@@ -30,6 +30,8 @@
 // (reference src/ios/ios_runtime.cu:313-331) and the algorithm search of :150-205.
 #include "kernels.h"
 
+#include <type_traits>
+
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cstdio>
@@ -447,6 +449,16 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // Warps 0 and 1 work through a few lanes only.  Their other lanes leave now: a lane that spins on a
     // barrier pays about 50 cycles per wait while the rest of its warp is parked at the reconvergence point.
     // (Not in a cluster: there every thread takes part in the cluster barriers below.)
+    // Weights never depend on the previous kernel: the weight tiles of the first `stages` K steps are
+    // requested before the grid dependency is waited for, so that under programmatic dependent launch
+    // their latency hides behind the predecessor's tail -- one lane per stage, all at once.
+    if (warp == 0 && lane < min(n_it, t.stages)) {
+        const uint32_t stage = smem_base + uint32_t(lane) * stage_bytes;
+        const uint32_t bar = full0 + 8u * lane;
+        mbar_expect_tx(bar, uint32_t(t.a_bytes + passes * b_bytes));
+        tma_load_2d(stage + b_off, &tmap_b, bar, (it_begin + lane) * t.chunk, cout0);
+        if (t.x3) tma_load_2d(stage + b_lo_off, &tmap_b, bar, (it_begin + lane) * t.chunk, t.cout_pad + cout0);
+    }
     if (!t.cluster && ((warp == 0 && lane >= t.producers) || (warp == 1 && lane != 0))) return;
 
     if (warp == 0) {
@@ -455,19 +467,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             // One thread gets through wait -> arm -> issue about once per 600-800 cycles, whatever the
             // tiles' size, so `producers` lanes share the K steps: lane l serves steps l, l + P, ... and,
             // P dividing the pipeline depth, owns stages l, l + P, ... for itself.
-            // Weights never depend on the previous kernel: the weight tiles of the first `stages` K steps
-            // are requested before the grid dependency is waited for, so that under programmatic dependent
-            // launch their latency hides behind the predecessor's tail.  Activations follow after the wait.
+            // (the weight tiles of the first `stages` K steps are on their way already)  Activations follow
+            // after the grid dependency.
             const int P = t.producers;
             const int early = min(n_it, t.stages);
-#pragma unroll 1
-            for (int i = lane; i < early; i += P) {
-                const uint32_t stage = smem_base + uint32_t(i) * stage_bytes;
-                const uint32_t bar = full0 + 8u * i;
-                mbar_expect_tx(bar, uint32_t(t.a_bytes + passes * b_bytes));
-                tma_load_2d(stage + b_off, &tmap_b, bar, (it_begin + i) * t.chunk, cout0);
-                if (t.x3) tma_load_2d(stage + b_lo_off, &tmap_b, bar, (it_begin + i) * t.chunk, t.cout_pad + cout0);
-            }
             asm volatile("griddepcontrol.wait;" ::: "memory");
             bool ok = true;
             int next = lane;            // this lane's first K step whose activation tile is not requested yet
@@ -591,17 +594,20 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const int tile_id = m_tile * gridDim.y + n_tile;
         bool finisher = true;
         if (t.split_k > 1 && t.cluster) {
-            // cluster reduction: park this CTA's partial tile in its own shared memory, [row][bn + 4] floats
+            // cluster reduction: this CTA's partial tile goes to the workspace as ws[tile][split][column quad][row]
+            // (float4 units; a warp writes 512 contiguous bytes).  It stays in L2: the CTAs of the cluster read it
+            // back right after the cluster barrier below.  (Loads from another CTA's shared memory were measured
+            // at a few bytes per cycle here, several times slower than this round trip through L2.)
             finisher = false;
             if (ok) {
-                float *part = reinterpret_cast<float *>(generic_base) + size_t(row) * (t.bn + 4);
+                float4 *ws = reinterpret_cast<float4 *>(p.workspace) + (size_t(tile_id) * t.split_k + split) * size_t(t.bn >> 2) * kTileM + row;
 #pragma unroll 1
                 for (int c = 0; c < t.bn; c += 32) {
                     float v[32];
                     acc_ld32(taddr + c, pair, v);
 #pragma unroll
                     for (int j = 0; j < 32; j += 4)
-                        *reinterpret_cast<float4 *>(part + c + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                        ws[size_t((c + j) >> 2) * kTileM] = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
                 }
             }
             if (threadIdx.x == 64) STAMP(6);
@@ -733,45 +739,38 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         tc_fence_before();
     }
     if (t.split_k > 1 && t.cluster) {
-        // Every thread of every CTA of the cluster passes both barriers, whatever happened before.
-        cluster_sync_all();                                   // all partial tiles are parked
+        // Every thread of every CTA of the cluster passes this barrier, whatever happened before; its
+        // release / acquire pair makes the partial tiles written above visible to the cluster.
+        cluster_sync_all();
+        if (threadIdx.x == 64) STAMP(10);
         if (warp >= 2) {
+            // CTA r of the cluster finishes rows [r*128/S, (r+1)*128/S) of the tile: it adds the S partial
+            // tiles in split order (so the result does not depend on timing), applies bias and activation
+            // and writes its rows.  A thread puts all its loads in flight before it adds anything.
             const int tid = threadIdx.x - 64;
-            const uint32_t rank = cluster_cta_rank();
-            const int r0 = int(rank) * kTileM / t.split_k, r1 = int(rank + 1) * kTileM / t.split_k;
+            const int rank = int(cluster_cta_rank());
+            const int r0 = rank * kTileM / t.split_k, r1 = (rank + 1) * kTileM / t.split_k;
+            const int rows = r1 - r0;
             const int quads = t.bn >> 2;
             const int valid = min(t.bn, g.Cout - cout0);
-            const int n_items = (r1 - r0) * quads;
-#pragma unroll 1
-            for (int item = tid; item < n_items; item += 128) {
-                const int row = r0 + item / quads;
-                const int c = (item - (row - r0) * quads) << 2;
-                long pix_off = -1;
+            const int n_items = rows * quads;
+            const int tile_id = m_tile * gridDim.y + n_tile;
+            const float4 *ws_tile = reinterpret_cast<const float4 *>(p.workspace) + size_t(tile_id) * t.split_k * size_t(quads) * kTileM;
+            // offset of the output pixel held by tile row `row`, or -1
+            auto pixel_offset = [&](int row) -> long {
                 if (t.flat) {
                     const long pix = long(ow0) + row;
-                    if (row < t.box_w && pix < long(g.N) * g.OH * g.OW) pix_off = pix * p.out.pitch;
-                } else {
-                    const int ww = row % t.box_w;
-                    const int hh = (row / t.box_w) % t.box_h;
-                    const int im = row / (t.box_w * t.box_h);
-                    const int ow = ow0 + ww, oh = oh0 + hh, n = n0 + im;
-                    if (im < t.box_n && ow < g.OW && oh < g.OH && n < g.N)
-                        pix_off = ((long(n) * g.OH + oh) * g.OW + ow) * p.out.pitch;
+                    return (row < t.box_w && pix < long(g.N) * g.OH * g.OW) ? pix * p.out.pitch : -1;
                 }
-                if (pix_off < 0 || c >= valid) continue;
-                const uint32_t local = smem_base + uint32_t((row * (t.bn + 4) + c) * 4);
-                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 1
-                for (int sp = 0; sp < t.split_k; sp += 4) {
-                    float4 part[4];
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) part[u] = ld_cluster_f4(map_to_cta(local, uint32_t(min(sp + u, t.split_k - 1))));
-#pragma unroll
-                    for (int u = 0; u < 4; ++u)
-                        if (sp + u < t.split_k) {
-                            acc.x += part[u].x; acc.y += part[u].y; acc.z += part[u].z; acc.w += part[u].w;
-                        }
-                }
+                const int ww = row % t.box_w;
+                const int hh = (row / t.box_w) % t.box_h;
+                const int im = row / (t.box_w * t.box_h);
+                const int ow = ow0 + ww, oh = oh0 + hh, n = n0 + im;
+                return (im < t.box_n && ow < g.OW && oh < g.OH && n < g.N) ? ((long(n) * g.OH + oh) * g.OW + ow) * p.out.pitch : -1;
+            };
+            auto finish = [&](int row, int c, float4 acc) {
+                const long pix_off = pixel_offset(row);
+                if (pix_off < 0 || c >= valid) return;
                 float o[4] = {acc.x, acc.y, acc.z, acc.w};
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -779,10 +778,53 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     o[j] = t.round_tf32 ? round_tf32(z) : z;
                 }
                 store4_direct(p.out.ptr, t.bf16, pix_off + cout0 + c, make_float4(o[0], o[1], o[2], o[3]), valid - c);
+            };
+            auto reduce = [&](auto split_tag) {
+                constexpr int S = decltype(split_tag)::value;
+                constexpr int kItems = 16 / S;
+#pragma unroll 1
+                for (int first = tid; first < n_items; first += 128 * kItems) {
+                    float4 part[kItems][S];
+#pragma unroll
+                    for (int k = 0; k < kItems; ++k) {
+                        const int item = min(first + k * 128, n_items - 1);
+                        const int q4 = item / rows;
+                        const float4 *src = ws_tile + size_t(q4) * kTileM + r0 + (item - q4 * rows);
+#pragma unroll
+                        for (int sp = 0; sp < S; ++sp) part[k][sp] = __ldcg(src + size_t(sp) * quads * kTileM);
+                    }
+#pragma unroll
+                    for (int k = 0; k < kItems; ++k) {
+                        const int item = first + k * 128;
+                        if (item >= n_items) break;
+                        const int q4 = item / rows;
+                        float4 acc = part[k][0];
+#pragma unroll
+                        for (int sp = 1; sp < S; ++sp) {
+                            acc.x += part[k][sp].x; acc.y += part[k][sp].y; acc.z += part[k][sp].z; acc.w += part[k][sp].w;
+                        }
+                        finish(r0 + (item - q4 * rows), q4 << 2, acc);
+                    }
+                }
+            };
+            if (t.split_k == 8) reduce(std::integral_constant<int, 8>());
+            else if (t.split_k == 4) reduce(std::integral_constant<int, 4>());
+            else if (t.split_k == 2) reduce(std::integral_constant<int, 2>());
+            else
+#pragma unroll 1
+            for (int item = tid; item < n_items; item += 128) {
+                const int q4 = item / rows;
+                const float4 *src = ws_tile + size_t(q4) * kTileM + r0 + (item - q4 * rows);
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+                for (int sp = 0; sp < t.split_k; ++sp) {
+                    const float4 x = __ldcg(src + size_t(sp) * quads * kTileM);
+                    acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+                }
+                finish(r0 + (item - q4 * rows), q4 << 2, acc);
             }
             if (threadIdx.x == 64) STAMP(7);
         }
-        cluster_sync_all();                                   // nobody leaves while its tile may still be read
     }
     if (warp < 2) return;       // the producer lanes and the MMA issuer have nothing left to do
     // warps 0 and 1 are gone by now or on their way out; the warps that read the accumulator free it
@@ -1299,11 +1341,8 @@ void conv_tc_set_split(ConvTcPlan *plan, int split) {
     }
     if (q.stages == 5 || q.stages == 7) --q.stages;    // a depth that 2, 3 or 4 producer lanes can share evenly
     if (split > 8) q.cluster = 0;          // larger splits go through the global workspace
-    // the store staging needs one 16 KiB slab per 32 output channels inside the pipeline buffers,
-    // the cluster reduction one [128][bn + 4] float tile
+    // the store staging needs one 16 KiB slab per 32 output channels inside the pipeline buffers
     while (q.stages * stage_bytes < ceil_div(q.bn, slab_channels) * kATileBytes) ++q.stages;
-    if (split > 1 && q.cluster)
-        while (size_t(q.stages) * stage_bytes < size_t(kTileM) * (q.bn + 4) * sizeof(float)) ++q.stages;
     q.smem_bytes = size_t(q.stages) * stage_bytes + 24 * q.stages + 64 + 1024;
     // More tiles than CTAs that fit at once: persistent CTAs with two accumulators in TMEM, the store
     // staging in an area of its own behind the pipeline stages.
@@ -1327,9 +1366,10 @@ void conv_tc_set_split(ConvTcPlan *plan, int split) {
             if (resident == 1) q.smem_bytes = std::max(q.smem_bytes, size_t(120 * 1024));
         }
     }
-    const bool through_workspace = split > 1 && !q.cluster;
-    q.workspace_bytes = through_workspace ? size_t(base) * split * q.bn * kTileM * sizeof(float) : 0;
-    q.counter_bytes = through_workspace ? size_t(base) * sizeof(unsigned int) : 0;
+    // partial tiles meet in a workspace (one region per tile and split); splits of more than 8, which no
+    // cluster covers, also need an arrival counter per tile
+    q.workspace_bytes = split > 1 ? size_t(base) * split * q.bn * kTileM * sizeof(float) : 0;
+    q.counter_bytes = (split > 1 && !q.cluster) ? size_t(base) * sizeof(unsigned int) : 0;
 }
 
 static uint16_t bf16_round_host(float v) {

@@ -47,6 +47,12 @@ public:
         counter_cursor_ = plan_.zero_begin;
         counter_end_ = plan_.zero_begin + (dry_ ? 0 : plan_.zero_bytes);
         counter_total_ = 0;
+        // split-K workspaces: group j of every stage runs on stream j, one kernel after another, so the
+        // convolutions of a group slot share one region, sized by the dry pass
+        ws_need_.assign(plan_.group_workspace_bytes.size(), 0);
+        ws_offset_.clear();
+        if (!dry_)
+            for (size_t bytes : plan_.group_workspace_bytes) ws_offset_.push_back(alloc(bytes));
 
         size_t in_floats = 0;
         for (int idx : m_.placeholders) {
@@ -65,7 +71,7 @@ public:
         place_concats();
 
         plan_.max_groups = 1;
-        plan_.workspace_bytes = 0;
+        if (dry_) plan_.workspace_bytes = 0;
         for (size_t s = 0; s < m_.stages.size(); ++s) {
             const auto &stage = m_.stages[s];
             plan_.max_groups = std::max(plan_.max_groups, int(stage.size()));
@@ -79,7 +85,11 @@ public:
         plan_.launches_per_forward = int(plan_.steps.size());
         if (dry_) {
             plan_.zero_bytes = counter_total_;
-            plan_.arena_bytes = align_up(cursor_ + counter_total_ + kAlign, 4096);
+            plan_.group_workspace_bytes = ws_need_;
+            size_t ws_total = 0;
+            for (size_t bytes : ws_need_) ws_total += align_up(bytes, kAlign) + kAlign;
+            plan_.workspace_bytes = ws_total;
+            plan_.arena_bytes = align_up(cursor_ + counter_total_ + ws_total + kAlign, 4096);
         }
     }
 
@@ -90,6 +100,7 @@ private:
     bool dry_;
     int sms_;
     size_t cursor_ = 0, counter_cursor_ = 0, counter_end_ = 0, counter_total_ = 0;
+    std::vector<size_t> ws_need_, ws_offset_;     // split-K workspace per group slot: bytes needed (dry pass), arena offset
     int stage_ = 0, group_ = 0, width_ = 1;
     int esize_ = 4, per16_ = 4;
     std::vector<bool> placed_, has_tensor_;
@@ -424,8 +435,14 @@ private:
             s.tc.counters = nullptr;
             s.tc.timeline = plan_.options.timeline ? reinterpret_cast<long long *>(at(plan_.error_flag_offset) + 16) : nullptr;
             if (slot.tcplan.split_k > 1) {
-                s.tc.workspace = at(alloc(slot.tcplan.workspace_bytes));
-                plan_.workspace_bytes += slot.tcplan.workspace_bytes;
+                if (dry_) {
+                    if (ws_need_.size() <= size_t(group_)) ws_need_.resize(group_ + 1, 0);
+                    ws_need_[group_] = std::max(ws_need_[group_], slot.tcplan.workspace_bytes);
+                } else {
+                    if (size_t(group_) >= ws_offset_.size() || plan_.group_workspace_bytes[group_] < slot.tcplan.workspace_bytes)
+                        throw std::runtime_error("internal: split-K workspace of a group slot is too small");
+                    s.tc.workspace = reinterpret_cast<float *>(at(ws_offset_[group_]));
+                }
                 counter_total_ += align_up(slot.tcplan.counter_bytes, 16);
                 if (!dry_) {
                     s.tc.counters = reinterpret_cast<unsigned int *>(at(counter_cursor_));

@@ -74,6 +74,7 @@ struct Plan {
     size_t staging_in_offset = 0, staging_out_offset = 0;   // NCHW staging for host transfers
     size_t error_flag_offset = 0;
     size_t workspace_bytes = 0;
+    std::vector<size_t> group_workspace_bytes;   // split-K workspace shared by the convolutions of each group slot
     bool input_round_tf32 = false;
     int launches_per_forward = 0;
     int max_groups = 1;
