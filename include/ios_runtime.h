@@ -81,6 +81,7 @@ IOS_API const char *ios_last_error(void);
  *                  waits only for the groups that produced its inputs)
  * Testing aids (each switches one mechanism of the tensor-core convolution off or pins one choice):
  * "im2col" "1"/"0" (pixel tiles over the flattened pixel axis by im2col-mode loads / boxes of the image),
+ * "stem" "1"/"0" (a convolution over at most 4 input channels runs on CUDA cores / on the tensor cores like the rest),
  * "persistent" "1"/"0" (grids of several waves run as resident CTAs that walk the tiles / one CTA per tile),
  * "bulk_store" "1"/"0" (results leave through a bulk tensor store / straight from registers),
  * "split_k", "bn", "stages", "producers" (a positive number overrides the K split, the output-channel tile

@@ -11,18 +11,20 @@
 
 #include <cuda_bf16.h>
 
+#include <algorithm>
 #include <cstring>
 
 namespace ios {
 namespace {
 
+// sigmoid / tanh are rare; inlined, their code would be executed under predication by every thread
+__device__ __noinline__ float act_slow(float v, int act) {
+    return act == 2 ? 1.0f / (1.0f + __expf(-v)) : tanhf(v);
+}
 __device__ __forceinline__ float act_only(float v, int act) {
-    switch (act) {
-        case 1: return fmaxf(v, 0.0f);
-        case 2: return 1.0f / (1.0f + __expf(-v));
-        case 3: return tanhf(v);
-        default: return v;
-    }
+    if (act == 1) return fmaxf(v, 0.0f);
+    if (act == 0) return v;
+    return act_slow(v, act);
 }
 __device__ __forceinline__ float to_tf32(float v) {
     uint32_t r;
@@ -104,6 +106,150 @@ __global__ void __launch_bounds__(128) conv_direct_kernel(const ConvDirectParams
     }
 }
 
+// ---- few input channels (the 3-channel stem of every network) ---------------------------------
+// With 3 input channels an implicit-GEMM K step is one filter tap of a 128-byte row that is 90 %
+// padding, and the layer is bound by the bytes it writes, not by a contraction.  Here a thread owns
+// CG output channels (32 if Cout allows) of 2 output pixels: per tap it reads each pixel once (16
+// bytes) and every weight as part of a float4 broadcast from shared memory, so that four of five
+// instructions are multiply-adds.  The filter sits in shared memory as [tap][cin][CG/4][Cout/CG]
+// float4 -- the threads of one pixel, which differ in their channel group, read neighbouring words --
+// and the threads of a pixel together write its channels as one contiguous span.  Products and sums
+// are float32.  KH, KW: the window if known at compile time (3x3: fully unrolled), else 0; kPadded:
+// windows may reach outside the image.
+template <typename T, int CG, int PX, int KH, int KW, bool kPadded>
+__global__ void __launch_bounds__(128, 4) conv_few_channels_kernel(const ConvDirectParams p, int pixels_per_block) {
+    extern __shared__ float4 w_s4[];
+    constexpr int Q = CG / 4;
+    const ConvGeom &g = p.g;
+    const int kh = KH ? KH : g.kh, kw = KW ? KW : g.kw;
+    const int groups = g.Cout / CG;
+    {
+        // global [tap][cin][Cout] -> shared [tap][cin][k][group] float4, Cout index = group * CG + 4 k + e
+        const int n4 = (kh * kw * g.Cin * g.Cout) >> 2;
+        const float4 *src = reinterpret_cast<const float4 *>(p.weight);
+        const int per_row = g.Cout >> 2;
+        for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+            const int row = i / per_row, co4 = i - row * per_row;      // row = tap * Cin + cin
+            const int j = co4 / Q, k = co4 - j * Q;
+            w_s4[(row * Q + k) * groups + j] = src[i];
+        }
+    }
+    __syncthreads();
+    const int j = threadIdx.x % groups, lp = threadIdx.x / groups;
+    const int per_image = g.OH * g.OW;
+    const int total = g.N * per_image;
+    const T *in = p.in.as<const T>();
+    T *out = p.out.as<T>();
+    const int row_step = g.W * p.in.pitch;              // elements from one input row to the next
+    const float4 *wj = w_s4 + j;
+    // PX pixels per thread, pixels_per_block apart: they share every weight load
+    for (int pix0 = blockIdx.x * PX * pixels_per_block + lp; pix0 < total; pix0 += gridDim.x * PX * pixels_per_block) {
+        const T *corner[PX];                             // input pixel under the window's first tap
+        int h0[PX], w0[PX];
+        bool live[PX];
+#pragma unroll
+        for (int u = 0; u < PX; ++u) {
+            const int pix = pix0 + u * pixels_per_block;
+            live[u] = pix < total;
+            const int pc = live[u] ? pix : pix0;
+            const int n = pc / per_image;
+            const int rem = pc - n * per_image;
+            const int oh = rem / g.OW;
+            h0[u] = oh * g.sh - g.ph;
+            w0[u] = (rem - oh * g.OW) * g.sw - g.pw;
+            corner[u] = in + (size_t(n) * g.H + h0[u]) * row_step + w0[u] * p.in.pitch;
+        }
+        float acc[PX][CG];
+#pragma unroll
+        for (int u = 0; u < PX; ++u)
+#pragma unroll
+            for (int e = 0; e < CG; ++e) acc[u][e] = 0.0f;
+        auto tap = [&](int r, int s) {
+            float x[PX][4];
+#pragma unroll
+            for (int u = 0; u < PX; ++u) {
+                const bool inside = !kPadded || (h0[u] + r >= 0 && h0[u] + r < g.H && w0[u] + s >= 0 && w0[u] + s < g.W);
+                const float4 v = inside ? load4(corner[u] + r * row_step + s * p.in.pitch) : make_float4(0.f, 0.f, 0.f, 0.f);
+                x[u][0] = v.x; x[u][1] = v.y; x[u][2] = v.z; x[u][3] = v.w;
+            }
+            const float4 *wt = wj + (r * kw + s) * g.Cin * Q * groups;
+            // channels beyond Cin are padding of the pixel pitch and never enter a product
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                if (c < g.Cin) {
+#pragma unroll
+                    for (int k = 0; k < Q; ++k) {
+                        const float4 wv = wt[(c * Q + k) * groups];
+#pragma unroll
+                        for (int u = 0; u < PX; ++u) {
+                            acc[u][4 * k + 0] = fmaf(x[u][c], wv.x, acc[u][4 * k + 0]);
+                            acc[u][4 * k + 1] = fmaf(x[u][c], wv.y, acc[u][4 * k + 1]);
+                            acc[u][4 * k + 2] = fmaf(x[u][c], wv.z, acc[u][4 * k + 2]);
+                            acc[u][4 * k + 3] = fmaf(x[u][c], wv.w, acc[u][4 * k + 3]);
+                        }
+                    }
+                }
+            }
+        };
+        if (KH && KW) {
+#pragma unroll
+            for (int r = 0; r < (KH ? KH : 1); ++r)
+#pragma unroll
+                for (int s = 0; s < (KW ? KW : 1); ++s) tap(r, s);
+        } else {
+#pragma unroll 1
+            for (int r = 0; r < kh; ++r)
+#pragma unroll 1
+                for (int s = 0; s < kw; ++s) tap(r, s);
+        }
+        const float *bias = p.bias ? p.bias + j * CG : nullptr;
+#pragma unroll
+        for (int u = 0; u < PX; ++u) {
+            if (!live[u]) continue;
+            T *dst = out + size_t(pix0 + u * pixels_per_block) * p.out.pitch + j * CG;
+#pragma unroll
+            for (int k = 0; k < Q; ++k) {
+                const float4 b = bias ? *reinterpret_cast<const float4 *>(bias + 4 * k) : make_float4(0.f, 0.f, 0.f, 0.f);
+                float4 o;
+                o.x = act_apply(acc[u][4 * k + 0] + b.x, g.act); o.y = act_apply(acc[u][4 * k + 1] + b.y, g.act);
+                o.z = act_apply(acc[u][4 * k + 2] + b.z, g.act); o.w = act_apply(acc[u][4 * k + 3] + b.w, g.act);
+                store4(dst + 4 * k, o);
+            }
+        }
+    }
+}
+
+template <typename T, int CG, int PX>
+void launch_few_channels_cg(const ConvDirectParams &p, cudaStream_t stream) {
+    const ConvGeom &g = p.g;
+    const int groups = g.Cout / CG;
+    const int pixels_per_block = std::max(1, 128 / groups);
+    const size_t smem = size_t(g.kh) * g.kw * g.Cin * g.Cout * sizeof(float);
+    const long spans = (long(g.N) * g.OH * g.OW + PX * pixels_per_block - 1) / (PX * pixels_per_block);
+    const int grid = int(std::min<long>(spans, 148L * 16));
+    const int threads = groups * pixels_per_block;
+    const bool padded = g.ph > 0 || g.pw > 0 || (g.OH - 1) * g.sh + g.kh > g.H || (g.OW - 1) * g.sw + g.kw > g.W;
+    static bool raised = false;               // filters above 48 KiB need the opt-in limit
+    if (!raised) {
+        cudaFuncSetAttribute(conv_few_channels_kernel<T, CG, PX, 0, 0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        cudaFuncSetAttribute(conv_few_channels_kernel<T, CG, PX, 3, 3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        cudaFuncSetAttribute(conv_few_channels_kernel<T, CG, PX, 3, 3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        raised = true;
+    }
+    if (g.kh == 3 && g.kw == 3 && !padded) conv_few_channels_kernel<T, CG, PX, 3, 3, false><<<grid, threads, smem, stream>>>(p, pixels_per_block);
+    else if (g.kh == 3 && g.kw == 3) conv_few_channels_kernel<T, CG, PX, 3, 3, true><<<grid, threads, smem, stream>>>(p, pixels_per_block);
+    else conv_few_channels_kernel<T, CG, PX, 0, 0, true><<<grid, threads, smem, stream>>>(p, pixels_per_block);
+}
+
+template <typename T>
+void launch_few_channels(const ConvDirectParams &p, cudaStream_t stream) {
+    const int cout = p.g.Cout;
+    if (cout % 32 == 0) launch_few_channels_cg<T, 32, 2>(p, stream);
+    else if (cout % 16 == 0) launch_few_channels_cg<T, 16, 2>(p, stream);
+    else if (cout % 8 == 0) launch_few_channels_cg<T, 8, 2>(p, stream);
+    else launch_few_channels_cg<T, 4, 2>(p, stream);
+}
+
 template <typename T, bool kVec>
 __global__ void __launch_bounds__(256) conv_depthwise_kernel(const ConvDirectParams p) {
     const ConvGeom &g = p.g;
@@ -170,8 +316,20 @@ inline int blocks_for(long work, int threads) {
 
 }  // namespace
 
+bool conv_few_channels_supported(const TensorRef &in, const TensorRef &out, const ConvGeom &g) {
+    const size_t filter_bytes = size_t(g.kh) * g.kw * g.Cin * g.Cout * sizeof(float);
+    return g.groups == 1 && g.Cin <= 4 && !g.pre_relu && g.Cout % 4 == 0 && g.Cout >= 4 && g.Cout <= 512 &&
+           filter_bytes <= 96 * 1024 && in.vec4() && out.vec4() && long(g.N) * g.OH * g.OW < (1l << 30);
+}
+
 void launch_conv_direct(const ConvDirectParams &p, cudaStream_t stream) {
     const ConvGeom &g = p.g;
+    if (conv_few_channels_supported(p.in, p.out, g) && (reinterpret_cast<uintptr_t>(p.weight) & 15) == 0 &&
+        (!p.bias || (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0)) {
+        if (p.in.esize == 2) launch_few_channels<__nv_bfloat16>(p, stream);
+        else launch_few_channels<float>(p, stream);
+        return;
+    }
     const int cout_g = g.Cout / g.groups;
     const long work = long(g.N) * g.OH * g.OW * ((cout_g + kCoPerThread - 1) / kCoPerThread) * g.groups;
     if (p.in.esize == 2) conv_direct_kernel<__nv_bfloat16><<<blocks_for(work, 128), 128, 0, stream>>>(p);

@@ -88,6 +88,9 @@ struct ConvDirectParams {
     ConvGeom g;
 };
 void launch_conv_direct(const ConvDirectParams &p, cudaStream_t stream);
+// Does launch_conv_direct have its fast form for this layer (at most 4 input channels, Cout % 4 == 0,
+// 16-byte aligned pixels)?  Such layers are bound by the bytes they write and are kept off the tensor cores.
+bool conv_few_channels_supported(const TensorRef &in, const TensorRef &out, const ConvGeom &g);
 // Depthwise (groups == Cin == Cout).  Weights: [tap][C rounded up to 4] float32, zero padded.
 void launch_conv_depthwise(const ConvDirectParams &p, cudaStream_t stream);
 

@@ -144,9 +144,18 @@ private:
     }
 
     // ---- which convolutions will run on the tensor cores (by geometry; view alignment is checked later)
+    // A convolution over at most 4 input channels (a network's stem) is bound by the bytes it writes; from
+    // some 150 000 output pixels on (Inception-v3 at batch 7) it is faster on CUDA cores
+    // (launch_conv_direct's form for few input channels: measured 1.5x at batch 64) whatever the precision.
+    // Below that the tensor-core kernel's split over the taps wins.
+    bool few_channels(const Op &op) const {
+        return !plan_.options.no_stem_kernel && op.groups == 1 && op.inC <= 4 && op.C % 4 == 0 &&
+               size_t(op.kh) * op.kw * op.inC * op.C * sizeof(float) <= 96 * 1024 &&
+               long(m_.batch) * op.H * op.W >= 150000;
+    }
     bool tc_candidate(const Op &op) const {
         return op.kind == OpKind::Conv && op.groups == 1 && (plan_.options.tf32 || plan_.options.bf16) && plan_.options.allow_tc &&
-               op.sh <= 8 && op.sw <= 8;
+               op.sh <= 8 && op.sw <= 8 && !few_channels(op);
     }
     // Round a tensor to TF32 when it is stored?  Only if every reader is a tensor-core convolution
     // that takes it unchanged, and it is not the tensor handed back to the caller.

@@ -33,6 +33,7 @@ struct Options {
     int force_bn = 0;           // testing aid: > 0 overrides the output-channel tile width
     int force_stages = 0;       // testing aid: > 0 caps the depth of the shared-memory pipeline
     int producers = 0;          // testing aid: > 0 caps the lanes that issue TMA loads in the convolution kernel
+    bool no_stem_kernel = false; // testing aid: convolutions over at most 4 input channels take the tensor-core kernel too
     bool no_persistent = false; // testing aid: grids of several waves launch one CTA per tile instead of resident CTAs
     bool no_im2col = false;     // testing aid: windows with taps tile the image in boxes instead of the flat pixel axis
     bool no_bulk_store = false; // testing aid: the epilogue stores straight from registers

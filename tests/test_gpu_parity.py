@@ -32,6 +32,7 @@ def default_options():
     rt.set_option('split_k', '0')
     rt.set_option('im2col', '1')
     rt.set_option('persistent', '1')
+    rt.set_option('stem', '1')
     yield
 
 
@@ -76,6 +77,7 @@ TC_SHAPES = [
 @pytest.mark.parametrize('shape', TC_SHAPES)
 def test_conv_tensor_core_vs_oracle(shape, im2col):
     rt.set_option('im2col', im2col)
+    rt.set_option('stem', '0')          # 3-channel shapes take the tensor-core kernel here
     assert _conv_case(shape, 'tensor') <= TOL_FP32          # three-pass TF32: fp32-grade
     assert _conv_case(shape, 'tensor1') <= TOL_TF32         # single-pass TF32
     assert _conv_case(shape, 'bf16') <= TOL_BF16            # bfloat16 operands
@@ -96,9 +98,26 @@ PERSISTENT_SHAPES = [
 @pytest.mark.parametrize('shape', PERSISTENT_SHAPES)
 def test_conv_many_tiles_vs_oracle(shape, persistent):
     rt.set_option('persistent', persistent)
+    rt.set_option('stem', '0')
     assert _conv_case(shape, 'tensor') <= TOL_FP32
     assert _conv_case(shape, 'tensor1') <= TOL_TF32
     assert _conv_case(shape, 'bf16') <= TOL_BF16
+
+
+# at most 4 input channels and many pixels: the CUDA-core kernel that keeps the filter in shared memory
+@pytest.mark.parametrize('shape', [
+    (8, 3, 299, 299, 32, 3, 3, 2, 2, 0, 0, 1),     # Inception stem at batch 8
+    (40, 3, 128, 128, 96, 7, 7, 2, 2, 3, 3, 1),    # 7x7 stride 2 with padding, three channel groups per pixel
+    (20, 1, 100, 90, 8, 5, 3, 1, 2, 2, 1, 1),      # one input channel, uneven window, 8 channels per thread
+    (7, 4, 150, 151, 20, 3, 3, 1, 1, 1, 1, 1),     # four input channels, 4 channels per thread, odd pixel count
+])
+def test_conv_few_input_channels_vs_oracle(shape):
+    for prec in ('tf32x3', 'bf16'):
+        rt.set_option('precision', prec)
+        assert _conv_case(shape, 'auto', act='tanh') <= (TOL_BF16 if prec == 'bf16' else TOL_FP32)
+    rt.set_option('stem', '0')      # the same layer on the tensor cores
+    rt.set_option('precision', 'tf32x3')
+    assert _conv_case(shape, 'auto', act='tanh') <= TOL_FP32
 
 
 @pytest.mark.parametrize('shape', TC_SHAPES[:6] + [
