@@ -281,18 +281,25 @@ __device__ __forceinline__ void stage4(uint8_t *staging, int row, int cc, float4
         *reinterpret_cast<uint2 *>(staging + size_t(cc >> 6) * kATileBytes + sw128_offset(row, (cc & 63) >> 3) + ((cc & 7) << 1)) = raw;
     }
 }
-// Store up to four finished values straight to the output window at element offset `at`.
+// Store up to four finished values straight to the output window at element offset `at`.  The whole,
+// aligned group is the common case; everything else goes element by element, out of line.
+__device__ __noinline__ void store_some_direct(void *out, int bf16, long at, float4 o, int count) {
+    const float v[4] = {o.x, o.y, o.z, o.w};
+    if (!bf16) {
+        float *dst = static_cast<float *>(out) + at;
+        for (int j = 0; j < 4; ++j)
+            if (j < count) dst[j] = v[j];
+    } else {
+        __nv_bfloat16 *dst = static_cast<__nv_bfloat16 *>(out) + at;
+        for (int j = 0; j < 4; ++j)
+            if (j < count) dst[j] = __float2bfloat16_rn(v[j]);
+    }
+}
 __device__ __forceinline__ void store4_direct(void *out, int bf16, long at, float4 o, int count) {
     if (!bf16) {
         float *dst = static_cast<float *>(out) + at;
-        if (count >= 4 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-            *reinterpret_cast<float4 *>(dst) = o;
-        } else {
-            const float v[4] = {o.x, o.y, o.z, o.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-                if (j < count) dst[j] = v[j];
-        }
+        if (count >= 4 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) *reinterpret_cast<float4 *>(dst) = o;
+        else store_some_direct(out, bf16, at, o, count);
     } else {
         __nv_bfloat16 *dst = static_cast<__nv_bfloat16 *>(out) + at;
         if (count >= 4 && (reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
@@ -302,12 +309,18 @@ __device__ __forceinline__ void store4_direct(void *out, int bf16, long at, floa
             raw.y = *reinterpret_cast<const uint32_t *>(&hi);
             *reinterpret_cast<uint2 *>(dst) = raw;
         } else {
-            const float v[4] = {o.x, o.y, o.z, o.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-                if (j < count) dst[j] = __float2bfloat16_rn(v[j]);
+            store_some_direct(out, bf16, at, o, count);
         }
     }
+}
+// Element offset of the output pixel that row `row` of a boxed (not flattened) pixel tile holds, or -1.
+__device__ __noinline__ long boxed_pixel_offset(int row, int box_w, int box_h, int box_n, int ow0, int oh0, int n0, int N, int OH,
+                                                int OW, int pitch) {
+    const int ww = row % box_w;
+    const int hh = (row / box_w) % box_h;
+    const int im = row / (box_w * box_h);
+    const int ow = ow0 + ww, oh = oh0 + hh, n = n0 + im;
+    return (im < box_n && ow < OW && oh < OH && n < N) ? ((long(n) * OH + oh) * OW + ow) * pitch : -1;
 }
 
 // The MMA issuer's K loop, one copy per operand mode (0: TF32, 1: three-pass TF32, 2: BF16) so that the
@@ -367,15 +380,20 @@ __device__ __forceinline__ bool mma_loop(int n_it, int stages, uint32_t wait0, u
 }
 
 // ---- the kernel ------------------------------------------------------------------------------
+// One instantiation per operand mode (0: TF32, 1: three-pass TF32, 2: BF16) and per reduction form
+// (kCluster: the split_k CTAs of a tile are a cluster): a CTA runs its code once, so what it does not
+// need should not be in its instruction stream.
+template <int MODE, bool kCluster>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ CUtensorMap tmap_c, const ConvTcParams p, const TileGeom t) {
+    constexpr bool kX3 = MODE == 1, kBf16 = MODE == 2;
     extern __shared__ uint8_t smem_raw[];
     __shared__ float bias_s[256];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
     const int b_bytes = t.bn * kRowBytes;
-    const int passes = t.x3 ? 2 : 1;                       // operand planes per stage: value (+ residual)
+    const int passes = kX3 ? 2 : 1;                       // operand planes per stage: value (+ residual)
     const int stage_bytes = passes * (kATileBytes + b_bytes);
     // stage layout: A | A residual | B | B residual
     const uint32_t a_lo_off = kATileBytes;
@@ -457,9 +475,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const uint32_t bar = full0 + 8u * lane;
         mbar_expect_tx(bar, uint32_t(t.a_bytes + passes * b_bytes));
         tma_load_2d(stage + b_off, &tmap_b, bar, (it_begin + lane) * t.chunk, cout0);
-        if (t.x3) tma_load_2d(stage + b_lo_off, &tmap_b, bar, (it_begin + lane) * t.chunk, t.cout_pad + cout0);
+        if (kX3) tma_load_2d(stage + b_lo_off, &tmap_b, bar, (it_begin + lane) * t.chunk, t.cout_pad + cout0);
     }
-    if (!t.cluster && ((warp == 0 && lane >= t.producers) || (warp == 1 && lane != 0))) return;
+    if (!kCluster && ((warp == 0 && lane >= t.producers) || (warp == 1 && lane != 0))) return;
 
     if (warp == 0) {
         if (lane < t.producers) {
@@ -495,7 +513,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     const int kcol = (it_begin + i) * t.chunk;
                     mbar_expect_tx(bar, uint32_t(t.a_bytes + passes * b_bytes));
                     tma_load_2d(stage + b_off, &tmap_b, bar, kcol, cout0);
-                    if (t.x3) tma_load_2d(stage + b_lo_off, &tmap_b, bar, kcol, t.cout_pad + cout0);
+                    if (kX3) tma_load_2d(stage + b_lo_off, &tmap_b, bar, kcol, t.cout_pad + cout0);
                 }
                 if (t.im2col) tma_load_im2col(stage, &tmap_a, bar, cc * t.chunk, im_w, im_h, n0, uint32_t(sx), uint32_t(r));
                 else if (t.flat) tma_load_4d(stage, &tmap_a, bar, cc * t.chunk, ow0, 0, 0);
@@ -528,7 +546,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (lane == 0) {
             // ---------------- MMA issuer ----------------
             // instruction descriptor: fp32 accumulator, A/B format (2 = TF32, 1 = BF16), K-major, N, M
-            const uint32_t fmt = t.bf16 ? 1u : 2u;
+            const uint32_t fmt = kBf16 ? 1u : 2u;
             const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(t.bn >> 3) << 17) | (uint32_t(kTileM >> 4) << 24);
             // three-pass mode: the weight tile and its residual lie behind one another, so one instruction
             // of twice the width forms a_hi*w_hi (columns [0, bn)) and a_hi*w_lo (columns [bn, 2 bn))
@@ -536,8 +554,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             MmaRing ring;
             ring.start(smem_base, a_lo_off, b_off, b_lo_off, stage_bytes);
 #define IOS_MMA_LOOP(MODE, WAIT) mma_loop<MODE>(n_it, t.stages, WAIT, empty0, ring, tmem_base, idesc, idesc_wide, p)
-            const bool ok = t.x3 ? (t.wide ? IOS_MMA_LOOP(3, ready0) : IOS_MMA_LOOP(1, ready0))
-                                 : (t.bf16 ? IOS_MMA_LOOP(2, full0) : IOS_MMA_LOOP(0, full0));
+            const bool ok = kX3 ? (t.wide ? IOS_MMA_LOOP(3, ready0) : IOS_MMA_LOOP(1, ready0))
+                                 : (kBf16 ? IOS_MMA_LOOP(2, full0) : IOS_MMA_LOOP(0, full0));
 #undef IOS_MMA_LOOP
             if (ok) umma_commit(accum_bar);
             else atomicExch(p.error_flag, 2);
@@ -551,7 +569,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         asm volatile("griddepcontrol.wait;" ::: "memory");
         for (int j = tid; j < t.bn; j += 128) bias_s[j] = (p.bias && cout0 + j < g.Cout) ? p.bias[cout0 + j] : 0.0f;
         bool ok = true;
-        if (t.x3) {
+        if (kX3) {
             // The tensor core reads the 19 leading bits of an fp32 operand (sign, exponent, 10 mantissa
             // bits), so the landed activation tile serves as the TF32 value as it is.  What the hardware
             // drops -- x minus x with the low 13 bits cleared, exact in fp32 -- is written to the residual
@@ -593,7 +611,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const uint32_t pair = t.wide ? uint32_t(t.bn) : 0u;
         const int tile_id = m_tile * gridDim.y + n_tile;
         bool finisher = true;
-        if (t.split_k > 1 && t.cluster) {
+        if (kCluster) {
             // cluster reduction: this CTA's partial tile goes to the workspace as ws[tile][split][column quad][row]
             // (float4 units; a warp writes 512 contiguous bytes).  It stays in L2: the CTAs of the cluster read it
             // back right after the cluster barrier below.  (Loads from another CTA's shared memory were measured
@@ -611,7 +629,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 }
             }
             if (threadIdx.x == 64) STAMP(6);
-        } else if (ok && t.split_k > 1) {
+        } else if (!kCluster && ok && t.split_k > 1) {
             // publish this CTA's partial tile: ws[tile][split][col][row], rows contiguous
             float *ws = p.workspace + (size_t(tile_id) * t.split_k + split) * size_t(t.bn) * kTileM;
 #pragma unroll 1
@@ -639,12 +657,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 const long pix = long(ow0) + row;
                 if (row < t.box_w && pix < long(g.N) * g.OH * g.OW) pix_off = pix * p.out.pitch;
             } else {
-                const int ww = row % t.box_w;
-                const int hh = (row / t.box_w) % t.box_h;
-                const int im = row / (t.box_w * t.box_h);
-                const int ow = ow0 + ww, oh = oh0 + hh, n = n0 + im;
-                if (im < t.box_n && ow < g.OW && oh < g.OH && n < g.N)
-                    pix_off = ((long(n) * g.OH + oh) * g.OW + ow) * p.out.pitch;
+                pix_off = boxed_pixel_offset(row, t.box_w, t.box_h, t.box_n, ow0, oh0, n0, g.N, g.OH, g.OW, p.out.pitch);
             }
             const int valid = min(t.bn, g.Cout - cout0);
             const float *ws_tile = p.workspace + size_t(tile_id) * t.split_k * size_t(t.bn) * kTileM;
@@ -664,7 +677,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                             const float z = act_apply(v[j + u] + bias_s[c + j + u], g.act);
                             o[u] = t.round_tf32 ? round_tf32(z) : z;
                         }
-                        stage4(generic_base, row, c + j, make_float4(o[0], o[1], o[2], o[3]), t.bf16);
+                        stage4(generic_base, row, c + j, make_float4(o[0], o[1], o[2], o[3]), kBf16);
                     }
                 }
             } else
@@ -705,7 +718,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     // stage the tile as [slab][row][128 B], swizzled like a TMA box, for the bulk store
 #pragma unroll
                     for (int j = 0; j < 16; j += 4)
-                        stage4(generic_base, row, c + j, make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]), t.bf16);
+                        stage4(generic_base, row, c + j, make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]), kBf16);
                     if (c == 0 && threadIdx.x == 64) STAMP(15);
                     continue;
                 }
@@ -713,7 +726,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
                 for (int j = 0; j < 16; j += 4)
                     if (c + j < valid)
-                        store4_direct(p.out.ptr, t.bf16, pix_off + cout0 + c + j, make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]),
+                        store4_direct(p.out.ptr, kBf16, pix_off + cout0 + c + j, make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]),
                                       valid - (c + j));
             }
             if (threadIdx.x == 64) STAMP(10);
@@ -738,7 +751,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (threadIdx.x == 64) STAMP(7);
         tc_fence_before();
     }
-    if (t.split_k > 1 && t.cluster) {
+    if (kCluster) {
         // Every thread of every CTA of the cluster passes this barrier, whatever happened before; its
         // release / acquire pair makes the partial tiles written above visible to the cluster.
         cluster_sync_all();
@@ -762,11 +775,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     const long pix = long(ow0) + row;
                     return (row < t.box_w && pix < long(g.N) * g.OH * g.OW) ? pix * p.out.pitch : -1;
                 }
-                const int ww = row % t.box_w;
-                const int hh = (row / t.box_w) % t.box_h;
-                const int im = row / (t.box_w * t.box_h);
-                const int ow = ow0 + ww, oh = oh0 + hh, n = n0 + im;
-                return (im < t.box_n && ow < g.OW && oh < g.OH && n < g.N) ? ((long(n) * g.OH + oh) * g.OW + ow) * p.out.pitch : -1;
+                return boxed_pixel_offset(row, t.box_w, t.box_h, t.box_n, ow0, oh0, n0, g.N, g.OH, g.OW, p.out.pitch);
             };
             auto finish = [&](int row, int c, float4 acc) {
                 const long pix_off = pixel_offset(row);
@@ -777,7 +786,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     const float z = act_apply(o[j] + bias_s[c + j], g.act);
                     o[j] = t.round_tf32 ? round_tf32(z) : z;
                 }
-                store4_direct(p.out.ptr, t.bf16, pix_off + cout0 + c, make_float4(o[0], o[1], o[2], o[3]), valid - c);
+                store4_direct(p.out.ptr, kBf16, pix_off + cout0 + c, make_float4(o[0], o[1], o[2], o[3]), valid - c);
             };
             auto reduce = [&](auto split_tag) {
                 constexpr int S = decltype(split_tag)::value;
@@ -1085,12 +1094,7 @@ conv_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
                 const long pix = long(tc.ow0) + row;
                 if (row < t.box_w && pix < total_pixels) pix_off = pix * p.out.pitch;
             } else {
-                const int ww = row % t.box_w;
-                const int hh = (row / t.box_w) % t.box_h;
-                const int im = row / (t.box_w * t.box_h);
-                const int ow = tc.ow0 + ww, oh = tc.oh0 + hh, n = tc.n0 + im;
-                if (im < t.box_n && ow < g.OW && oh < g.OH && n < g.N)
-                    pix_off = ((long(n) * g.OH + oh) * g.OW + ow) * p.out.pitch;
+                pix_off = boxed_pixel_offset(row, t.box_w, t.box_h, t.box_n, tc.ow0, tc.oh0, tc.n0, g.N, g.OH, g.OW, p.out.pitch);
             }
             const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + a * uint32_t(pg.acc_stride);
 #pragma unroll 1
@@ -1516,8 +1520,13 @@ const char *conv_tc_encode_dense_weights(const ConvTcParams &p, ConvTcPlan *plan
 }
 
 cudaError_t conv_tc_prepare() {
-    cudaError_t err = cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024);
-    if (err != cudaSuccess) return err;
+    const void *forms[] = {reinterpret_cast<const void *>(conv_tc_kernel<0, false>), reinterpret_cast<const void *>(conv_tc_kernel<0, true>),
+                           reinterpret_cast<const void *>(conv_tc_kernel<1, false>), reinterpret_cast<const void *>(conv_tc_kernel<1, true>),
+                           reinterpret_cast<const void *>(conv_tc_kernel<2, false>), reinterpret_cast<const void *>(conv_tc_kernel<2, true>)};
+    for (const void *form : forms) {
+        cudaError_t err = cudaFuncSetAttribute(form, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024);
+        if (err != cudaSuccess) return err;
+    }
     return cudaFuncSetAttribute(conv_tc_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024);
 }
 
@@ -1587,8 +1596,18 @@ void launch_conv_tc(const ConvTcParams &p, const ConvTcPlan &q, cudaStream_t str
                            *reinterpret_cast<const CUtensorMap *>(q.tmap_b), *reinterpret_cast<const CUtensorMap *>(q.tmap_c), p, t, pg);
         return;
     }
-    cudaLaunchKernelEx(&cfg, conv_tc_kernel, *reinterpret_cast<const CUtensorMap *>(q.tmap_a),
-                       *reinterpret_cast<const CUtensorMap *>(q.tmap_b), *reinterpret_cast<const CUtensorMap *>(q.tmap_c), p, t);
+    const CUtensorMap &ma = *reinterpret_cast<const CUtensorMap *>(q.tmap_a), &mb = *reinterpret_cast<const CUtensorMap *>(q.tmap_b),
+                      &mc = *reinterpret_cast<const CUtensorMap *>(q.tmap_c);
+    const int mode = q.x3 ? 1 : (q.bf16 ? 2 : 0);
+    if (t.cluster) {
+        if (mode == 1) cudaLaunchKernelEx(&cfg, conv_tc_kernel<1, true>, ma, mb, mc, p, t);
+        else if (mode == 2) cudaLaunchKernelEx(&cfg, conv_tc_kernel<2, true>, ma, mb, mc, p, t);
+        else cudaLaunchKernelEx(&cfg, conv_tc_kernel<0, true>, ma, mb, mc, p, t);
+    } else {
+        if (mode == 1) cudaLaunchKernelEx(&cfg, conv_tc_kernel<1, false>, ma, mb, mc, p, t);
+        else if (mode == 2) cudaLaunchKernelEx(&cfg, conv_tc_kernel<2, false>, ma, mb, mc, p, t);
+        else cudaLaunchKernelEx(&cfg, conv_tc_kernel<0, false>, ma, mb, mc, p, t);
+    }
 }
 
 }  // namespace ios
