@@ -1,12 +1,12 @@
 """
 Regenerates the golden fixtures of this folder by running the REFERENCE implementation.
 
-Needs the reference checkout (default /root/reference); it is imported, never copied.  For each
+Needs the reference checkout (``--ref``); it is imported, never copied.  For each
 case the reference's own package builds the graph, the oracle's seeded generators provide weights
 and input (so that the tests can rebuild exactly the same arrays), and the reference's CPU executor
 ``ios.torch_utils.Net`` (python/ios/torch_utils.py:61-125) produces the output that is stored.
 
-    python tests/golden/make_golden.py [--ref /root/reference]
+    python tests/golden/make_golden.py [--ref <reference checkout>]
 
 Outputs: golden.npz (output vectors), manifest.json (graph hashes, seeds, shapes) and
 ref_schedules/*.json.gz (the reference's seven stored Inception-v3 schedules,
