@@ -893,16 +893,18 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, const TileGeom &t, con
     return c;
 }
 
+template <int MODE>      // operand mode, as for conv_tc_kernel
 __global__ void __launch_bounds__(kPersistThreads, 1)
 conv_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                           const __grid_constant__ CUtensorMap tmap_c, const ConvTcParams p, const TileGeom t,
                           const PersistGeom pg) {
+    constexpr bool kX3 = MODE == 1, kBf16 = MODE == 2;
     extern __shared__ uint8_t smem_raw[];
     __shared__ float bias_s[2][256];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
     const int b_bytes = t.bn * kRowBytes;
-    const int passes = t.x3 ? 2 : 1;
+    const int passes = kX3 ? 2 : 1;
     const int stage_bytes = passes * (kATileBytes + b_bytes);
     const uint32_t a_lo_off = kATileBytes;
     const uint32_t b_off = uint32_t(passes) * kATileBytes;
@@ -915,7 +917,7 @@ conv_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const ConvGeom &g = p.g;
-    const int epi_warps = t.x3 ? 4 : 8;
+    const int epi_warps = kX3 ? 4 : 8;
     const int my_tiles = (pg.total_tiles - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x);
 
     if (warp == 0) {
@@ -976,7 +978,7 @@ conv_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
                 const uint32_t bar = full0 + 8u * s;
                 mbar_expect_tx(bar, uint32_t(t.a_bytes + passes * b_bytes));
                 tma_load_2d(stage + b_off, &tmap_b, bar, it * t.chunk, tc.cout0);
-                if (t.x3) tma_load_2d(stage + b_lo_off, &tmap_b, bar, it * t.chunk, t.cout_pad + tc.cout0);
+                if (kX3) tma_load_2d(stage + b_lo_off, &tmap_b, bar, it * t.chunk, t.cout_pad + tc.cout0);
                 if (t.im2col) tma_load_im2col(stage, &tmap_a, bar, cc * t.chunk, tc.im_w, tc.im_h, tc.n0, uint32_t(sx), uint32_t(r));
                 else if (t.flat) tma_load_4d(stage, &tmap_a, bar, cc * t.chunk, tc.ow0, 0, 0);
                 else tma_load_4d(stage, &tmap_a, bar, cc * t.chunk, tc.ow0 * g.sw - g.pw + sx, tc.oh0 * g.sh - g.ph + r, tc.n0);
@@ -1006,7 +1008,7 @@ conv_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     }
     if (warp == 1) {
         // ---------------- MMA issuer ----------------
-        const uint32_t fmt = t.bf16 ? 1u : 2u;
+        const uint32_t fmt = kBf16 ? 1u : 2u;
         const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(t.bn >> 3) << 17) | (uint32_t(kTileM >> 4) << 24);
         const uint32_t idesc_wide = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(t.bn >> 2) << 17) | (uint32_t(kTileM >> 4) << 24);
         MmaRing ring;
@@ -1021,15 +1023,15 @@ conv_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             tc_fence_after();
             const uint32_t tmem_d = tmem_base + a * uint32_t(pg.acc_stride);
 #define IOS_MMA_LOOP(MODE, WAIT) mma_loop<MODE>(t.k_iters, t.stages, WAIT, empty0, ring, tmem_d, idesc, idesc_wide, p)
-            ok = t.x3 ? (t.wide ? IOS_MMA_LOOP(3, ready0) : IOS_MMA_LOOP(1, ready0))
-                      : (t.bf16 ? IOS_MMA_LOOP(2, full0) : IOS_MMA_LOOP(0, full0));
+            ok = kX3 ? (t.wide ? IOS_MMA_LOOP(3, ready0) : IOS_MMA_LOOP(1, ready0))
+                      : (kBf16 ? IOS_MMA_LOOP(2, full0) : IOS_MMA_LOOP(0, full0));
 #undef IOS_MMA_LOOP
             if (ok) umma_commit(acc_full0 + 8u * a);
         }
         if (!ok) atomicExch(p.error_flag, 2);
         return;
     }
-    if (t.x3 && warp >= 6) {
+    if (kX3 && warp >= 6) {
         // ---------------- warps 6..9 (three-pass mode): residual of every landed activation tile ----------------
         const int tid = threadIdx.x - 192;
         const int n_vec = t.a_bytes >> 4;
@@ -1109,12 +1111,12 @@ conv_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
                 if (t.tma_store) {
 #pragma unroll
                     for (int j = 0; j < 16; j += 4)
-                        stage4(staging, row, c + j, make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]), t.bf16);
+                        stage4(staging, row, c + j, make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]), kBf16);
                 } else if (pix_off >= 0 && c < valid) {
 #pragma unroll
                     for (int j = 0; j < 16; j += 4)
                         if (c + j < valid)
-                            store4_direct(p.out.ptr, t.bf16, pix_off + tc.cout0 + c + j, make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]),
+                            store4_direct(p.out.ptr, kBf16, pix_off + tc.cout0 + c + j, make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]),
                                           valid - (c + j));
                 }
             }
@@ -1527,7 +1529,13 @@ cudaError_t conv_tc_prepare() {
         cudaError_t err = cudaFuncSetAttribute(form, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024);
         if (err != cudaSuccess) return err;
     }
-    return cudaFuncSetAttribute(conv_tc_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024);
+    const void *resident[] = {reinterpret_cast<const void *>(conv_tc_persistent_kernel<0>), reinterpret_cast<const void *>(conv_tc_persistent_kernel<1>),
+                              reinterpret_cast<const void *>(conv_tc_persistent_kernel<2>)};
+    for (const void *form : resident) {
+        cudaError_t err = cudaFuncSetAttribute(form, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024);
+        if (err != cudaSuccess) return err;
+    }
+    return cudaSuccess;
 }
 
 void launch_conv_tc(const ConvTcParams &p, const ConvTcPlan &q, cudaStream_t stream) {
@@ -1591,14 +1599,15 @@ void launch_conv_tc(const ConvTcParams &p, const ConvTcPlan &q, cudaStream_t str
     }
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
-    if (q.persistent) {
-        cudaLaunchKernelEx(&cfg, conv_tc_persistent_kernel, *reinterpret_cast<const CUtensorMap *>(q.tmap_a),
-                           *reinterpret_cast<const CUtensorMap *>(q.tmap_b), *reinterpret_cast<const CUtensorMap *>(q.tmap_c), p, t, pg);
-        return;
-    }
     const CUtensorMap &ma = *reinterpret_cast<const CUtensorMap *>(q.tmap_a), &mb = *reinterpret_cast<const CUtensorMap *>(q.tmap_b),
                       &mc = *reinterpret_cast<const CUtensorMap *>(q.tmap_c);
     const int mode = q.x3 ? 1 : (q.bf16 ? 2 : 0);
+    if (q.persistent) {
+        if (mode == 1) cudaLaunchKernelEx(&cfg, conv_tc_persistent_kernel<1>, ma, mb, mc, p, t, pg);
+        else if (mode == 2) cudaLaunchKernelEx(&cfg, conv_tc_persistent_kernel<2>, ma, mb, mc, p, t, pg);
+        else cudaLaunchKernelEx(&cfg, conv_tc_persistent_kernel<0>, ma, mb, mc, p, t, pg);
+        return;
+    }
     if (t.cluster) {
         if (mode == 1) cudaLaunchKernelEx(&cfg, conv_tc_kernel<1, true>, ma, mb, mc, p, t);
         else if (mode == 2) cudaLaunchKernelEx(&cfg, conv_tc_kernel<2, true>, ma, mb, mc, p, t);
