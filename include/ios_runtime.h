@@ -82,6 +82,7 @@ IOS_API const char *ios_last_error(void);
  * Testing aids (each switches one mechanism of the tensor-core convolution off or pins one choice):
  * "im2col" "1"/"0" (pixel tiles over the flattened pixel axis by im2col-mode loads / boxes of the image),
  * "stem" "1"/"0" (a convolution over at most 4 input channels runs on CUDA cores / on the tensor cores like the rest),
+ * "half_rows" "1"/"0" (bfloat16 layers of at most 32 input channels use 64-byte / 128-byte operand rows),
  * "persistent" "1"/"0" (grids of several waves run as resident CTAs that walk the tiles / one CTA per tile),
  * "bulk_store" "1"/"0" (results leave through a bulk tensor store / straight from registers),
  * "split_k", "bn", "stages", "producers" (a positive number overrides the K split, the output-channel tile

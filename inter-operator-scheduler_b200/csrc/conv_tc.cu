@@ -64,7 +64,9 @@ struct TileGeom {
     int tma_store;    // 1: the epilogue stages the tile in shared memory and stores it with bulk tensor stores
     int cluster;      // 1: the split_k CTAs of a tile form a thread-block cluster and reduce through shared memory
     int bf16;         // 1: bfloat16 operands / activations (kind::f16), 0: float32 storage (kind::tf32)
-    int chunk;        // elements of K per 128-byte row: 32 (float32) or 64 (bfloat16)
+    int chunk;        // elements of K per pipeline step: 32 (float32), 64 (bfloat16) or 32 (bfloat16, 64-byte rows)
+    int row_bytes;    // bytes of K per operand row: 128, or 64 for bfloat16 layers of at most 32 input channels
+    int slab;         // output channels per 128-byte row of the store staging: 32 (float32) or 64 (bfloat16)
     int producers;    // lanes of warp 0 that issue TMA loads; divides `stages`
     int wide;         // 1: (three-pass mode, bn <= 128) one instruction of width 2 bn covers the weight tile and its
                       //    residual; the residual's products accumulate in columns [bn, 2 bn)
@@ -233,13 +235,14 @@ __device__ __forceinline__ void acc_ld16(uint32_t taddr, uint32_t pair, float *v
     }
 }
 // K-major operand tile with 128-byte swizzle: rows are 128 bytes, groups of 8 rows are 1024 bytes apart.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+// (row_bytes 64: the same with the 64-byte swizzle, rows are 64 bytes and groups of 8 rows 512 bytes apart)
+__device__ __forceinline__ uint64_t smem_desc_kmajor(uint32_t addr, int row_bytes) {
     uint64_t d = 0;
     d |= uint64_t((addr & 0x3FFFF) >> 4);    // start address, 16-byte units
     d |= uint64_t(1) << 16;                  // leading-dimension byte offset (unused for swizzled K-major)
-    d |= uint64_t(1024 >> 4) << 32;          // stride-dimension byte offset: 8 rows * 128 B
+    d |= uint64_t((8 * row_bytes) >> 4) << 32;   // stride-dimension byte offset: 8 rows
     d |= uint64_t(1) << 46;                  // descriptor version for sm_100
-    d |= uint64_t(2) << 61;                  // SWIZZLE_128B
+    d |= uint64_t(row_bytes == 128 ? 2 : 4) << 61;   // SWIZZLE_128B / SWIZZLE_64B
     return d;
 }
 // sigmoid / tanh are rare; keeping them out of line keeps the unrolled epilogue small
@@ -331,11 +334,14 @@ struct MmaRing {
     uint64_t da0, db0, dal0, dbl0, dstep;   // descriptors of stage 0 and their step per stage (16-byte units)
     uint64_t da, db, dal, dbl;
     uint32_t s, phase;
-    __device__ __forceinline__ void start(uint32_t smem_base, uint32_t a_lo_off, uint32_t b_off, uint32_t b_lo_off, int stage_bytes) {
-        da0 = smem_desc_sw128(smem_base);
-        db0 = smem_desc_sw128(smem_base + b_off);
-        dal0 = smem_desc_sw128(smem_base + a_lo_off);
-        dbl0 = smem_desc_sw128(smem_base + b_lo_off);
+    int ksteps;                             // instructions per K step: row bytes / 32
+    __device__ __forceinline__ void start(uint32_t smem_base, uint32_t a_lo_off, uint32_t b_off, uint32_t b_lo_off, int stage_bytes,
+                                          int row_bytes) {
+        ksteps = row_bytes >> 5;
+        da0 = smem_desc_kmajor(smem_base, row_bytes);
+        db0 = smem_desc_kmajor(smem_base + b_off, row_bytes);
+        dal0 = smem_desc_kmajor(smem_base + a_lo_off, row_bytes);
+        dbl0 = smem_desc_kmajor(smem_base + b_lo_off, row_bytes);
         dstep = uint64_t(stage_bytes >> 4);
         da = da0; db = db0; dal = dal0; dbl = dbl0;
         s = 0; phase = 0;
@@ -353,6 +359,7 @@ __device__ __forceinline__ bool mma_loop(int n_it, int stages, uint32_t wait0, u
         const uint64_t da = ring.da, db = ring.db, dal = ring.dal, dbl = ring.dbl;
 #pragma unroll
         for (int k = 0; k < kRowBytes / 32; ++k) {       // 32 bytes of K per instruction: 8 TF32 or 16 BF16
+            if (k >= ring.ksteps) break;                 // (64-byte rows: two instructions)
             const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
             if (MODE == 3) {
                 // a*w ~= a_hi*[w_hi | w_lo] + a_lo*w_hi
@@ -392,12 +399,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     __shared__ float bias_s[256];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
-    const int b_bytes = t.bn * kRowBytes;
+    const int a_tile_bytes = kTileM * t.row_bytes, b_bytes = t.bn * t.row_bytes;
     const int passes = kX3 ? 2 : 1;                       // operand planes per stage: value (+ residual)
-    const int stage_bytes = passes * (kATileBytes + b_bytes);
+    const int stage_bytes = passes * (a_tile_bytes + b_bytes);
     // stage layout: A | A residual | B | B residual
-    const uint32_t a_lo_off = kATileBytes;
-    const uint32_t b_off = uint32_t(passes) * kATileBytes;
+    const uint32_t a_lo_off = uint32_t(a_tile_bytes);
+    const uint32_t b_off = uint32_t(passes) * a_tile_bytes;
     const uint32_t b_lo_off = b_off + uint32_t(b_bytes);
     const uint32_t bars = smem_base + uint32_t(t.stages) * stage_bytes;
     const uint32_t full0 = bars, empty0 = bars + 8u * t.stages, ready0 = bars + 16u * t.stages;
@@ -552,7 +559,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             // of twice the width forms a_hi*w_hi (columns [0, bn)) and a_hi*w_lo (columns [bn, 2 bn))
             const uint32_t idesc_wide = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(t.bn >> 2) << 17) | (uint32_t(kTileM >> 4) << 24);
             MmaRing ring;
-            ring.start(smem_base, a_lo_off, b_off, b_lo_off, stage_bytes);
+            ring.start(smem_base, a_lo_off, b_off, b_lo_off, stage_bytes, t.row_bytes);
 #define IOS_MMA_LOOP(MODE, WAIT) mma_loop<MODE>(n_it, t.stages, WAIT, empty0, ring, tmem_base, idesc, idesc_wide, p)
             const bool ok = kX3 ? (t.wide ? IOS_MMA_LOOP(3, ready0) : IOS_MMA_LOOP(1, ready0))
                                  : (kBf16 ? IOS_MMA_LOOP(2, full0) : IOS_MMA_LOOP(0, full0));
@@ -736,8 +743,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 if (threadIdx.x == 64) {
                     STAMP(11);
                     // one bulk tensor store per 128-byte slab; pixels and channels outside the tensor are clipped
-                    for (int c = 0; c < valid; c += t.chunk) {
-                        const uint32_t src = smem_base + uint32_t(c / t.chunk) * kATileBytes;
+                    for (int c = 0; c < valid; c += t.slab) {
+                        const uint32_t src = smem_base + uint32_t(c / t.slab) * kATileBytes;
                         if (t.flat) tma_store_4d(&tmap_c, src, cout0 + c, ow0, 0, 0);
                         else tma_store_4d(&tmap_c, src, cout0 + c, ow0, oh0, n0);
                     }
@@ -903,13 +910,13 @@ conv_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     __shared__ float bias_s[2][256];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
-    const int b_bytes = t.bn * kRowBytes;
+    const int a_tile_bytes = kTileM * t.row_bytes, b_bytes = t.bn * t.row_bytes;
     const int passes = kX3 ? 2 : 1;
-    const int stage_bytes = passes * (kATileBytes + b_bytes);
-    const uint32_t a_lo_off = kATileBytes;
-    const uint32_t b_off = uint32_t(passes) * kATileBytes;
+    const int stage_bytes = passes * (a_tile_bytes + b_bytes);
+    const uint32_t a_lo_off = uint32_t(a_tile_bytes);
+    const uint32_t b_off = uint32_t(passes) * a_tile_bytes;
     const uint32_t b_lo_off = b_off + uint32_t(b_bytes);
-    const int slabs = (t.bn + t.chunk - 1) / t.chunk;
+    const int slabs = (t.bn + t.slab - 1) / t.slab;
     const uint32_t bars = smem_base + uint32_t(pg.staging_off) + (t.tma_store ? uint32_t(slabs) * kATileBytes : 0u);
     const uint32_t full0 = bars, empty0 = bars + 8u * t.stages, ready0 = bars + 16u * t.stages;
     const uint32_t acc_full0 = bars + 24u * t.stages, acc_empty0 = acc_full0 + 16u;
@@ -1012,7 +1019,7 @@ conv_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(t.bn >> 3) << 17) | (uint32_t(kTileM >> 4) << 24);
         const uint32_t idesc_wide = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(t.bn >> 2) << 17) | (uint32_t(kTileM >> 4) << 24);
         MmaRing ring;
-        ring.start(smem_base, a_lo_off, b_off, b_lo_off, stage_bytes);
+        ring.start(smem_base, a_lo_off, b_off, b_lo_off, stage_bytes, t.row_bytes);
         bool ok = true;
 #pragma unroll 1
         for (int ti = 0; ti < my_tiles && ok; ++ti) {
@@ -1129,8 +1136,8 @@ conv_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("bar.sync 1, %0;" ::"r"(epi_threads) : "memory");  // the tile is staged
             if (ok && etid == 0) {
-                for (int c = 0; c < valid; c += t.chunk) {
-                    const uint32_t src = smem_base + uint32_t(pg.staging_off) + uint32_t(c / t.chunk) * kATileBytes;
+                for (int c = 0; c < valid; c += t.slab) {
+                    const uint32_t src = smem_base + uint32_t(pg.staging_off) + uint32_t(c / t.slab) * kATileBytes;
                     if (t.flat) tma_store_4d(&tmap_c, src, tc.cout0 + c, tc.ow0, 0, 0);
                     else tma_store_4d(&tmap_c, src, tc.cout0 + c, tc.ow0, tc.oh0, tc.n0);
                 }
@@ -1227,7 +1234,12 @@ void conv_tc_choose(const ConvGeom &g, int sm_count, int concurrency_hint, bool 
     q.sm_count = sm_count;
     q.x3 = (three_pass && !bf16) ? 1 : 0;
     q.cluster = 1;
-    const int chunk = bf16 ? 64 : 32;            // K elements per 128-byte row
+    // K elements per pipeline step = one operand row: 128 bytes, except that bfloat16 layers of at most 32
+    // input channels use 64-byte rows (64-byte swizzle) -- half-empty 128-byte rows would cost the TMA
+    // unit and shared memory twice the bytes for the same work
+    q.half_rows = (bf16 && g.Cin <= 32 && !q.no_half_rows) ? 1 : 0;
+    const int row_bytes = q.half_rows ? 64 : 128;
+    const int chunk = bf16 ? (q.half_rows ? 32 : 64) : 32;
     const int bn_step = bf16 ? 64 : 32;          // output channels per 128-byte row of the store staging
     const bool flat = g.kh == 1 && g.kw == 1 && g.sh == 1 && g.sw == 1 && g.ph == 0 && g.pw == 0;
     q.flat_1x1 = flat ? 1 : 0;
@@ -1293,8 +1305,8 @@ void conv_tc_choose(const ConvGeom &g, int sm_count, int concurrency_hint, bool 
             if (bn == last_bn) continue;
             last_bn = bn;
             const int nt = ceil_div(g.Cout, bn);
-            const double load_bytes = rows * 128.0 + double(planes) * bn * 128.0;
-            const double stage_bytes = double(planes) * (kATileBytes + bn * 128.0);
+            const double load_bytes = double(rows) * row_bytes + double(planes) * bn * row_bytes;
+            const double stage_bytes = double(planes) * (kTileM + bn) * row_bytes;
             const bool wide = q.x3 && bn <= 128;
             const double tensor = bn * kTensorPerColumn * (q.x3 ? 3.0 : 1.0);
             const double epilogue = bn * kEpiloguePerColumn * (wide ? 1.3 : 1.0);
@@ -1334,7 +1346,7 @@ void conv_tc_set_split(ConvTcPlan *plan, int split) {
     split = std::max(1, std::min(split, q.k_iters));
     const int base = q.tiles_w * q.tiles_h * q.tiles_n * q.n_tiles;
     q.split_k = split;
-    const int stage_bytes = (q.x3 ? 2 : 1) * (kATileBytes + q.bn * kRowBytes);
+    const int stage_bytes = (q.x3 ? 2 : 1) * (kTileM + q.bn) * (q.half_rows ? 64 : 128);
     const int slab_channels = q.bf16 ? 64 : 32;
     const int per_split = ceil_div(q.k_iters, split);
     q.stages = std::max(2, std::min({8, per_split, (200 * 1024) / stage_bytes}));
@@ -1387,13 +1399,13 @@ static uint16_t bf16_round_host(float v) {
 }
 
 size_t conv_tc_packed_bytes(const ConvGeom &g, const ConvTcPlan &plan) {
-    const size_t elems = size_t(plan.x3 ? 2 : 1) * plan.cout_pad * g.kh * g.kw * plan.cchunks * (plan.bf16 ? 64 : 32);
+    const size_t elems = size_t(plan.x3 ? 2 : 1) * plan.cout_pad * g.kh * g.kw * plan.cchunks * (plan.bf16 && !plan.half_rows ? 64 : 32);
     return elems * (plan.bf16 ? 2 : 4);
 }
 
 void conv_tc_pack_weights(const float *oihw, const ConvGeom &g, const ConvTcPlan &plan, void *packed_out) {
     const int taps = g.kh * g.kw;
-    const int chunk = plan.bf16 ? 64 : 32;
+    const int chunk = (plan.bf16 && !plan.half_rows) ? 64 : 32;
     const size_t row = size_t(taps) * plan.cchunks * chunk;
     const size_t plane = size_t(plan.cout_pad) * row;
     std::memset(packed_out, 0, conv_tc_packed_bytes(g, plan));
@@ -1422,7 +1434,9 @@ const char *conv_tc_encode(const ConvTcParams &p, ConvTcPlan *plan) {
     static thread_local char msg[160];
     const CUtensorMapDataType dtype = q.bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
     const cuuint64_t esize = q.bf16 ? 2 : 4;
-    const cuuint32_t chunk = q.bf16 ? 64 : 32;
+    const cuuint32_t chunk = (q.bf16 && !q.half_rows) ? 64 : 32;     // K elements per operand row
+    const cuuint32_t slab = q.bf16 ? 64 : 32;                          // output channels per staging row
+    const CUtensorMapSwizzle k_swizzle = q.half_rows ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
     auto fail = [&](const char *what, CUresult r) {
         std::snprintf(msg, sizeof msg, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, int(r));
         return msg;
@@ -1448,7 +1462,7 @@ const char *conv_tc_encode(const ConvTcParams &p, ConvTcPlan *plan) {
             im2col_corners(g.H, g.OH, g.sh, g.ph, &lower[1], &upper[1]);
             CUresult r = encode_im2col(reinterpret_cast<CUtensorMap *>(q.tmap_a), dtype, 4, p.in.ptr, dims, strides, lower,
                                        upper, chunk, cuuint32_t(q.box_w), estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                       k_swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
             if (r != CUDA_SUCCESS) return fail("activations, im2col", r);
         } else {
@@ -1459,7 +1473,7 @@ const char *conv_tc_encode(const ConvTcParams &p, ConvTcPlan *plan) {
         }
         if (!q.im2col) {
             CUresult r = encode(reinterpret_cast<CUtensorMap *>(q.tmap_a), dtype, 4, p.in.ptr, dims,
-                                strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, k_swizzle,
                                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
             if (r != CUDA_SUCCESS) return fail("activations", r);
         }
@@ -1472,7 +1486,7 @@ const char *conv_tc_encode(const ConvTcParams &p, ConvTcPlan *plan) {
         cuuint32_t estr[2] = {1, 1};
         CUresult r = encode(reinterpret_cast<CUtensorMap *>(q.tmap_b), dtype, 2,
                             const_cast<void *>(p.weight_packed), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            k_swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail("weights", r);
     }
@@ -1490,11 +1504,11 @@ const char *conv_tc_encode(const ConvTcParams &p, ConvTcPlan *plan) {
         if (q.flat_1x1 || q.im2col) {
             dims[0] = cuuint64_t(g.Cout); dims[1] = cuuint64_t(g.N) * g.OH * g.OW; dims[2] = 1; dims[3] = 1;
             strides[0] = pix_bytes; strides[1] = pix_bytes * dims[1]; strides[2] = strides[1];
-            box[0] = chunk; box[1] = cuuint32_t(q.box_w); box[2] = 1; box[3] = 1;
+            box[0] = slab; box[1] = cuuint32_t(q.box_w); box[2] = 1; box[3] = 1;
         } else {
             dims[0] = cuuint64_t(g.Cout); dims[1] = cuuint64_t(g.OW); dims[2] = cuuint64_t(g.OH); dims[3] = cuuint64_t(g.N);
             strides[0] = pix_bytes; strides[1] = pix_bytes * g.OW; strides[2] = pix_bytes * g.OW * g.OH;
-            box[0] = chunk; box[1] = cuuint32_t(q.box_w); box[2] = cuuint32_t(q.box_h); box[3] = cuuint32_t(q.box_n);
+            box[0] = slab; box[1] = cuuint32_t(q.box_w); box[2] = cuuint32_t(q.box_h); box[3] = cuuint32_t(q.box_n);
         }
         CUresult r = encode(reinterpret_cast<CUtensorMap *>(q.tmap_c), dtype, 4, p.out.ptr, dims,
                             strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -1552,9 +1566,11 @@ void launch_conv_tc(const ConvTcParams &p, const ConvTcPlan &q, cudaStream_t str
         if (q.stages % cand == 0) t.producers = cand;
     t.flat = (q.flat_1x1 || q.im2col) ? 1 : 0;
     t.im2col = q.im2col;
-    t.a_bytes = q.box_w * q.box_h * q.box_n * kRowBytes;
+    t.row_bytes = q.half_rows ? 64 : 128;
+    t.a_bytes = q.box_w * q.box_h * q.box_n * t.row_bytes;
     t.bf16 = q.bf16;
-    t.chunk = q.bf16 ? 64 : 32;
+    t.chunk = (q.bf16 && !q.half_rows) ? 64 : 32;
+    t.slab = q.bf16 ? 64 : 32;
     t.wide = (q.x3 && q.bn <= 128) ? 1 : 0;
     int cols = 32;
     while (cols < (t.wide ? 2 : 1) * q.bn) cols *= 2;   // the wide form keeps a second accumulator range
@@ -1569,7 +1585,7 @@ void launch_conv_tc(const ConvTcParams &p, const ConvTcPlan &q, cudaStream_t str
     if (q.persistent) {
         pg.n_tiles = q.n_tiles;
         pg.total_tiles = q.tiles_w * q.tiles_h * q.tiles_n * q.n_tiles;
-        pg.staging_off = q.stages * (q.x3 ? 2 : 1) * (kATileBytes + q.bn * kRowBytes);
+        pg.staging_off = q.stages * (q.x3 ? 2 : 1) * (kTileM + q.bn) * t.row_bytes;
         pg.acc_stride = (t.wide ? 2 : 1) * ceil_div(q.bn, 32) * 32;
         cols = 32;
         while (cols < 2 * pg.acc_stride) cols *= 2;

@@ -112,6 +112,8 @@ struct ConvTcPlan {
     int persistent;                // 1: CTAs stay resident and walk the tiles (grids of several waves, split_k == 1)
     int grid_ctas;                 // CTAs launched
     int no_persistent;             // testing aid: never use the persistent kernel
+    int half_rows;                 // 1: bfloat16 layer of at most 32 input channels: 64-byte operand rows (32 K elements per step)
+    int no_half_rows;              // testing aid: such layers use 128-byte rows like the rest
     int max_producers;             // testing aid: cap on the lanes that issue TMA loads (0: the default, 4)
     int im2col;                    // 1: pixels flattened into one axis, activations fetched by im2col-mode TMA
     int x3;                        // 1: three-pass TF32 (operands split into value + residual)

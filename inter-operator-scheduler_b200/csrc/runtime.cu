@@ -641,6 +641,7 @@ int ios_set_option(const char *key, const char *value) {
         else if (k == "im2col" && (v == "0" || v == "1")) g_options.no_im2col = v == "0";
         else if (k == "persistent" && (v == "0" || v == "1")) g_options.no_persistent = v == "0";
         else if (k == "stem" && (v == "0" || v == "1")) g_options.no_stem_kernel = v == "0";
+        else if (k == "half_rows" && (v == "0" || v == "1")) g_options.no_half_rows = v == "0";
         else if (k == "timeline") g_options.timeline = v == "1";
         else if (k == "stage_barriers" && (v == "0" || v == "1")) g_options.stage_barriers = v == "1";
         else throw ArgumentError("unknown option " + k + "=" + v);
