@@ -65,7 +65,6 @@ struct TileGeom {
     int cluster;      // 1: the split_k CTAs of a tile form a thread-block cluster and reduce through shared memory
     int bf16;         // 1: bfloat16 operands / activations (kind::f16), 0: float32 storage (kind::tf32)
     int chunk;        // elements of K per pipeline step: 32 (float32), 64 (bfloat16) or 32 (bfloat16, 64-byte rows)
-    int row_bytes;    // bytes of K per operand row: 128, or 64 for bfloat16 layers of at most 32 input channels
     int slab;         // output channels per 128-byte row of the store staging: 32 (float32) or 64 (bfloat16)
     int producers;    // lanes of warp 0 that issue TMA loads; divides `stages`
     int wide;         // 1: (three-pass mode, bn <= 128) one instruction of width 2 bn covers the weight tile and its
@@ -327,17 +326,16 @@ __device__ __noinline__ long boxed_pixel_offset(int row, int box_w, int box_h, i
 }
 
 // The MMA issuer's K loop, one copy per operand mode (0: TF32, 1: three-pass TF32, 2: BF16) so that the
-// (3: three-pass TF32 with the weight tile and its residual under one instruction of twice the width)
+// (3: three-pass TF32 with the weight tile and its residual under one instruction of twice the width,
+//  4: BF16 with 64-byte operand rows, two instructions per K step)
 // loop body carries no mode tests: wait for the stage, issue its instructions, hand the stage back.
 // Position of the MMA issuer in the ring of pipeline stages (it outlives a tile in the persistent kernel).
 struct MmaRing {
     uint64_t da0, db0, dal0, dbl0, dstep;   // descriptors of stage 0 and their step per stage (16-byte units)
     uint64_t da, db, dal, dbl;
     uint32_t s, phase;
-    int ksteps;                             // instructions per K step: row bytes / 32
     __device__ __forceinline__ void start(uint32_t smem_base, uint32_t a_lo_off, uint32_t b_off, uint32_t b_lo_off, int stage_bytes,
                                           int row_bytes) {
-        ksteps = row_bytes >> 5;
         da0 = smem_desc_kmajor(smem_base, row_bytes);
         db0 = smem_desc_kmajor(smem_base + b_off, row_bytes);
         dal0 = smem_desc_kmajor(smem_base + a_lo_off, row_bytes);
@@ -358,8 +356,7 @@ __device__ __forceinline__ bool mma_loop(int n_it, int stages, uint32_t wait0, u
         tc_fence_after();
         const uint64_t da = ring.da, db = ring.db, dal = ring.dal, dbl = ring.dbl;
 #pragma unroll
-        for (int k = 0; k < kRowBytes / 32; ++k) {       // 32 bytes of K per instruction: 8 TF32 or 16 BF16
-            if (k >= ring.ksteps) break;                 // (64-byte rows: two instructions)
+        for (int k = 0; k < (MODE == 4 ? 2 : 4); ++k) {   // 32 bytes of K per instruction: 8 TF32 or 16 BF16; 64-byte rows: two
             const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
             if (MODE == 3) {
                 // a*w ~= a_hi*[w_hi | w_lo] + a_lo*w_hi
@@ -370,7 +367,7 @@ __device__ __forceinline__ bool mma_loop(int n_it, int stages, uint32_t wait0, u
                 umma_tf32(tmem_d, dal + uint64_t(k * 2), db + uint64_t(k * 2), idesc, acc);
                 umma_tf32(tmem_d, da + uint64_t(k * 2), dbl + uint64_t(k * 2), idesc, 1u);
                 umma_tf32(tmem_d, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, 1u);
-            } else if (MODE == 2) {
+            } else if (MODE == 2 || MODE == 4) {
                 umma_f16(tmem_d, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, acc);
             } else {
                 umma_tf32(tmem_d, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, acc);
@@ -387,19 +384,22 @@ __device__ __forceinline__ bool mma_loop(int n_it, int stages, uint32_t wait0, u
 }
 
 // ---- the kernel ------------------------------------------------------------------------------
-// One instantiation per operand mode (0: TF32, 1: three-pass TF32, 2: BF16) and per reduction form
+// One instantiation per operand mode (0: TF32, 1: three-pass TF32, 2: BF16, 4: BF16 with 64-byte operand rows)
+// and per reduction form
 // (kCluster: the split_k CTAs of a tile are a cluster): a CTA runs its code once, so what it does not
 // need should not be in its instruction stream.
 template <int MODE, bool kCluster>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ CUtensorMap tmap_c, const ConvTcParams p, const TileGeom t) {
-    constexpr bool kX3 = MODE == 1, kBf16 = MODE == 2;
+    constexpr bool kX3 = MODE == 1, kBf16 = MODE == 2 || MODE == 4;
+    constexpr int kRow = MODE == 4 ? 64 : 128;          // bytes of K per operand row (MODE 4: bfloat16, 64-byte rows)
     extern __shared__ uint8_t smem_raw[];
     __shared__ float bias_s[256];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
-    const int a_tile_bytes = kTileM * t.row_bytes, b_bytes = t.bn * t.row_bytes;
+    constexpr int a_tile_bytes = kTileM * kRow;
+    const int b_bytes = t.bn * kRow;
     const int passes = kX3 ? 2 : 1;                       // operand planes per stage: value (+ residual)
     const int stage_bytes = passes * (a_tile_bytes + b_bytes);
     // stage layout: A | A residual | B | B residual
@@ -559,10 +559,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             // of twice the width forms a_hi*w_hi (columns [0, bn)) and a_hi*w_lo (columns [bn, 2 bn))
             const uint32_t idesc_wide = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(t.bn >> 2) << 17) | (uint32_t(kTileM >> 4) << 24);
             MmaRing ring;
-            ring.start(smem_base, a_lo_off, b_off, b_lo_off, stage_bytes, t.row_bytes);
-#define IOS_MMA_LOOP(MODE, WAIT) mma_loop<MODE>(n_it, t.stages, WAIT, empty0, ring, tmem_base, idesc, idesc_wide, p)
+            ring.start(smem_base, a_lo_off, b_off, b_lo_off, stage_bytes, kRow);
+#define IOS_MMA_LOOP(FORM, WAIT) mma_loop<FORM>(n_it, t.stages, WAIT, empty0, ring, tmem_base, idesc, idesc_wide, p)
             const bool ok = kX3 ? (t.wide ? IOS_MMA_LOOP(3, ready0) : IOS_MMA_LOOP(1, ready0))
-                                 : (kBf16 ? IOS_MMA_LOOP(2, full0) : IOS_MMA_LOOP(0, full0));
+                                 : (kBf16 ? IOS_MMA_LOOP(MODE, full0) : IOS_MMA_LOOP(0, full0));
 #undef IOS_MMA_LOOP
             if (ok) umma_commit(accum_bar);
             else atomicExch(p.error_flag, 2);
@@ -905,12 +905,14 @@ __global__ void __launch_bounds__(kPersistThreads, 1)
 conv_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                           const __grid_constant__ CUtensorMap tmap_c, const ConvTcParams p, const TileGeom t,
                           const PersistGeom pg) {
-    constexpr bool kX3 = MODE == 1, kBf16 = MODE == 2;
+    constexpr bool kX3 = MODE == 1, kBf16 = MODE == 2 || MODE == 4;
+    constexpr int kRow = MODE == 4 ? 64 : 128;          // bytes of K per operand row (MODE 4: bfloat16, 64-byte rows)
     extern __shared__ uint8_t smem_raw[];
     __shared__ float bias_s[2][256];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
-    const int a_tile_bytes = kTileM * t.row_bytes, b_bytes = t.bn * t.row_bytes;
+    constexpr int a_tile_bytes = kTileM * kRow;
+    const int b_bytes = t.bn * kRow;
     const int passes = kX3 ? 2 : 1;
     const int stage_bytes = passes * (a_tile_bytes + b_bytes);
     const uint32_t a_lo_off = uint32_t(a_tile_bytes);
@@ -1019,7 +1021,7 @@ conv_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(t.bn >> 3) << 17) | (uint32_t(kTileM >> 4) << 24);
         const uint32_t idesc_wide = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(t.bn >> 2) << 17) | (uint32_t(kTileM >> 4) << 24);
         MmaRing ring;
-        ring.start(smem_base, a_lo_off, b_off, b_lo_off, stage_bytes, t.row_bytes);
+        ring.start(smem_base, a_lo_off, b_off, b_lo_off, stage_bytes, kRow);
         bool ok = true;
 #pragma unroll 1
         for (int ti = 0; ti < my_tiles && ok; ++ti) {
@@ -1029,9 +1031,9 @@ conv_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             if (!ok) break;
             tc_fence_after();
             const uint32_t tmem_d = tmem_base + a * uint32_t(pg.acc_stride);
-#define IOS_MMA_LOOP(MODE, WAIT) mma_loop<MODE>(t.k_iters, t.stages, WAIT, empty0, ring, tmem_d, idesc, idesc_wide, p)
+#define IOS_MMA_LOOP(FORM, WAIT) mma_loop<FORM>(t.k_iters, t.stages, WAIT, empty0, ring, tmem_d, idesc, idesc_wide, p)
             ok = kX3 ? (t.wide ? IOS_MMA_LOOP(3, ready0) : IOS_MMA_LOOP(1, ready0))
-                      : (kBf16 ? IOS_MMA_LOOP(2, full0) : IOS_MMA_LOOP(0, full0));
+                      : (kBf16 ? IOS_MMA_LOOP(MODE, full0) : IOS_MMA_LOOP(0, full0));
 #undef IOS_MMA_LOOP
             if (ok) umma_commit(acc_full0 + 8u * a);
         }
@@ -1538,13 +1540,14 @@ const char *conv_tc_encode_dense_weights(const ConvTcParams &p, ConvTcPlan *plan
 cudaError_t conv_tc_prepare() {
     const void *forms[] = {reinterpret_cast<const void *>(conv_tc_kernel<0, false>), reinterpret_cast<const void *>(conv_tc_kernel<0, true>),
                            reinterpret_cast<const void *>(conv_tc_kernel<1, false>), reinterpret_cast<const void *>(conv_tc_kernel<1, true>),
-                           reinterpret_cast<const void *>(conv_tc_kernel<2, false>), reinterpret_cast<const void *>(conv_tc_kernel<2, true>)};
+                           reinterpret_cast<const void *>(conv_tc_kernel<2, false>), reinterpret_cast<const void *>(conv_tc_kernel<2, true>),
+                           reinterpret_cast<const void *>(conv_tc_kernel<4, false>), reinterpret_cast<const void *>(conv_tc_kernel<4, true>)};
     for (const void *form : forms) {
         cudaError_t err = cudaFuncSetAttribute(form, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024);
         if (err != cudaSuccess) return err;
     }
     const void *resident[] = {reinterpret_cast<const void *>(conv_tc_persistent_kernel<0>), reinterpret_cast<const void *>(conv_tc_persistent_kernel<1>),
-                              reinterpret_cast<const void *>(conv_tc_persistent_kernel<2>)};
+                              reinterpret_cast<const void *>(conv_tc_persistent_kernel<2>), reinterpret_cast<const void *>(conv_tc_persistent_kernel<4>)};
     for (const void *form : resident) {
         cudaError_t err = cudaFuncSetAttribute(form, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024);
         if (err != cudaSuccess) return err;
@@ -1566,8 +1569,8 @@ void launch_conv_tc(const ConvTcParams &p, const ConvTcPlan &q, cudaStream_t str
         if (q.stages % cand == 0) t.producers = cand;
     t.flat = (q.flat_1x1 || q.im2col) ? 1 : 0;
     t.im2col = q.im2col;
-    t.row_bytes = q.half_rows ? 64 : 128;
-    t.a_bytes = q.box_w * q.box_h * q.box_n * t.row_bytes;
+    const int row_bytes = q.half_rows ? 64 : 128;
+    t.a_bytes = q.box_w * q.box_h * q.box_n * row_bytes;
     t.bf16 = q.bf16;
     t.chunk = (q.bf16 && !q.half_rows) ? 64 : 32;
     t.slab = q.bf16 ? 64 : 32;
@@ -1585,7 +1588,7 @@ void launch_conv_tc(const ConvTcParams &p, const ConvTcPlan &q, cudaStream_t str
     if (q.persistent) {
         pg.n_tiles = q.n_tiles;
         pg.total_tiles = q.tiles_w * q.tiles_h * q.tiles_n * q.n_tiles;
-        pg.staging_off = q.stages * (q.x3 ? 2 : 1) * (kTileM + q.bn) * t.row_bytes;
+        pg.staging_off = q.stages * (q.x3 ? 2 : 1) * (kTileM + q.bn) * row_bytes;
         pg.acc_stride = (t.wide ? 2 : 1) * ceil_div(q.bn, 32) * 32;
         cols = 32;
         while (cols < 2 * pg.acc_stride) cols *= 2;
@@ -1617,20 +1620,23 @@ void launch_conv_tc(const ConvTcParams &p, const ConvTcPlan &q, cudaStream_t str
     cfg.numAttrs = n_attr;
     const CUtensorMap &ma = *reinterpret_cast<const CUtensorMap *>(q.tmap_a), &mb = *reinterpret_cast<const CUtensorMap *>(q.tmap_b),
                       &mc = *reinterpret_cast<const CUtensorMap *>(q.tmap_c);
-    const int mode = q.x3 ? 1 : (q.bf16 ? 2 : 0);
+    const int mode = q.x3 ? 1 : (q.bf16 ? (q.half_rows ? 4 : 2) : 0);
     if (q.persistent) {
         if (mode == 1) cudaLaunchKernelEx(&cfg, conv_tc_persistent_kernel<1>, ma, mb, mc, p, t, pg);
         else if (mode == 2) cudaLaunchKernelEx(&cfg, conv_tc_persistent_kernel<2>, ma, mb, mc, p, t, pg);
+        else if (mode == 4) cudaLaunchKernelEx(&cfg, conv_tc_persistent_kernel<4>, ma, mb, mc, p, t, pg);
         else cudaLaunchKernelEx(&cfg, conv_tc_persistent_kernel<0>, ma, mb, mc, p, t, pg);
         return;
     }
     if (t.cluster) {
         if (mode == 1) cudaLaunchKernelEx(&cfg, conv_tc_kernel<1, true>, ma, mb, mc, p, t);
         else if (mode == 2) cudaLaunchKernelEx(&cfg, conv_tc_kernel<2, true>, ma, mb, mc, p, t);
+        else if (mode == 4) cudaLaunchKernelEx(&cfg, conv_tc_kernel<4, true>, ma, mb, mc, p, t);
         else cudaLaunchKernelEx(&cfg, conv_tc_kernel<0, true>, ma, mb, mc, p, t);
     } else {
         if (mode == 1) cudaLaunchKernelEx(&cfg, conv_tc_kernel<1, false>, ma, mb, mc, p, t);
         else if (mode == 2) cudaLaunchKernelEx(&cfg, conv_tc_kernel<2, false>, ma, mb, mc, p, t);
+        else if (mode == 4) cudaLaunchKernelEx(&cfg, conv_tc_kernel<4, false>, ma, mb, mc, p, t);
         else cudaLaunchKernelEx(&cfg, conv_tc_kernel<0, false>, ma, mb, mc, p, t);
     }
 }

@@ -448,7 +448,7 @@ private:
                 if (dry_) {
                     if (ws_need_.size() <= size_t(group_)) ws_need_.resize(group_ + 1, 0);
                     ws_need_[group_] = std::max(ws_need_[group_], slot.tcplan.workspace_bytes);
-                } else {
+                } else if (slot.tcplan.workspace_bytes > 0) {
                     if (size_t(group_) >= ws_offset_.size() || plan_.group_workspace_bytes[group_] < slot.tcplan.workspace_bytes)
                         throw std::runtime_error("internal: split-K workspace of a group slot is too small");
                     s.tc.workspace = reinterpret_cast<float *>(at(ws_offset_[group_]));
