@@ -259,10 +259,12 @@ __device__ __forceinline__ float round_tf32(float v) {
     return __uint_as_float(r);
 }
 
-// Optional diagnostics: CTA (0,0,0) stamps the SM clock at fixed points of its life.
+// Optional diagnostics: CTA (0,0,0) stamps the SM clock at fixed points of its life.  The stamps sit
+// in the single-thread role loops, where the mere test for them was measured at 3 % of batch-1
+// latency, so they exist only in the kTimeline instantiations (option "timeline").
 #define STAMP(slot)                                                                     \
     do {                                                                                \
-        if (p.timeline && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) p.timeline[slot] = clock64(); \
+        if (kTimeline && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) p.timeline[slot] = clock64(); \
     } while (0)
 
 // Byte offset of 16-byte column `c4` of row `row` inside a [rows][128 B] tile with the 128-byte swizzle.
@@ -346,7 +348,7 @@ struct MmaRing {
     }
 };
 
-template <int MODE>
+template <int MODE, bool kTimeline>
 __device__ __forceinline__ bool mma_loop(int n_it, int stages, uint32_t wait0, uint32_t empty0, MmaRing &ring, uint32_t tmem_d,
                                          uint32_t idesc, uint32_t idesc_wide, const ConvTcParams &p) {
 #pragma unroll 1
@@ -388,7 +390,7 @@ __device__ __forceinline__ bool mma_loop(int n_it, int stages, uint32_t wait0, u
 // and per reduction form
 // (kCluster: the split_k CTAs of a tile are a cluster): a CTA runs its code once, so what it does not
 // need should not be in its instruction stream.
-template <int MODE, bool kCluster>
+template <int MODE, bool kCluster, bool kTimeline>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ CUtensorMap tmap_c, const ConvTcParams p, const TileGeom t) {
@@ -560,7 +562,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const uint32_t idesc_wide = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(t.bn >> 2) << 17) | (uint32_t(kTileM >> 4) << 24);
             MmaRing ring;
             ring.start(smem_base, a_lo_off, b_off, b_lo_off, stage_bytes, kRow);
-#define IOS_MMA_LOOP(FORM, WAIT) mma_loop<FORM>(n_it, t.stages, WAIT, empty0, ring, tmem_base, idesc, idesc_wide, p)
+#define IOS_MMA_LOOP(FORM, WAIT) mma_loop<FORM, kTimeline>(n_it, t.stages, WAIT, empty0, ring, tmem_base, idesc, idesc_wide, p)
             const bool ok = kX3 ? (t.wide ? IOS_MMA_LOOP(3, ready0) : IOS_MMA_LOOP(1, ready0))
                                  : (kBf16 ? IOS_MMA_LOOP(MODE, full0) : IOS_MMA_LOOP(0, full0));
 #undef IOS_MMA_LOOP
@@ -1031,7 +1033,7 @@ conv_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             if (!ok) break;
             tc_fence_after();
             const uint32_t tmem_d = tmem_base + a * uint32_t(pg.acc_stride);
-#define IOS_MMA_LOOP(FORM, WAIT) mma_loop<FORM>(t.k_iters, t.stages, WAIT, empty0, ring, tmem_d, idesc, idesc_wide, p)
+#define IOS_MMA_LOOP(FORM, WAIT) mma_loop<FORM, false>(t.k_iters, t.stages, WAIT, empty0, ring, tmem_d, idesc, idesc_wide, p)
             ok = kX3 ? (t.wide ? IOS_MMA_LOOP(3, ready0) : IOS_MMA_LOOP(1, ready0))
                       : (kBf16 ? IOS_MMA_LOOP(MODE, full0) : IOS_MMA_LOOP(0, full0));
 #undef IOS_MMA_LOOP
@@ -1538,10 +1540,13 @@ const char *conv_tc_encode_dense_weights(const ConvTcParams &p, ConvTcPlan *plan
 }
 
 cudaError_t conv_tc_prepare() {
-    const void *forms[] = {reinterpret_cast<const void *>(conv_tc_kernel<0, false>), reinterpret_cast<const void *>(conv_tc_kernel<0, true>),
-                           reinterpret_cast<const void *>(conv_tc_kernel<1, false>), reinterpret_cast<const void *>(conv_tc_kernel<1, true>),
-                           reinterpret_cast<const void *>(conv_tc_kernel<2, false>), reinterpret_cast<const void *>(conv_tc_kernel<2, true>),
-                           reinterpret_cast<const void *>(conv_tc_kernel<4, false>), reinterpret_cast<const void *>(conv_tc_kernel<4, true>)};
+    const void *forms[] = {
+#define IOS_FORMS(MODE)                                                                                          \
+    reinterpret_cast<const void *>(conv_tc_kernel<MODE, false, false>), reinterpret_cast<const void *>(conv_tc_kernel<MODE, true, false>), \
+    reinterpret_cast<const void *>(conv_tc_kernel<MODE, false, true>), reinterpret_cast<const void *>(conv_tc_kernel<MODE, true, true>)
+        IOS_FORMS(0), IOS_FORMS(1), IOS_FORMS(2), IOS_FORMS(4)
+#undef IOS_FORMS
+    };
     for (const void *form : forms) {
         cudaError_t err = cudaFuncSetAttribute(form, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024);
         if (err != cudaSuccess) return err;
@@ -1628,17 +1633,22 @@ void launch_conv_tc(const ConvTcParams &p, const ConvTcPlan &q, cudaStream_t str
         else cudaLaunchKernelEx(&cfg, conv_tc_persistent_kernel<0>, ma, mb, mc, p, t, pg);
         return;
     }
-    if (t.cluster) {
-        if (mode == 1) cudaLaunchKernelEx(&cfg, conv_tc_kernel<1, true>, ma, mb, mc, p, t);
-        else if (mode == 2) cudaLaunchKernelEx(&cfg, conv_tc_kernel<2, true>, ma, mb, mc, p, t);
-        else if (mode == 4) cudaLaunchKernelEx(&cfg, conv_tc_kernel<4, true>, ma, mb, mc, p, t);
-        else cudaLaunchKernelEx(&cfg, conv_tc_kernel<0, true>, ma, mb, mc, p, t);
-    } else {
-        if (mode == 1) cudaLaunchKernelEx(&cfg, conv_tc_kernel<1, false>, ma, mb, mc, p, t);
-        else if (mode == 2) cudaLaunchKernelEx(&cfg, conv_tc_kernel<2, false>, ma, mb, mc, p, t);
-        else if (mode == 4) cudaLaunchKernelEx(&cfg, conv_tc_kernel<4, false>, ma, mb, mc, p, t);
-        else cudaLaunchKernelEx(&cfg, conv_tc_kernel<0, false>, ma, mb, mc, p, t);
-    }
+    const bool stamps = p.timeline != nullptr;
+#define IOS_LAUNCH(MODE)                                                                                         \
+    do {                                                                                                         \
+        if (t.cluster) {                                                                                         \
+            if (stamps) cudaLaunchKernelEx(&cfg, conv_tc_kernel<MODE, true, true>, ma, mb, mc, p, t);            \
+            else cudaLaunchKernelEx(&cfg, conv_tc_kernel<MODE, true, false>, ma, mb, mc, p, t);                  \
+        } else {                                                                                                 \
+            if (stamps) cudaLaunchKernelEx(&cfg, conv_tc_kernel<MODE, false, true>, ma, mb, mc, p, t);           \
+            else cudaLaunchKernelEx(&cfg, conv_tc_kernel<MODE, false, false>, ma, mb, mc, p, t);                 \
+        }                                                                                                        \
+    } while (0)
+    if (mode == 1) IOS_LAUNCH(1);
+    else if (mode == 2) IOS_LAUNCH(2);
+    else if (mode == 4) IOS_LAUNCH(4);
+    else IOS_LAUNCH(0);
+#undef IOS_LAUNCH
 }
 
 }  // namespace ios
