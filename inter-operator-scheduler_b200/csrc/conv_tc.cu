@@ -479,55 +479,65 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // Weights never depend on the previous kernel: the weight tiles of the first `stages` K steps are
     // requested before the grid dependency is waited for, so that under programmatic dependent launch
     // their latency hides behind the predecessor's tail -- one lane per stage, all at once.
-    if (warp == 0 && lane < min(n_it, t.stages)) {
+    if (warp == 2 && lane < min(n_it, t.stages)) {      // (an epilogue warp, idle at this point: warp 0 goes straight to the activations)
         const uint32_t stage = smem_base + uint32_t(lane) * stage_bytes;
         const uint32_t bar = full0 + 8u * lane;
         mbar_expect_tx(bar, uint32_t(t.a_bytes + passes * b_bytes));
         tma_load_2d(stage + b_off, &tmap_b, bar, (it_begin + lane) * t.chunk, cout0);
         if (kX3) tma_load_2d(stage + b_lo_off, &tmap_b, bar, (it_begin + lane) * t.chunk, t.cout_pad + cout0);
     }
-    if (!kCluster && ((warp == 0 && lane >= t.producers) || (warp == 1 && lane != 0))) return;
+    if (!kCluster && ((warp == 0 && lane >= max(t.producers, min(n_it, t.stages))) || (warp == 1 && lane != 0))) return;
 
     if (warp == 0) {
-        if (lane < t.producers) {
-            // ---------------- TMA producers ----------------
+        // ---------------- TMA producers ----------------
+        // The activation tiles of the first `stages` K steps go out at once, one lane per step (at batch 1
+        // a CTA of a split-K cluster has no more steps than that); their weight tiles are on their way.
+        const int early = min(n_it, t.stages);
+        if (lane < early) {
+            const int it = it_begin + lane;
+            const int tap = it / t.cchunks, cc = it - tap * t.cchunks;
+            const int r = tap / g.kw, sx = tap - r * g.kw;
+            const uint32_t stage = smem_base + uint32_t(lane) * stage_bytes;
+            const uint32_t bar = full0 + 8u * lane;
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            if (t.im2col) tma_load_im2col(stage, &tmap_a, bar, cc * t.chunk, im_w, im_h, n0, uint32_t(sx), uint32_t(r));
+            else if (t.flat) tma_load_4d(stage, &tmap_a, bar, cc * t.chunk, ow0, 0, 0);
+            else tma_load_4d(stage, &tmap_a, bar, cc * t.chunk, ow0 * g.sw - g.pw + sx, oh0 * g.sh - g.ph + r, n0);
+            if (lane == 0) STAMP(2);
+        }
+        if (!kCluster && lane >= t.producers) return;
+        if (lane < t.producers && n_it > t.stages) {
             // One thread gets through wait -> arm -> issue about once per 600-800 cycles, whatever the
-            // tiles' size, so `producers` lanes share the K steps: lane l serves steps l, l + P, ... and,
-            // P dividing the pipeline depth, owns stages l, l + P, ... for itself.
-            // (the weight tiles of the first `stages` K steps are on their way already)  Activations follow
-            // after the grid dependency.
+            // tiles' size, so `producers` lanes share the remaining K steps: lane l serves steps l + stages,
+            // l + stages + P, ... and, P dividing the pipeline depth, owns stages l, l + P, ... for itself.
             const int P = t.producers;
-            const int early = min(n_it, t.stages);
             asm volatile("griddepcontrol.wait;" ::: "memory");
             bool ok = true;
-            int next = lane;            // this lane's first K step whose activation tile is not requested yet
+            int next = lane + t.stages;     // this lane's first K step whose tiles are not requested yet
             // running position of this lane (divisions cost more than the loads they would steer):
             // stage s and its phase, channel chunk cc and filter tap (r, sx) of K step it_begin + i
-            int s = lane, phase = 1;
+            int s = lane, phase = 0;
             int cc, r, sx;
             {
-                const int it = it_begin + lane;
+                const int it = it_begin + next;
                 const int tap = it / t.cchunks;
                 cc = it - tap * t.cchunks;
                 r = tap / g.kw;
                 sx = tap - r * g.kw;
             }
 #pragma unroll 1
-            for (int i = lane; i < n_it; i += P) {
+            for (int i = next; i < n_it; i += P) {
                 const uint32_t stage = smem_base + uint32_t(s) * stage_bytes;
                 const uint32_t bar = full0 + 8u * s;
-                if (i >= t.stages) {
-                    ok = mbar_wait(empty0 + 8u * s, uint32_t(phase), p.error_flag);
-                    if (!ok) break;
-                    const int kcol = (it_begin + i) * t.chunk;
-                    mbar_expect_tx(bar, uint32_t(t.a_bytes + passes * b_bytes));
-                    tma_load_2d(stage + b_off, &tmap_b, bar, kcol, cout0);
-                    if (kX3) tma_load_2d(stage + b_lo_off, &tmap_b, bar, kcol, t.cout_pad + cout0);
-                }
+                ok = mbar_wait(empty0 + 8u * s, uint32_t(phase), p.error_flag);
+                if (!ok) break;
+                const int kcol = (it_begin + i) * t.chunk;
+                mbar_expect_tx(bar, uint32_t(t.a_bytes + passes * b_bytes));
+                tma_load_2d(stage + b_off, &tmap_b, bar, kcol, cout0);
+                if (kX3) tma_load_2d(stage + b_lo_off, &tmap_b, bar, kcol, t.cout_pad + cout0);
                 if (t.im2col) tma_load_im2col(stage, &tmap_a, bar, cc * t.chunk, im_w, im_h, n0, uint32_t(sx), uint32_t(r));
                 else if (t.flat) tma_load_4d(stage, &tmap_a, bar, cc * t.chunk, ow0, 0, 0);
                 else tma_load_4d(stage, &tmap_a, bar, cc * t.chunk, ow0 * g.sw - g.pw + sx, oh0 * g.sh - g.ph + r, n0);
-                if (i == 0) STAMP(2);
                 next = i + P;
                 s += P;
                 if (s >= t.stages) { s -= t.stages; phase ^= 1; }
@@ -539,15 +549,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             }
             if (!ok) {
                 atomicExch(p.error_flag, 1);
-                // drain: the loads already issued still land in this CTA's shared memory; a stage whose
-                // activation tile was never requested is completed by hand so that its barrier can fire;
-                // then the latest armed step of each stage this lane owns is waited for
-                int last = next - P;
-                for (int j = next; j < early; j += P) {
-                    asm volatile("mbarrier.complete_tx.shared::cta.relaxed.cta.b64 [%0], %1;" ::"r"(full0 + 8u * (j % t.stages)), "r"(uint32_t(t.a_bytes)) : "memory");
-                    last = j;
-                }
-                for (int j = last, k = 0; j >= 0 && k < t.stages; j -= P, k += P)
+                // drain: the loads already issued still land in this CTA's shared memory; the latest
+                // armed step of each stage this lane owns is waited for
+                for (int j = next - P, k = 0; j >= 0 && k < t.stages; j -= P, k += P)
                     mbar_wait(full0 + 8u * (j % t.stages), uint32_t((j / t.stages) & 1), nullptr);
             }
         }
