@@ -763,6 +763,14 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         if (threadIdx.x == 64) STAMP(7);
         tc_fence_before();
+        if (kCluster) {
+            // the accumulator has been read: give TMEM back now, behind the cluster barrier's wait
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (warp == 2) {
+                tc_fence_after();
+                tmem_dealloc(tmem_base, uint32_t(t.tmem_cols));
+            }
+        }
     }
     if (kCluster) {
         // Every thread of every CTA of the cluster passes this barrier, whatever happened before; its
@@ -848,7 +856,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (threadIdx.x == 64) STAMP(7);
         }
     }
-    if (warp < 2) return;       // the producer lanes and the MMA issuer have nothing left to do
+    if (warp < 2 || kCluster) return;   // the producer lanes and the MMA issuer have nothing left to do
     // warps 0 and 1 are gone by now or on their way out; the warps that read the accumulator free it
     asm volatile("bar.sync 1, 128;" ::: "memory");
     if (warp == 2) {
