@@ -15,6 +15,8 @@
 #ifndef IOS_RUNTIME_H_
 #define IOS_RUNTIME_H_
 
+#include <stddef.h>
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -79,6 +81,9 @@ IOS_API const char *ios_last_error(void);
  * key "pdl":       "1" (default; consecutive convolution kernels use programmatic dependent launch), "0"
  * key "stage_barriers": "1" (default; every stage joins all its groups, as the reference does), "0" (a group
  *                  waits only for the groups that produced its inputs)
+ * key "pdl_edges": "0"/"1"; in a captured schedule every kernel -> kernel dependency, also between groups
+ *                  on different streams, becomes a programmatic one: a kernel's set-up overlaps the tail of
+ *                  all its predecessors, not only of the one on its own stream
  * Testing aids (each switches one mechanism of the tensor-core convolution off or pins one choice):
  * "im2col" "1"/"0" (pixel tiles over the flattened pixel axis by im2col-mode loads / boxes of the image),
  * "stem" "1"/"0" (a convolution over at most 4 input channels runs on CUDA cores / on the tensor cores like the rest),
@@ -91,10 +96,18 @@ IOS_API const char *ios_last_error(void);
 IOS_API int ios_set_option(const char *key, const char *value);
 IOS_API int ios_get_option(const char *key, char *value, int capacity);
 
-/* Select the CUDA device used by subsequent calls of this process (reference: device 0 only,
- * src/ios/profile.cu:40-46). */
+/* Select the CUDA device used by subsequent calls of the calling thread; it also becomes the default
+ * of threads that never chose one (reference: device 0 only, src/ios/profile.cu:40-46).  An engine stays
+ * on the device it was created on and has streams of its own: engines on one or several devices can be
+ * driven from several host threads at once, each call taking only its engine's lock. */
 IOS_API int ios_set_device(int device);
 IOS_API int ios_device_count(int *count);
+
+/* Page-lock / release caller-owned host memory (cudaHostRegister, portable across devices) so that the
+ * copies of ios_engine_run / ios_engine_run_pipelined from and to it are asynchronous.  Used by the batch
+ * sharder for the shared-memory arrays its worker processes map.  No reference counterpart. */
+IOS_API int ios_host_register(void *memory, size_t bytes);
+IOS_API int ios_host_unregister(void *memory);
 
 /* ---- engine: build once, run many (replaces the per-call map()/unmap() of the reference,
  *      src/ios/ios_runtime.cu:1273-1285, 1318-1327, for serving and for benchmarking) ---------- */
@@ -107,6 +120,14 @@ IOS_API int ios_engine_create(const char *graph_json, int batch_size, int num_co
 IOS_API int ios_engine_destroy(ios_engine *engine);
 /* Host in -> host out.  input[batch, C, H, W], output[batch, Cexit, Hexit, Wexit]. */
 IOS_API int ios_engine_run(ios_engine *engine, const float *input, float *output);
+/* Host in -> host out for `count` batches in a row, copies overlapped with compute: while batch i runs,
+ * batch i + 1 is uploaded and the result of batch i - 1 downloaded (two staging buffers each way, three
+ * streams).  inputs[i] / outputs[i] are laid out as for ios_engine_run; the copies only overlap when the
+ * buffers are page-locked (cudaHostAlloc / cudaHostRegister), pageable memory works but serialises.
+ * Returns after the last result has arrived.  (The reference copies, runs and copies back strictly in
+ * turn, src/ios/ios_runtime.cu:1500-1517.) */
+IOS_API int ios_engine_run_pipelined(ios_engine *engine, int count, const float *const *inputs,
+                                     float *const *outputs);
 /* Execute `iters` forwards on the resident input; *ms_per_iter receives the CUDA-event time. */
 IOS_API int ios_engine_time(ios_engine *engine, int iters, float *ms_per_iter);
 /* Describe the plan: writes a JSON text (kernel launches per forward, arena bytes, workspace bytes,
@@ -149,10 +170,18 @@ IOS_API int ios_conv2d(const float *x, const float *w, const float *bias, float 
  * cudaStream_t, NULL = default stream) and NOT synchronised.  Every call shares the one array,
  * which keeps the previous call's contents (the words that must be zero are cleared in stream
  * order at the start of each call): calls that overlap on the GPU race.  The first call on a
- * device resolves the array's device address; make it before any stream capture begins. */
+ * device resolves the array's device address; make it before any stream capture begins.
+ * Results leave through bulk tensor stores when y is 16-byte aligned and cout % 4 == 0, through plain
+ * stores from registers otherwise: same values, any alignment of y and any cout are accepted. */
 IOS_API int ios_pointwise_conv_static_scratch(const float *x, const float *w, const float *bias, float *y,
                                               int pixels, int cin, int cout, int act, int split_k,
                                               void *cuda_stream);
+
+/* Companion of the call above (it, too, has no counterpart in the reference): waits for cuda_stream,
+ * then reads the time-out word of the static scratch -- without allocating -- and returns
+ * IOS_ERR_TIMEOUT if a bounded wait inside the kernel ran out since the last check (the output of that
+ * call is then incomplete; the word and the counters are cleared), IOS_OK otherwise. */
+IOS_API int ios_static_scratch_status(void *cuda_stream);
 
 #ifdef __cplusplus
 }

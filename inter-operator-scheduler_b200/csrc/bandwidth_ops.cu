@@ -73,6 +73,7 @@ inline int grid_for(long work, int threads, int max_blocks = 148 * 32) {
 // ---------------------------------------------------------------------------------------------
 template <typename T, bool kVec>
 __global__ void __launch_bounds__(kThreads) sum_act_kernel(const SumActParams p) {
+    grid_dependency_entry();
     const int lanes = kVec ? (p.C + 3) / 4 : p.C;      // work items per pixel
     const long total = p.pixels * lanes;
     T *out = static_cast<T *>(p.out);
@@ -119,6 +120,7 @@ __global__ void __launch_bounds__(kThreads) sum_act_kernel(const SumActParams p)
 // ---------------------------------------------------------------------------------------------
 template <typename T, bool kVec>
 __global__ void __launch_bounds__(kThreads) pool_kernel(const PoolParams p) {
+    grid_dependency_entry();
     const int lanes = kVec ? (p.in.C + 3) / 4 : p.in.C;
     const long total = p.out.pixels() * lanes;
     const float inv_window = 1.0f / float(p.kh * p.kw);   // padding counts (CUDNN_POOLING_AVERAGE_COUNT_INCLUDE_PADDING)
@@ -235,6 +237,7 @@ template <> struct VecIo<__nv_bfloat16, 8> {
 // the reference's mode, src/ios/ios_runtime.cu:546-553).
 template <typename T, int V, bool kMax>
 __global__ void __launch_bounds__(kThreads) pool3x3_kernel(const PoolParams p, int rows_per_thread) {
+    grid_dependency_entry();
     typedef typename VecIo<T, V>::Raw Raw;
     constexpr int kRows = 4;
     // grid: x covers (output column, channel group), y the row segments, z the images -- no 64-bit index arithmetic
@@ -327,6 +330,7 @@ void launch_pool3x3(const PoolParams &p, cudaStream_t stream) {
 // each warp reads one contiguous span per pixel; partial results meet in shared memory.
 template <typename T>
 __global__ void __launch_bounds__(256) global_pool_kernel(const PoolParams p) {
+    grid_dependency_entry();
     __shared__ float part[8][33];
     const int slabs = (p.in.C + 31) / 32;
     const int n = blockIdx.x / slabs;
@@ -356,6 +360,7 @@ __global__ void __launch_bounds__(256) global_pool_kernel(const PoolParams p) {
 // run along the respective fastest axis.  The NCHW side is always float32 (the API boundary).
 template <typename T>
 __global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const float *__restrict__ src, TensorRef dst, int round_out) {
+    grid_dependency_entry();
     __shared__ float tile[32][33];
     const int hw = dst.H * dst.W;
     const int n = blockIdx.z;
@@ -375,6 +380,7 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const float *__restri
 
 template <typename T>
 __global__ void __launch_bounds__(256) nhwc_to_nchw_kernel(TensorRef src, float *__restrict__ dst) {
+    grid_dependency_entry();
     __shared__ float tile[32][33];
     const int hw = src.H * src.W;
     const int n = blockIdx.z;

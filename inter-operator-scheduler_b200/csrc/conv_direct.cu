@@ -65,6 +65,7 @@ constexpr int kCoPerThread = 4;
 
 template <typename T>
 __global__ void __launch_bounds__(128) conv_direct_kernel(const ConvDirectParams p) {
+    grid_dependency_entry();
     const ConvGeom &g = p.g;
     const int cin_g = g.Cin / g.groups, cout_g = g.Cout / g.groups;
     const int quads_g = (cout_g + kCoPerThread - 1) / kCoPerThread;
@@ -118,6 +119,7 @@ __global__ void __launch_bounds__(128) conv_direct_kernel(const ConvDirectParams
 // windows may reach outside the image.
 template <typename T, int CG, int PX, int KH, int KW, bool kPadded>
 __global__ void __launch_bounds__(128, 4) conv_few_channels_kernel(const ConvDirectParams p, int pixels_per_block) {
+    grid_dependency_entry();
     extern __shared__ float4 w_s4[];
     constexpr int Q = CG / 4;
     const ConvGeom &g = p.g;
@@ -252,6 +254,7 @@ void launch_few_channels(const ConvDirectParams &p, cudaStream_t stream) {
 
 template <typename T, bool kVec>
 __global__ void __launch_bounds__(256) conv_depthwise_kernel(const ConvDirectParams p) {
+    grid_dependency_entry();
     const ConvGeom &g = p.g;
     const int lanes = kVec ? (g.Cout + 3) / 4 : g.Cout;   // the last group may be partial: stored element by element
     const int wrow = (g.Cout + 3) / 4 * 4;                // packed weight rows are padded to a multiple of 4

@@ -35,6 +35,17 @@ struct TensorRef {
     __host__ __device__ T *as() const { return static_cast<T *>(ptr); }
 };
 
+#ifdef __CUDACC__
+// First statement of every kernel that runs inside a schedule.  A captured schedule may connect kernels
+// by programmatic dependencies: a kernel is then started before its predecessors have finished and must
+// wait here before it reads or writes anything they touch; its own successors may be started at once.
+// Without such a dependency both instructions do nothing.
+__device__ __forceinline__ void grid_dependency_entry() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+#endif
+
 constexpr int kMaxSumInputs = 8;
 
 // out = act(in_0 (+|*) in_1 ... in_{k-1}); k = 1 with act = identity is a strided copy.

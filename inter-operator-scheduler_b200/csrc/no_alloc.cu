@@ -15,7 +15,11 @@
 //    are always written before they are read; two calls that overlap on the GPU (different
 //    streams, no dependency) race on it and give undefined results;
 //  * the first call on a device looks up the array's device address and raises the kernel's
-//    shared-memory limit; make that first call outside of any stream capture.
+//    shared-memory limit; make that first call outside of any stream capture;
+//  * the call returns once the work is enqueued.  Whether a bounded wait inside the kernel ran out
+//    is only known afterwards: ios_static_scratch_status() synchronises the stream, reads the
+//    time-out word (again without allocating) and reports IOS_ERR_TIMEOUT, in which case y is not
+//    complete.
 #include <cuda_runtime.h>
 
 #include <cstdio>
@@ -143,6 +147,39 @@ extern "C" int ios_pointwise_conv_static_scratch(const float *x, const float *w,
         static thread_local char text[160];
         std::snprintf(text, sizeof text, "launching the convolution failed: %s", cudaGetErrorString(err));
         return fail(IOS_ERR_CUDA, text);
+    }
+    record_error("");
+    return IOS_OK;
+}
+
+extern "C" int ios_static_scratch_status(void *cuda_stream) {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return fail(IOS_ERR_CUDA, "no current CUDA device");
+    if (device < 0 || device >= kMaxDevices) return fail(IOS_ERR_LIMIT, "device index beyond the supported 64");
+    unsigned char *scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_setup_mutex);
+        if (g_devices[device].ready) scratch = g_devices[device].scratch;
+    }
+    if (!scratch) {                       // nothing has run on this device yet
+        record_error("");
+        return IOS_OK;
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+    cudaError_t err = cudaStreamSynchronize(stream);
+    int word = 0;
+    if (err == cudaSuccess) err = cudaMemcpy(&word, scratch, sizeof word, cudaMemcpyDeviceToHost);
+    if (err != cudaSuccess) {
+        static thread_local char text[160];
+        std::snprintf(text, sizeof text, "reading the time-out word failed: %s", cudaGetErrorString(err));
+        return fail(IOS_ERR_CUDA, text);
+    }
+    if (word != 0) {
+        // leave the scratch ready for the next call: the word and the arrival counters start at zero
+        cudaMemset(scratch, 0, kFlagBytes + kCounterBytes);
+        static thread_local char text[160];
+        std::snprintf(text, sizeof text, "a bounded wait inside the convolution kernel ran out (code %d): the output is incomplete", word);
+        return fail(IOS_ERR_TIMEOUT, text);
     }
     record_error("");
     return IOS_OK;

@@ -28,6 +28,7 @@ struct Options {
     bool pdl = true;            // programmatic dependent launch between consecutive convolution kernels
     bool stage_barriers = true; // join all groups after every stage (the reference's semantics); false: data-flow edges
     bool use_graph = true;      // executor: CUDA graph or plain streams
+    bool pdl_edges = false;     // captured graphs: every kernel -> kernel edge becomes a programmatic dependency
     bool allow_tc = true;       // conv: auto or direct
     int force_split_k = 0;      // testing aid: > 0 overrides the split-K choice
     int force_bn = 0;           // testing aid: > 0 overrides the output-channel tile width

@@ -57,13 +57,49 @@ struct MissingWeights : std::runtime_error {
             throw CudaError(std::string(#expr) + ": " + cudaGetErrorString(err__));                     \
     } while (0)
 
-// ---- device context: streams, events, arena ------------------------------------------------
-struct DeviceContext {
-    int device = -1;
-    int sm_count = 148;
+// ---- streams and events of one executor ---------------------------------------------------
+// Group j of a stage runs on streams[j]; events are the fork / join edges.  The process-wide context of
+// a device owns one set (used by the latency and inference entry points), every engine owns its own, so
+// that engines run side by side from several host threads.
+struct StreamSet {
     std::vector<cudaStream_t> streams;
     std::vector<cudaEvent_t> events;       // fork / join edges, reused by every plan
     cudaEvent_t t_start = nullptr, t_end = nullptr;
+
+    void init_timers() {
+        if (!t_start) CUDA_OK(cudaEventCreate(&t_start));
+        if (!t_end) CUDA_OK(cudaEventCreate(&t_end));
+    }
+    void need_streams(int n) {
+        while (int(streams.size()) < n) {
+            cudaStream_t s;
+            CUDA_OK(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+            streams.push_back(s);
+        }
+    }
+    cudaEvent_t event(size_t i) {
+        while (events.size() <= i) {
+            cudaEvent_t e;
+            CUDA_OK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+            events.push_back(e);
+        }
+        return events[i];
+    }
+    void release() {
+        for (cudaStream_t s : streams) cudaStreamDestroy(s);
+        for (cudaEvent_t e : events) cudaEventDestroy(e);
+        if (t_start) cudaEventDestroy(t_start);
+        if (t_end) cudaEventDestroy(t_end);
+        streams.clear();
+        events.clear();
+        t_start = t_end = nullptr;
+    }
+};
+
+// ---- device context: shared streams and the grow-only arena --------------------------------
+struct DeviceContext : StreamSet {
+    int device = -1;
+    int sm_count = 148;
     char *arena = nullptr;
     size_t arena_capacity = 0;
 
@@ -82,24 +118,8 @@ struct DeviceContext {
             throw CudaError(std::string("device '") + prop.name + "' is not sm_100: the kernels are built for B200 only");
         sm_count = prop.multiProcessorCount;
         CUDA_OK(conv_tc_prepare());
-        CUDA_OK(cudaEventCreate(&t_start));
-        CUDA_OK(cudaEventCreate(&t_end));
+        init_timers();
         device = dev;
-    }
-    void need_streams(int n) {
-        while (int(streams.size()) < n) {
-            cudaStream_t s;
-            CUDA_OK(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
-            streams.push_back(s);
-        }
-    }
-    cudaEvent_t event(size_t i) {
-        while (events.size() <= i) {
-            cudaEvent_t e;
-            CUDA_OK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
-            events.push_back(e);
-        }
-        return events[i];
     }
     char *need_arena(size_t bytes) {
         if (bytes > arena_capacity) {
@@ -129,12 +149,18 @@ struct DeviceContext {
 
 std::map<int, DeviceContext> g_contexts;   // one per device this process has used
 
-DeviceContext &context() {
-    DeviceContext &ctx = g_contexts[g_device];
-    ctx.init(g_device);
-    CUDA_OK(cudaSetDevice(g_device));
+// The device of the calling thread: what this thread last passed to ios_set_device, else the process default.
+thread_local int t_device = -1;
+int current_device() { return t_device >= 0 ? t_device : g_device; }
+
+// Callers hold g_mutex.
+DeviceContext &context(int device) {
+    DeviceContext &ctx = g_contexts[device];
+    ctx.init(device);
+    CUDA_OK(cudaSetDevice(device));
     return ctx;
 }
+DeviceContext &context() { return context(current_device()); }
 
 // ---- issuing a plan -------------------------------------------------------------------------
 void launch_step(const Step &s, cudaStream_t stream) {
@@ -152,7 +178,7 @@ void launch_step(const Step &s, cudaStream_t stream) {
 // edge when the producer ran on another stream).  Legal because no buffer of a plan is ever reused:
 // read-after-write is the only hazard.  The schedule keeps deciding what is merged and what shares
 // a stream; a short branch no longer idles until the longest group of its stage has finished.
-void issue_forward_dataflow(DeviceContext &ctx, const Plan &plan) {
+void issue_forward_dataflow(StreamSet &ctx, const Plan &plan) {
     ctx.need_streams(plan.max_groups);
     cudaStream_t spine = ctx.streams[0];
     const Model &m = plan.model;
@@ -213,7 +239,7 @@ void issue_forward_dataflow(DeviceContext &ctx, const Plan &plan) {
 
 // Issues one forward on the context's streams.  stage_marks (optional) receives one timing event
 // per stage, recorded on stream 0 after the stage's groups have joined.
-void issue_forward(DeviceContext &ctx, const Plan &plan, const std::vector<cudaEvent_t> *stage_marks) {
+void issue_forward(StreamSet &ctx, const Plan &plan, const std::vector<cudaEvent_t> *stage_marks) {
     if (!stage_marks && !plan.options.stage_barriers) {
         issue_forward_dataflow(ctx, plan);
         return;
@@ -254,8 +280,35 @@ struct GraphExec {
     }
 };
 
+// Turns every full kernel -> kernel dependency of a captured graph into a programmatic one, so that the
+// prologue of a kernel (barrier set-up, tensor-memory allocation, the first weight tiles) also overlaps the
+// tail of predecessors that ran on OTHER streams -- the fork and join edges of a multi-group stage.  Stream
+// capture only makes the edge to the predecessor on the same stream programmatic.  Every kernel of this
+// library executes griddepcontrol.wait before it touches memory another kernel writes or reads.
+void make_edges_programmatic(cudaGraph_t graph) {
+    size_t n = 0;
+    CUDA_OK(cudaGraphGetEdges_v2(graph, nullptr, nullptr, nullptr, &n));
+    if (n == 0) return;
+    std::vector<cudaGraphNode_t> from(n), to(n);
+    std::vector<cudaGraphEdgeData> data(n);
+    CUDA_OK(cudaGraphGetEdges_v2(graph, from.data(), to.data(), data.data(), &n));
+    for (size_t i = 0; i < n; ++i) {
+        if (data[i].type != cudaGraphDependencyTypeDefault) continue;
+        cudaGraphNodeType tf, tt;
+        CUDA_OK(cudaGraphNodeGetType(from[i], &tf));
+        CUDA_OK(cudaGraphNodeGetType(to[i], &tt));
+        if (tf != cudaGraphNodeTypeKernel || tt != cudaGraphNodeTypeKernel) continue;
+        CUDA_OK(cudaGraphRemoveDependencies_v2(graph, &from[i], &to[i], &data[i], 1));
+        cudaGraphEdgeData edge = {};
+        edge.from_port = cudaGraphKernelNodePortProgrammatic;
+        edge.to_port = 0;
+        edge.type = cudaGraphDependencyTypeProgrammatic;
+        CUDA_OK(cudaGraphAddDependencies_v2(graph, &from[i], &to[i], &edge, 1));
+    }
+}
+
 template <class F>
-void capture(DeviceContext &ctx, GraphExec *out, F &&body) {
+void capture(StreamSet &ctx, GraphExec *out, F &&body, bool programmatic_edges = false) {
     cudaStream_t spine = ctx.streams[0];
     cudaGraph_t graph = nullptr;
     CUDA_OK(cudaStreamBeginCapture(spine, cudaStreamCaptureModeThreadLocal));
@@ -268,7 +321,25 @@ void capture(DeviceContext &ctx, GraphExec *out, F &&body) {
         throw;
     }
     CUDA_OK(cudaStreamEndCapture(spine, &graph));
-    cudaError_t err = cudaGraphInstantiate(&out->exec, graph, 0);
+    cudaError_t err = cudaErrorUnknown;
+    if (programmatic_edges) {
+        // on a driver that refuses such a graph the captured edges are kept as they were
+        cudaGraph_t upgraded = nullptr;
+        if (cudaGraphClone(&upgraded, graph) == cudaSuccess) {
+            try {
+                make_edges_programmatic(upgraded);
+                err = cudaGraphInstantiate(&out->exec, upgraded, 0);
+            } catch (const CudaError &) {
+                err = cudaErrorUnknown;
+            }
+            cudaGraphDestroy(upgraded);
+            if (err != cudaSuccess) {
+                cudaGetLastError();
+                out->exec = nullptr;
+            }
+        }
+    }
+    if (err != cudaSuccess) err = cudaGraphInstantiate(&out->exec, graph, 0);
     cudaGraphDestroy(graph);
     CUDA_OK(err);
 }
@@ -298,6 +369,8 @@ void check_error_flag(const Plan &plan, char *base) {
     CUDA_OK(cudaMemcpy(&flag, base + plan.error_flag_offset, sizeof flag, cudaMemcpyDeviceToHost));
     if (flag != 0) {
         CUDA_OK(cudaMemset(base + plan.error_flag_offset, 0, sizeof(int)));
+        // a CTA that gave up never reached its tile's arrival counter: start the next run from zero again
+        if (plan.zero_bytes) CUDA_OK(cudaMemset(base + plan.zero_begin, 0, plan.zero_bytes));
         throw TimeoutError("a bounded wait inside the convolution kernel ran out (code " + std::to_string(flag) + ")");
     }
 }
@@ -341,18 +414,19 @@ void load_parameters(const Plan &plan, char *base, const HostWeights *host, cuda
 }
 
 // Lays the plan out, binds it to `base` (or to the shared arena when base is null).
-char *bind_plan(DeviceContext &ctx, Plan *plan, char *base) {
+char *bind_plan(DeviceContext &ctx, Plan *plan, char *base, StreamSet *streams = nullptr) {
     plan->options = g_options;
     plan_layout(plan, ctx.sm_count);
     if (!base) base = ctx.need_arena(plan->arena_bytes);
     plan_bind(plan, base, ctx.sm_count);
-    ctx.need_streams(plan->max_groups);
-    CUDA_OK(cudaMemsetAsync(base + plan->error_flag_offset, 0, 256, ctx.streams[0]));
-    if (plan->zero_bytes) CUDA_OK(cudaMemsetAsync(base + plan->zero_begin, 0, plan->zero_bytes, ctx.streams[0]));
+    StreamSet &set = streams ? *streams : ctx;
+    set.need_streams(plan->max_groups);
+    CUDA_OK(cudaMemsetAsync(base + plan->error_flag_offset, 0, 256, set.streams[0]));
+    if (plan->zero_bytes) CUDA_OK(cudaMemsetAsync(base + plan->zero_begin, 0, plan->zero_bytes, set.streams[0]));
     return base;
 }
 
-void fill_inputs(DeviceContext &ctx, const Plan &plan, char *base) {
+void fill_inputs(StreamSet &ctx, const Plan &plan, char *base) {
     uint32_t seed = 1000;
     for (size_t i = 0; i < plan.model.placeholders.size(); ++i) {
         const TensorRef &t = plan.tensors[plan.model.placeholders[i]];
@@ -393,7 +467,7 @@ void measure_graph(const Model &model_in, int warmup, int number, int repeat, bo
         else issue_forward(ctx, plan, profile_stage ? &marks : nullptr);
     };
     try {
-        if (replay) capture(ctx, &exec, [&]() { issue_forward(ctx, plan, nullptr); });
+        if (replay) capture(ctx, &exec, [&]() { issue_forward(ctx, plan, nullptr); }, plan.options.pdl_edges);
         for (int i = 0; i < warmup; ++i) forward();
         CUDA_OK(cudaDeviceSynchronize());
         check_error_flag(plan, base);
@@ -442,7 +516,7 @@ void measure_stage(const Model &model_in, int warmup, int number, int repeat, fl
     cudaStream_t spine = ctx.streams[0];
     GraphExec exec;
     const bool replay = plan.options.use_graph;
-    if (replay) capture(ctx, &exec, [&]() { for (int t = 0; t < number; ++t) issue_forward(ctx, plan, nullptr); });
+    if (replay) capture(ctx, &exec, [&]() { for (int t = 0; t < number; ++t) issue_forward(ctx, plan, nullptr); }, plan.options.pdl_edges);
     auto sample = [&]() {
         if (replay) CUDA_OK(cudaGraphLaunch(exec.exec, spine));
         else for (int t = 0; t < number; ++t) issue_forward(ctx, plan, nullptr);
@@ -529,19 +603,35 @@ int guarded(F &&body) {
 void record_error(const char *message) { g_last_error = message ? message : ""; }
 
 // ---- engine ----------------------------------------------------------------------------------
+// A plan bound to memory, streams and events of its own: engines on the same or on different devices run
+// side by side from several host threads; a call only takes the engine's own lock.
 struct EngineImpl {
     Plan plan;
     int device = 0;
     char *base = nullptr;
     size_t bytes = 0;
+    std::mutex mutex;
+    StreamSet set;
     GraphExec exec;            // staging -> NHWC, forward, NHWC -> staging
     GraphExec exec_core;       // forward only (resident input)
     size_t in_bytes = 0, out_bytes = 0;
+    // host-buffer pipeline: a second staging pair behind the plan's arena, copy streams and their events
+    size_t stage_in_off[2] = {0, 0}, stage_out_off[2] = {0, 0};
+    cudaStream_t copy_in = nullptr, copy_out = nullptr;
+    cudaEvent_t in_ready[2] = {nullptr, nullptr}, in_free[2] = {nullptr, nullptr};
+    cudaEvent_t out_ready[2] = {nullptr, nullptr}, out_free[2] = {nullptr, nullptr};
+    int *flag_host = nullptr;  // pinned: the time-out word travels with the results, no extra round trip
+
     ~EngineImpl() {
-        if (base) {
-            cudaSetDevice(device);
-            cudaFree(base);
-        }
+        cudaSetDevice(device);
+        set.release();
+        if (copy_in) cudaStreamDestroy(copy_in);
+        if (copy_out) cudaStreamDestroy(copy_out);
+        for (int i = 0; i < 2; ++i)
+            for (cudaEvent_t e : {in_ready[i], in_free[i], out_ready[i], out_free[i]})
+                if (e) cudaEventDestroy(e);
+        if (flag_host) cudaFreeHost(flag_host);
+        if (base) cudaFree(base);
     }
 };
 
@@ -644,6 +734,7 @@ int ios_set_option(const char *key, const char *value) {
         else if (k == "half_rows" && (v == "0" || v == "1")) g_options.no_half_rows = v == "0";
         else if (k == "timeline") g_options.timeline = v == "1";
         else if (k == "stage_barriers" && (v == "0" || v == "1")) g_options.stage_barriers = v == "1";
+        else if (k == "pdl_edges" && (v == "0" || v == "1")) g_options.pdl_edges = v == "1";
         else throw ArgumentError("unknown option " + k + "=" + v);
     });
 }
@@ -651,11 +742,15 @@ int ios_set_option(const char *key, const char *value) {
 int ios_get_option(const char *key, char *value, int capacity) {
     return guarded([&]() {
         if (!key || !value || capacity <= 0) throw ArgumentError("key and value must not be NULL");
+        std::lock_guard<std::mutex> lock(g_mutex);
         const std::string k = key;
         std::string v;
         if (k == "precision") v = g_options.bf16 ? "bf16" : !g_options.tf32 ? "fp32" : g_options.three_pass ? "tf32x3" : "tf32";
         else if (k == "pdl") v = g_options.pdl ? "1" : "0";
         else if (k == "stage_barriers") v = g_options.stage_barriers ? "1" : "0";
+        else if (k == "pdl_edges") v = g_options.pdl_edges ? "1" : "0";
+        else if (k == "bulk_store") v = g_options.no_bulk_store ? "0" : "1";
+        else if (k == "persistent") v = g_options.no_persistent ? "0" : "1";
         else if (k == "executor") v = g_options.use_graph ? "graph" : "streams";
         else if (k == "conv") v = g_options.allow_tc ? "auto" : "direct";
         else if (k == "split_k") v = std::to_string(g_options.force_split_k);
@@ -670,7 +765,8 @@ int ios_set_device(int device) {
         int count = 0;
         CUDA_OK(cudaGetDeviceCount(&count));
         if (device < 0 || device >= count) throw ArgumentError("device index out of range");
-        g_device = device;
+        g_device = device;      // the default of threads that never chose one
+        t_device = device;      // what this thread uses from now on
     });
 }
 
@@ -678,6 +774,20 @@ int ios_device_count(int *count) {
     return guarded([&]() {
         if (!count) throw ArgumentError("count must not be NULL");
         CUDA_OK(cudaGetDeviceCount(count));
+    });
+}
+
+int ios_host_register(void *memory, size_t bytes) {
+    return guarded([&]() {
+        if (!memory || bytes == 0) throw ArgumentError("memory must not be NULL and bytes > 0");
+        CUDA_OK(cudaHostRegister(memory, bytes, cudaHostRegisterPortable));
+    });
+}
+
+int ios_host_unregister(void *memory) {
+    return guarded([&]() {
+        if (!memory) throw ArgumentError("memory must not be NULL");
+        CUDA_OK(cudaHostUnregister(memory));
     });
 }
 
@@ -692,36 +802,50 @@ int ios_engine_create(const char *graph_json, int batch_size, int num_convs, cha
         DeviceContext &ctx = context();
         std::unique_ptr<ios_engine> holder(new ios_engine);
         EngineImpl &e = holder->impl;
-        e.device = g_device;
+        e.device = ctx.device;
         e.plan.model = model;
         e.plan.options = g_options;
         plan_layout(&e.plan, ctx.sm_count);
-        e.bytes = e.plan.arena_bytes;
+        const Op &in_op = e.plan.model.ops[e.plan.model.placeholders[0]];
+        const Op &out_op = e.plan.model.ops[e.plan.model.output];
+        e.in_bytes = size_t(batch_size) * in_op.C * in_op.H * in_op.W * sizeof(float);
+        e.out_bytes = size_t(batch_size) * out_op.C * out_op.H * out_op.W * sizeof(float);
+        // the plan's arena, then the second staging pair of the host-buffer pipeline
+        auto up = [](size_t v) { return (v + 255) / 256 * 256; };
+        e.stage_in_off[1] = up(e.plan.arena_bytes);
+        e.stage_out_off[1] = e.stage_in_off[1] + up(e.in_bytes);
+        e.bytes = e.stage_out_off[1] + up(e.out_bytes);
         CUDA_OK(cudaMalloc(&e.base, e.bytes));
         CUDA_OK(cudaMemset(e.base, 0, e.bytes));
         CUDA_OK(cudaDeviceSynchronize());      // the working streams do not wait for the default stream
-        bind_plan(ctx, &e.plan, e.base);
-        cudaStream_t spine = ctx.streams[0];
+        e.set.init_timers();
+        bind_plan(ctx, &e.plan, e.base, &e.set);
+        e.stage_in_off[0] = e.plan.staging_in_offset;
+        e.stage_out_off[0] = e.plan.staging_out_offset;
+        CUDA_OK(cudaStreamCreateWithFlags(&e.copy_in, cudaStreamNonBlocking));
+        CUDA_OK(cudaStreamCreateWithFlags(&e.copy_out, cudaStreamNonBlocking));
+        for (int i = 0; i < 2; ++i)
+            for (cudaEvent_t *ev : {&e.in_ready[i], &e.in_free[i], &e.out_ready[i], &e.out_free[i]})
+                CUDA_OK(cudaEventCreateWithFlags(ev, cudaEventDisableTiming));
+        CUDA_OK(cudaHostAlloc(reinterpret_cast<void **>(&e.flag_host), 64, cudaHostAllocDefault));
+        e.flag_host[0] = 0;
+        cudaStream_t spine = e.set.streams[0];
         if (filter_data && bias_data && conv_names) {
             HostWeights hw{num_convs, conv_names, filter_data, bias_data};
             load_parameters(e.plan, e.base, &hw, spine);
         } else {
             load_parameters(e.plan, e.base, nullptr, spine);
         }
-        fill_inputs(ctx, e.plan, e.base);
-        const Op &in_op = e.plan.model.ops[e.plan.model.placeholders[0]];
-        const Op &out_op = e.plan.model.ops[e.plan.model.output];
-        e.in_bytes = size_t(batch_size) * in_op.C * in_op.H * in_op.W * sizeof(float);
-        e.out_bytes = size_t(batch_size) * out_op.C * out_op.H * out_op.W * sizeof(float);
-        float *stage_in = reinterpret_cast<float *>(e.base + e.plan.staging_in_offset);
-        float *stage_out = reinterpret_cast<float *>(e.base + e.plan.staging_out_offset);
+        fill_inputs(e.set, e.plan, e.base);
+        float *stage_in = reinterpret_cast<float *>(e.base + e.stage_in_off[0]);
+        float *stage_out = reinterpret_cast<float *>(e.base + e.stage_out_off[0]);
         if (e.plan.options.use_graph) {
-            capture(ctx, &e.exec, [&]() {
+            capture(e.set, &e.exec, [&]() {
                 launch_nchw_to_nhwc(stage_in, e.plan.tensors[e.plan.model.placeholders[0]], e.plan.input_round_tf32, spine);
-                issue_forward(ctx, e.plan, nullptr);
+                issue_forward(e.set, e.plan, nullptr);
                 launch_nhwc_to_nchw(e.plan.tensors[e.plan.model.output], stage_out, spine);
-            });
-            capture(ctx, &e.exec_core, [&]() { issue_forward(ctx, e.plan, nullptr); });
+            }, e.plan.options.pdl_edges);
+            capture(e.set, &e.exec_core, [&]() { issue_forward(e.set, e.plan, nullptr); }, e.plan.options.pdl_edges);
         }
         CUDA_OK(cudaDeviceSynchronize());
         *engine = holder.release();
@@ -731,40 +855,97 @@ int ios_engine_create(const char *graph_json, int batch_size, int num_convs, cha
 int ios_engine_destroy(ios_engine *engine) {
     return guarded([&]() {
         if (!engine) return;
-        std::lock_guard<std::mutex> lock(g_mutex);
-        cudaSetDevice(engine->impl.device);
-        cudaDeviceSynchronize();
+        {
+            std::lock_guard<std::mutex> lock(engine->impl.mutex);
+            cudaSetDevice(engine->impl.device);
+            cudaDeviceSynchronize();
+        }
         delete engine;
     });
 }
 
-static void engine_forward(DeviceContext &ctx, EngineImpl &e, bool with_layout) {
-    cudaStream_t spine = ctx.streams[0];
-    float *stage_in = reinterpret_cast<float *>(e.base + e.plan.staging_in_offset);
-    float *stage_out = reinterpret_cast<float *>(e.base + e.plan.staging_out_offset);
+static void engine_forward(EngineImpl &e, bool with_layout) {
+    cudaStream_t spine = e.set.streams[0];
+    float *stage_in = reinterpret_cast<float *>(e.base + e.stage_in_off[0]);
+    float *stage_out = reinterpret_cast<float *>(e.base + e.stage_out_off[0]);
     if (e.plan.options.use_graph) {
         CUDA_OK(cudaGraphLaunch(with_layout ? e.exec.exec : e.exec_core.exec, spine));
         return;
     }
     if (with_layout)
         launch_nchw_to_nhwc(stage_in, e.plan.tensors[e.plan.model.placeholders[0]], e.plan.input_round_tf32, spine);
-    issue_forward(ctx, e.plan, nullptr);
+    issue_forward(e.set, e.plan, nullptr);
     if (with_layout) launch_nhwc_to_nchw(e.plan.tensors[e.plan.model.output], stage_out, spine);
+}
+
+// The time-out word rides behind the results: an asynchronous copy into pinned memory on the stream
+// that was just used, read after the stream has been synchronised.
+static void engine_fetch_flag(EngineImpl &e, cudaStream_t stream) {
+    CUDA_OK(cudaMemcpyAsync(e.flag_host, e.base + e.plan.error_flag_offset, sizeof(int), cudaMemcpyDeviceToHost, stream));
+}
+static void engine_check_flag(EngineImpl &e) {
+    if (e.flag_host[0] != 0 || e.plan.options.timeline) check_error_flag(e.plan, e.base);
 }
 
 int ios_engine_run(ios_engine *engine, const float *input, float *output) {
     return guarded([&]() {
         if (!engine || !input || !output) throw ArgumentError("engine, input and output must not be NULL");
         EngineImpl &e = engine->impl;
-        std::lock_guard<std::mutex> lock(g_mutex);
-        g_device = e.device;
-        DeviceContext &ctx = context();
-        cudaStream_t spine = ctx.streams[0];
-        CUDA_OK(cudaMemcpyAsync(e.base + e.plan.staging_in_offset, input, e.in_bytes, cudaMemcpyHostToDevice, spine));
-        engine_forward(ctx, e, true);
-        CUDA_OK(cudaMemcpyAsync(output, e.base + e.plan.staging_out_offset, e.out_bytes, cudaMemcpyDeviceToHost, spine));
+        std::lock_guard<std::mutex> lock(e.mutex);
+        CUDA_OK(cudaSetDevice(e.device));
+        cudaStream_t spine = e.set.streams[0];
+        CUDA_OK(cudaMemcpyAsync(e.base + e.stage_in_off[0], input, e.in_bytes, cudaMemcpyHostToDevice, spine));
+        engine_forward(e, true);
+        CUDA_OK(cudaMemcpyAsync(output, e.base + e.stage_out_off[0], e.out_bytes, cudaMemcpyDeviceToHost, spine));
+        engine_fetch_flag(e, spine);
         CUDA_OK(cudaStreamSynchronize(spine));
-        check_error_flag(e.plan, e.base);
+        engine_check_flag(e);
+    });
+}
+
+int ios_engine_run_pipelined(ios_engine *engine, int count, const float *const *inputs, float *const *outputs) {
+    return guarded([&]() {
+        if (!engine || count < 0 || (count > 0 && (!inputs || !outputs)))
+            throw ArgumentError("engine, inputs and outputs must not be NULL and count >= 0");
+        for (int i = 0; i < count; ++i)
+            if (!inputs[i] || !outputs[i]) throw ArgumentError("every input and output pointer must not be NULL");
+        if (count == 0) return;
+        EngineImpl &e = engine->impl;
+        std::lock_guard<std::mutex> lock(e.mutex);
+        CUDA_OK(cudaSetDevice(e.device));
+        cudaStream_t spine = e.set.streams[0];
+        const TensorRef &in_t = e.plan.tensors[e.plan.model.placeholders[0]];
+        const TensorRef &out_t = e.plan.tensors[e.plan.model.output];
+        // Batch i uses staging pair i % 2.  Three streams: uploads, the forward (layout kernels and the
+        // captured schedule), downloads.  An upload may overwrite its staging buffer once the layout kernel
+        // of batch i - 2 has read it; a layout kernel may overwrite the output staging once the download
+        // of batch i - 2 has read it.  So the upload of batch i + 1 and the download of batch i - 1 run
+        // beside the forward of batch i.
+        CUDA_OK(cudaEventRecord(e.in_free[0], spine));      // everything issued earlier on the spine is ordered before
+        CUDA_OK(cudaStreamWaitEvent(e.copy_in, e.in_free[0], 0));
+        for (int i = 0; i < count; ++i) {
+            const int b = i & 1;
+            float *stage_in = reinterpret_cast<float *>(e.base + e.stage_in_off[b]);
+            float *stage_out = reinterpret_cast<float *>(e.base + e.stage_out_off[b]);
+            if (i >= 2) CUDA_OK(cudaStreamWaitEvent(e.copy_in, e.in_free[b], 0));
+            CUDA_OK(cudaMemcpyAsync(stage_in, inputs[i], e.in_bytes, cudaMemcpyHostToDevice, e.copy_in));
+            CUDA_OK(cudaEventRecord(e.in_ready[b], e.copy_in));
+            CUDA_OK(cudaStreamWaitEvent(spine, e.in_ready[b], 0));
+            launch_nchw_to_nhwc(stage_in, in_t, e.plan.input_round_tf32, spine);
+            CUDA_OK(cudaEventRecord(e.in_free[b], spine));
+            if (e.plan.options.use_graph) CUDA_OK(cudaGraphLaunch(e.exec_core.exec, spine));
+            else issue_forward(e.set, e.plan, nullptr);
+            if (i >= 2) CUDA_OK(cudaStreamWaitEvent(spine, e.out_free[b], 0));
+            launch_nhwc_to_nchw(out_t, stage_out, spine);
+            CUDA_OK(cudaEventRecord(e.out_ready[b], spine));
+            CUDA_OK(cudaStreamWaitEvent(e.copy_out, e.out_ready[b], 0));
+            CUDA_OK(cudaMemcpyAsync(outputs[i], stage_out, e.out_bytes, cudaMemcpyDeviceToHost, e.copy_out));
+            CUDA_OK(cudaEventRecord(e.out_free[b], e.copy_out));
+        }
+        engine_fetch_flag(e, e.copy_out);
+        CUDA_OK(cudaStreamSynchronize(e.copy_out));
+        CUDA_OK(cudaStreamSynchronize(spine));
+        engine_check_flag(e);
     });
 }
 
@@ -772,11 +953,10 @@ int ios_engine_set_input(ios_engine *engine, const float *input) {
     return guarded([&]() {
         if (!engine || !input) throw ArgumentError("engine and input must not be NULL");
         EngineImpl &e = engine->impl;
-        std::lock_guard<std::mutex> lock(g_mutex);
-        g_device = e.device;
-        DeviceContext &ctx = context();
-        cudaStream_t spine = ctx.streams[0];
-        float *stage_in = reinterpret_cast<float *>(e.base + e.plan.staging_in_offset);
+        std::lock_guard<std::mutex> lock(e.mutex);
+        CUDA_OK(cudaSetDevice(e.device));
+        cudaStream_t spine = e.set.streams[0];
+        float *stage_in = reinterpret_cast<float *>(e.base + e.stage_in_off[0]);
         CUDA_OK(cudaMemcpyAsync(stage_in, input, e.in_bytes, cudaMemcpyHostToDevice, spine));
         launch_nchw_to_nhwc(stage_in, e.plan.tensors[e.plan.model.placeholders[0]], e.plan.input_round_tf32, spine);
         CUDA_OK(cudaStreamSynchronize(spine));
@@ -787,15 +967,15 @@ int ios_engine_get_output(ios_engine *engine, float *output) {
     return guarded([&]() {
         if (!engine || !output) throw ArgumentError("engine and output must not be NULL");
         EngineImpl &e = engine->impl;
-        std::lock_guard<std::mutex> lock(g_mutex);
-        g_device = e.device;
-        DeviceContext &ctx = context();
-        cudaStream_t spine = ctx.streams[0];
-        float *stage_out = reinterpret_cast<float *>(e.base + e.plan.staging_out_offset);
+        std::lock_guard<std::mutex> lock(e.mutex);
+        CUDA_OK(cudaSetDevice(e.device));
+        cudaStream_t spine = e.set.streams[0];
+        float *stage_out = reinterpret_cast<float *>(e.base + e.stage_out_off[0]);
         launch_nhwc_to_nchw(e.plan.tensors[e.plan.model.output], stage_out, spine);
         CUDA_OK(cudaMemcpyAsync(output, stage_out, e.out_bytes, cudaMemcpyDeviceToHost, spine));
+        engine_fetch_flag(e, spine);
         CUDA_OK(cudaStreamSynchronize(spine));
-        check_error_flag(e.plan, e.base);
+        engine_check_flag(e);
     });
 }
 
@@ -803,19 +983,19 @@ int ios_engine_time(ios_engine *engine, int iters, float *ms_per_iter) {
     return guarded([&]() {
         if (!engine || !ms_per_iter || iters <= 0) throw ArgumentError("engine, ms_per_iter must not be NULL and iters > 0");
         EngineImpl &e = engine->impl;
-        std::lock_guard<std::mutex> lock(g_mutex);
-        g_device = e.device;
-        DeviceContext &ctx = context();
-        cudaStream_t spine = ctx.streams[0];
+        std::lock_guard<std::mutex> lock(e.mutex);
+        CUDA_OK(cudaSetDevice(e.device));
+        cudaStream_t spine = e.set.streams[0];
         CUDA_OK(cudaStreamSynchronize(spine));
-        CUDA_OK(cudaEventRecord(ctx.t_start, spine));
-        for (int i = 0; i < iters; ++i) engine_forward(ctx, e, false);
-        CUDA_OK(cudaEventRecord(ctx.t_end, spine));
+        CUDA_OK(cudaEventRecord(e.set.t_start, spine));
+        for (int i = 0; i < iters; ++i) engine_forward(e, false);
+        CUDA_OK(cudaEventRecord(e.set.t_end, spine));
+        engine_fetch_flag(e, spine);
         CUDA_OK(cudaStreamSynchronize(spine));
         float ms = 0.f;
-        CUDA_OK(cudaEventElapsedTime(&ms, ctx.t_start, ctx.t_end));
+        CUDA_OK(cudaEventElapsedTime(&ms, e.set.t_start, e.set.t_end));
         *ms_per_iter = ms / float(iters);
-        check_error_flag(e.plan, e.base);
+        engine_check_flag(e);
     });
 }
 
@@ -825,9 +1005,9 @@ int ios_engine_profile(ios_engine *engine, int iters, int capacity, int *count, 
         if (!engine || !count || !step_ms || !step_kind || !step_work || iters <= 0)
             throw ArgumentError("engine and the output arrays must not be NULL and iters > 0");
         EngineImpl &e = engine->impl;
-        std::lock_guard<std::mutex> lock(g_mutex);
-        g_device = e.device;
-        DeviceContext &ctx = context();
+        std::lock_guard<std::mutex> lock(e.mutex);
+        CUDA_OK(cudaSetDevice(e.device));
+        StreamSet &ctx = e.set;
         cudaStream_t spine = ctx.streams[0];
         const int n = int(e.plan.steps.size());
         *count = n;
@@ -890,11 +1070,21 @@ int ios_engine_describe(ios_engine *engine, char *text, int capacity) {
         if (!engine || !text || capacity <= 0) throw ArgumentError("engine and text must not be NULL");
         const EngineImpl &e = engine->impl;
         const Plan &p = e.plan;
-        int n_tc = 0, n_direct = 0, n_dw = 0, n_sum = 0, n_pool = 0, n_split = 0;
+        int n_tc = 0, n_direct = 0, n_dw = 0, n_sum = 0, n_pool = 0, n_split = 0, n_persistent = 0, n_half = 0, n_few = 0,
+            n_direct_store = 0;
         for (const Step &s : p.steps) {
             switch (s.kind) {
-                case StepKind::ConvTc: ++n_tc; if (s.tcplan.split_k > 1) ++n_split; break;
-                case StepKind::ConvDirect: ++n_direct; break;
+                case StepKind::ConvTc:
+                    ++n_tc;
+                    if (s.tcplan.split_k > 1) ++n_split;
+                    if (s.tcplan.persistent) ++n_persistent;
+                    if (s.tcplan.half_rows) ++n_half;
+                    if (!s.tcplan.tma_store) ++n_direct_store;
+                    break;
+                case StepKind::ConvDirect:
+                    ++n_direct;
+                    if (conv_few_channels_supported(s.direct.in, s.direct.out, s.direct.g)) ++n_few;
+                    break;
                 case StepKind::ConvDepthwise: ++n_dw; break;
                 case StepKind::SumAct: ++n_sum; break;
                 case StepKind::Pool: ++n_pool; break;
@@ -904,13 +1094,17 @@ int ios_engine_describe(ios_engine *engine, char *text, int capacity) {
         for (const ConvSlot &c : p.convs) weight_bytes += c.weight_bytes + c.geom.Cout * sizeof(float);
         const Op &out = p.model.ops[p.model.output];
         std::snprintf(text, size_t(capacity),
-                      "{\"launches\": %d, \"conv_tc\": %d, \"conv_tc_split_k\": %d, \"conv_direct\": %d, \"conv_depthwise\": %d, "
+                      "{\"launches\": %d, \"conv_tc\": %d, \"conv_tc_split_k\": %d, \"conv_tc_persistent\": %d, "
+                      "\"conv_tc_half_rows\": %d, \"conv_tc_direct_store\": %d, \"conv_direct\": %d, \"conv_few_channels\": %d, "
+                      "\"conv_depthwise\": %d, "
                       "\"sum_act\": %d, \"pool\": %d, \"stages\": %zu, \"arena_bytes\": %zu, \"workspace_bytes\": %zu, "
                       "\"weight_bytes\": %zu, \"conv_flops\": %.0f, \"output_shape\": [%d, %d, %d, %d], \"executor\": \"%s\", "
-                      "\"precision\": \"%s\"}",
-                      p.launches_per_forward, n_tc, n_split, n_direct, n_dw, n_sum, n_pool, p.model.stages.size(), e.bytes,
+                      "\"stage_barriers\": %d, \"pdl_edges\": %d, \"device\": %d, \"precision\": \"%s\"}",
+                      p.launches_per_forward, n_tc, n_split, n_persistent, n_half, n_direct_store, n_direct, n_few, n_dw, n_sum,
+                      n_pool, p.model.stages.size(), e.bytes,
                       p.workspace_bytes, weight_bytes, p.model.conv_flops(), p.model.batch, out.C, out.H, out.W,
-                      p.options.use_graph ? "graph" : "streams",
+                      p.options.use_graph ? "graph" : "streams", p.options.stage_barriers ? 1 : 0, p.options.pdl_edges ? 1 : 0,
+                      e.device,
                       p.options.bf16 ? "bf16" : !p.options.tf32 ? "fp32" : p.options.three_pass ? "tf32x3" : "tf32");
     });
 }

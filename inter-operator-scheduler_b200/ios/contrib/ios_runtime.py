@@ -59,6 +59,7 @@ def load_ios_library():
                                              ctypes.POINTER(ctypes.c_void_p)]
         handle.ios_engine_destroy.argtypes = [ctypes.c_void_p]
         handle.ios_engine_run.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+        handle.ios_engine_run_pipelined.argtypes = [ctypes.c_void_p, _INT, _VOIDPP, _VOIDPP]
         handle.ios_engine_time.argtypes = [ctypes.c_void_p, _INT, _FLOATP]
         handle.ios_engine_describe.argtypes = [ctypes.c_void_p, ctypes.c_char_p, _INT]
         handle.ios_engine_profile.argtypes = [ctypes.c_void_p, _INT, _INT, ctypes.POINTER(_INT), _FLOATP,
@@ -69,6 +70,8 @@ def load_ios_library():
         handle.ios_get_option.argtypes = [_CHARP, ctypes.c_char_p, _INT]
         handle.ios_set_device.argtypes = [_INT]
         handle.ios_device_count.argtypes = [ctypes.POINTER(_INT)]
+        handle.ios_host_register.argtypes = [ctypes.c_void_p, ctypes.c_size_t]
+        handle.ios_host_unregister.argtypes = [ctypes.c_void_p]
         handle.ios_conv2d.argtypes = [ctypes.c_void_p] * 4 + [_INT] * 14
         return handle
     raise FileNotFoundError('IOS Backend library not found (build it with inter-operator-scheduler_b200/build.py)')
@@ -106,6 +109,15 @@ def device_count() -> int:
     n = ctypes.c_int(0)
     _check(_library().ios_device_count(ctypes.byref(n)))
     return n.value
+
+
+def host_register(array: np.ndarray) -> bool:
+    """Page-lock the memory of ``array`` so that copies from / to it overlap with compute.  False if refused."""
+    return _library().ios_host_register(ctypes.c_void_p(array.ctypes.data), array.nbytes) == 0
+
+
+def host_unregister(array: np.ndarray) -> bool:
+    return _library().ios_host_unregister(ctypes.c_void_p(array.ctypes.data)) == 0
 
 
 def _timed(entry, head_args, batch_size, warmup, number, repeat, profile_stage, num_stage_slots):
@@ -246,6 +258,31 @@ class Engine:
         out_ptr = result.ctypes.data_as(ctypes.c_void_p) if isinstance(result, np.ndarray) else ctypes.c_void_p(int(result))
         _check(self._lib.ios_engine_run(self._handle, in_ptr, out_ptr))
         return result
+
+    def run_pipelined(self, inputs, outputs=None):
+        """
+        Several batches in a row with the host copies overlapped with compute (upload of batch i + 1 and
+        download of batch i - 1 beside the forward of batch i).  ``inputs`` / ``outputs``: sequences of
+        float32 NCHW numpy arrays or raw host addresses; page-locked buffers are needed for the overlap.
+        """
+        count = len(inputs)
+        keep = []
+
+        def address(item, shape):
+            if isinstance(item, np.ndarray):
+                if item.dtype != np.float32 or not item.flags['C_CONTIGUOUS'] or tuple(item.shape) != tuple(shape):
+                    raise ValueError(f'expected a C-contiguous float32 array of shape {tuple(shape)}')
+                keep.append(item)
+                return item.ctypes.data
+            return int(item)
+
+        results = outputs
+        if outputs is None:
+            results = [np.empty(self.output_shape, dtype=np.float32) for _ in range(count)]
+        in_ptrs = (ctypes.c_void_p * count)(*[address(x, self.input_shape) for x in inputs])
+        out_ptrs = (ctypes.c_void_p * count)(*[address(y, self.output_shape) for y in results])
+        _check(self._lib.ios_engine_run_pipelined(self._handle, count, in_ptrs, out_ptrs))
+        return results
 
     def set_input(self, input: np.ndarray):
         data = np.ascontiguousarray(input, dtype=np.float32)

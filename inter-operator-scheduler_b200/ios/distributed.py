@@ -83,6 +83,40 @@ class RuntimeBackend:
     def engine_run(self, key, x):
         return self.engines[key].run(x)
 
+    def engine_attach(self, key, in_name, out_name, in_shape, out_shape, begin, end):
+        """
+        Map the parent's shared input / output arrays, page-lock this shard's part of them, and remember
+        the addresses: ``engine_run_shared`` then moves no data between processes at all.
+        """
+        from multiprocessing import shared_memory
+        shm_in = shared_memory.SharedMemory(name=in_name)
+        shm_out = shared_memory.SharedMemory(name=out_name)
+        x = np.ndarray(in_shape, dtype=np.float32, buffer=shm_in.buf)[begin:end]
+        y = np.ndarray(out_shape, dtype=np.float32, buffer=shm_out.buf)[begin:end]
+        pinned = [self.rt.host_register(x), self.rt.host_register(y)]
+        self.shared = getattr(self, 'shared', {})
+        self.shared[key] = (shm_in, shm_out, x, y, pinned)
+        return all(pinned)
+
+    def engine_run_shared(self, key, repeats=1):
+        _, _, x, y, _ = self.shared[key]
+        engine = self.engines[key]
+        if repeats == 1:
+            engine.run(x.ctypes.data, y.ctypes.data)
+        else:
+            engine.run_pipelined([x.ctypes.data] * repeats, [y.ctypes.data] * repeats)
+        return True
+
+    def engine_detach(self, key):
+        shm_in, shm_out, x, y, pinned = self.shared.pop(key)
+        for array, ok in zip((x, y), pinned):
+            if ok:
+                self.rt.host_unregister(array)
+        del x, y
+        shm_in.close()
+        shm_out.close()
+        return True
+
     def engine_time(self, key, iters):
         return self.engines[key].time(iters)
 
@@ -130,6 +164,7 @@ class GpuWorkerPool:
         self.max_attempts = max_attempts
         self.workers = {}
         self.lost = []
+        self._next_id = 0
         for device in devices:
             parent, child = self.ctx.Pipe()
             proc = self.ctx.Process(target=_worker_main, args=(child, device, backend_factory), daemon=True)
@@ -165,20 +200,45 @@ class GpuWorkerPool:
                 proc.terminate()
             proc.join(timeout=5)
 
-    def call(self, device, method, *args, timeout=None):
-        """Run one task on a specific worker (used for per-device state such as engines)."""
+    def new_task_id(self):
+        """Every request carries an id of its own; a reply with another id is a leftover and is discarded."""
+        self._next_id += 1
+        return self._next_id
+
+    def send(self, device, method, args):
+        """Post one request to a worker; returns its task id (collect the reply with ``receive``)."""
+        if device not in self.workers:
+            raise WorkerLost(f'worker {device} is gone')
+        task_id = self.new_task_id()
+        try:
+            self.workers[device][1].send((task_id, method, args))
+        except (BrokenPipeError, OSError):
+            self._drop(device, f'{method}: worker exited')
+            raise WorkerLost(f'worker {device} exited before {method}')
+        return task_id
+
+    def receive(self, device, task_id, method='task', timeout=None):
+        """The reply to ``task_id``: ``(status, value)``.  A worker that stays silent or exits is dropped."""
         if device not in self.workers:
             raise WorkerLost(f'worker {device} is gone')
         _, conn = self.workers[device]
-        conn.send((0, method, args))
-        if not conn.poll(self.task_timeout if timeout is None else timeout):
-            self._drop(device, f'{method} timed out')
-            raise WorkerLost(f'worker {device} timed out in {method}')
-        try:
-            _, status, value = conn.recv()
-        except EOFError:
-            self._drop(device, f'{method}: worker exited')
-            raise WorkerLost(f'worker {device} exited in {method}')
+        deadline = time.time() + (self.task_timeout if timeout is None else timeout)
+        while True:
+            if not conn.poll(max(0.0, deadline - time.time())):
+                self._drop(device, f'{method} timed out')
+                raise WorkerLost(f'worker {device} timed out in {method}')
+            try:
+                reply_id, status, value = conn.recv()
+            except (EOFError, OSError):
+                self._drop(device, f'{method}: worker exited')
+                raise WorkerLost(f'worker {device} exited in {method}')
+            if reply_id == task_id:
+                return status, value
+
+    def call(self, device, method, *args, timeout=None):
+        """Run one task on a specific worker (used for per-device state such as engines)."""
+        task_id = self.send(device, method, args)
+        status, value = self.receive(device, task_id, method, timeout)
         if status != 'ok':
             raise RuntimeError(f'worker {device}: {value}')
         return value
@@ -191,7 +251,8 @@ class GpuWorkerPool:
         results: List = [None] * len(arg_list)
         attempts = [0] * len(arg_list)
         queue = list(range(len(arg_list)))[::-1]
-        busy: Dict[int, Tuple[int, float]] = {}          # device -> (task index, start time)
+        busy: Dict[int, Tuple[int, float, int]] = {}     # device -> (task index, start time, task id)
+        self.last_devices = [None] * len(arg_list)       # which device produced each result
         done = 0
         while done < len(arg_list):
             if not self.workers:
@@ -200,32 +261,53 @@ class GpuWorkerPool:
                 if device not in busy and queue:
                     index = queue.pop()
                     attempts[index] += 1
-                    self.workers[device][1].send((index, method, arg_list[index]))
-                    busy[device] = (index, time.time())
+                    task_id = self.new_task_id()
+                    try:
+                        self.workers[device][1].send((task_id, method, arg_list[index]))
+                    except (BrokenPipeError, OSError):
+                        self._drop(device, f'exited before task {index}')
+                        self._requeue(index, attempts, queue)
+                        continue
+                    busy[device] = (index, time.time(), task_id)
             conns = {self.workers[d][1]: d for d in busy}
             ready = mp.connection.wait(list(conns), timeout=1.0)
             for conn in ready:
                 device = conns[conn]
-                index, _ = busy.pop(device)
+                index, _, task_id = busy[device]
                 try:
-                    task_id, status, value = conn.recv()
-                except EOFError:
+                    reply_id, status, value = conn.recv()
+                except (EOFError, OSError):
+                    busy.pop(device)
                     self._drop(device, f'exited while running task {index}')
                     self._requeue(index, attempts, queue)
                     continue
+                if reply_id != task_id:
+                    continue                                 # a leftover of an earlier, abandoned request
+                busy.pop(device)
                 if status != 'ok':
+                    self._drain(busy)
                     raise RuntimeError(f'task {index} failed on worker {device}: {value}')
-                results[task_id] = value
+                results[index] = value
+                self.last_devices[index] = device
                 done += 1
                 if on_result:
-                    on_result(task_id, value)
+                    on_result(index, value)
             now = time.time()
-            for device, (index, started) in list(busy.items()):
+            for device, (index, started, _) in list(busy.items()):
                 if now - started > self.task_timeout:
                     busy.pop(device)
                     self._drop(device, f'task {index} timed out')
                     self._requeue(index, attempts, queue)
         return results
+
+    def _drain(self, busy):
+        """Before an error leaves ``map``: collect (or give up on) every reply that is still outstanding."""
+        for device, (index, _, task_id) in list(busy.items()):
+            try:
+                self.receive(device, task_id, f'task {index}')
+            except WorkerLost:
+                pass
+        busy.clear()
 
     def _requeue(self, index, attempts, queue):
         if attempts[index] >= self.max_attempts:
@@ -273,9 +355,10 @@ class FarmCostModel:
     Cost model for ``ios.optimize`` backed by a worker pool.  ``optimize`` calls
     ``prefetch_stages`` once; it replays the search's enumeration with a recording cost model (the
     set of candidate stages does not depend on the latencies), measures all candidates in parallel,
-    and the real search then reads the memo.  ``top_k_device`` re-measures nothing by default: all
-    GPUs of one box are the same part at the same clocks; pass ``calibrate=True`` to scale every
-    worker's numbers by a common calibration stage measured on all of them.
+    and the real search then reads the memo.  All GPUs of one box are the same part at the same
+    clocks; ``calibrate=True`` still measures one common stage on every worker first and multiplies
+    each worker's later numbers by (median over workers) / (its own time for that stage); the
+    factors are kept in ``self.scale``.
     """
 
     def __init__(self, pool: GpuWorkerPool, memo_path: Optional[str] = None, calibrate: bool = False):
@@ -313,15 +396,17 @@ class FarmCostModel:
             return
         scale = {}
         if self.calibrate and todo:
+            # one common stage on every worker: a worker's numbers are multiplied by median / its own
             probe = todo[0]
             times = self.pool.broadcast('stage_latency', *probe)
             ref = float(np.median([np.mean(t) for t in times.values()]))
             scale = {d: ref / float(np.mean(t)) for d, t in times.items()}
         values = self.pool.map('stage_latency', todo)
-        for args, value in zip(todo, values):
-            self.memo[self._key(*args)] = value
+        for args, value, device in zip(todo, values, self.pool.last_devices):
+            factor = scale.get(device, 1.0)
+            self.memo[self._key(*args)] = [float(v) * factor for v in value]
         self.measured += len(todo)
-        self._scale = scale
+        self.scale = scale
         if self.memo_path:
             self.save(self.memo_path)
 
@@ -350,37 +435,86 @@ class ShardedInference:
     Run a graph on a batch split across the pool's GPUs.  ``graph_for_batch(b)`` returns the graph
     (with weights and a schedule) to use for a shard of ``b`` images -- IOS schedules are
     specialised to the batch size -- and defaults to the given graph for every size.
+
+    Input and output live in two shared-memory arrays (``self.input``, ``self.output``) that every
+    worker maps and page-locks for its own slice, so a run moves no tensor between processes: the
+    parent writes the batch into ``self.input`` (or passes it to ``run``, which copies it there),
+    each worker uploads its slice straight from the shared pages and downloads into them.
     """
 
     def __init__(self, pool: GpuWorkerPool, graph, batch: int, graph_for_batch: Optional[Callable] = None):
+        from multiprocessing import shared_memory
         self.pool = pool
         self.batch = batch
         self.slices = plan_shards(batch, len(pool.devices))
         self.devices = pool.devices[:len(self.slices)]
         self.output_shape = None
+        self.key = f'shard-{id(self)}'
+        in_shape = (batch, *graph.input.output_shape)
         for device, (begin, end) in zip(self.devices, self.slices):
             shard_graph = graph_for_batch(end - begin) if graph_for_batch else graph
             weights = {conv.name: (conv.weight, conv.bias) for conv in shard_graph.convs()}
-            shape = pool.call(device, 'engine_create', 'shard', json.dumps(shard_graph.export_config()), end - begin,
+            shape = pool.call(device, 'engine_create', self.key, json.dumps(shard_graph.export_config()), end - begin,
                               weights, timeout=600)
             self.output_shape = (batch, *shape[1:])
+        self._shm_in = shared_memory.SharedMemory(create=True, size=max(4, int(np.prod(in_shape)) * 4))
+        self._shm_out = shared_memory.SharedMemory(create=True, size=max(4, int(np.prod(self.output_shape)) * 4))
+        self.input = np.ndarray(in_shape, dtype=np.float32, buffer=self._shm_in.buf)
+        self.output = np.ndarray(self.output_shape, dtype=np.float32, buffer=self._shm_out.buf)
+        self.pinned = True
+        for device, (begin, end) in zip(self.devices, self.slices):
+            ok = pool.call(device, 'engine_attach', self.key, self._shm_in.name, self._shm_out.name, in_shape,
+                           self.output_shape, begin, end)
+            self.pinned = self.pinned and bool(ok)
 
-    def run(self, x: np.ndarray) -> np.ndarray:
-        if x.shape[0] != self.batch:
-            raise ValueError(f'expected a batch of {self.batch}, got {x.shape[0]}')
-        out = np.empty(self.output_shape, dtype=np.float32)
-        # issue every shard before collecting any result: the workers run concurrently
-        for device, (begin, end) in zip(self.devices, self.slices):
-            self.pool.workers[device][1].send((0, 'engine_run', ('shard', np.ascontiguousarray(x[begin:end]))))
-        for device, (begin, end) in zip(self.devices, self.slices):
-            conn = self.pool.workers[device][1]
-            if not conn.poll(self.pool.task_timeout):
-                raise WorkerLost(f'worker {device} timed out')
-            _, status, value = conn.recv()
-            if status != 'ok':
-                raise RuntimeError(f'worker {device}: {value}')
-            out[begin:end] = value
-        return out
+    def run(self, x: Optional[np.ndarray] = None, repeats: int = 1) -> np.ndarray:
+        """
+        One pass over the batch (``repeats`` > 1: the same batch that many times through the pipelined
+        entry point, for timing).  ``x`` = None runs on what is already in ``self.input``.  Every shard is
+        issued before any reply is collected; all replies are collected (or their workers dropped) before
+        an error is raised, so a failed run never leaves a stale reply for the next one.
+        """
+        if x is not None:
+            if x.shape[0] != self.batch:
+                raise ValueError(f'expected a batch of {self.batch}, got {x.shape[0]}')
+            np.copyto(self.input, x, casting='same_kind')
+        pending, failure = [], None
+        for device in self.devices:
+            try:
+                pending.append((device, self.pool.send(device, 'engine_run_shared', (self.key, repeats))))
+            except WorkerLost as err:
+                failure = failure or err
+        for device, task_id in pending:
+            try:
+                status, value = self.pool.receive(device, task_id, 'engine_run_shared')
+                if status != 'ok':
+                    failure = failure or RuntimeError(f'worker {device}: {value}')
+            except WorkerLost as err:
+                failure = failure or err
+        if failure is not None:
+            raise failure
+        return self.output.copy()
+
+    def close(self):
+        for device in self.devices:
+            if device in self.pool.workers:
+                try:
+                    self.pool.call(device, 'engine_detach', self.key)
+                except (WorkerLost, RuntimeError):
+                    pass
+        self.input = self.output = None
+        for shm in (self._shm_in, self._shm_out):
+            try:
+                shm.close()
+                shm.unlink()
+            except (FileNotFoundError, BufferError):
+                pass
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
 
 
 def gather_to_rank0(local: np.ndarray, batch: int, group=None) -> Optional[np.ndarray]:

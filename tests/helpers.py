@@ -90,3 +90,9 @@ def has_gpu():
         return ios.ios_runtime.device_count() > 0
     except Exception:
         return False
+
+
+def oracle_in_chunks(config, weights, x, chunk=16):
+    """The oracle over a large batch, a few images at a time (every operator is per image): bounded host memory."""
+    parts = [oracle.run_config(config, weights, x[i:i + chunk]) for i in range(0, x.shape[0], chunk)]
+    return np.concatenate(parts, axis=0)

@@ -113,3 +113,54 @@ def test_gloo_world_size_2_gather(tmp_path):
     tmp.spawn(_gloo_rank, args=(2, _free_port(), batch, str(tmp_path)), nprocs=2, join=True)
     got = np.load(str(tmp_path / 'gathered.npy'))
     assert np.array_equal(got, np.arange(batch * 3, dtype=np.float32).reshape(batch, 3) * 2.0)
+
+
+def _sharded_case(batch=18):
+    graph = sample_block()
+    graph.sequential_schedule()
+    x = np.random.default_rng(0).standard_normal((batch, 375, 15, 15)).astype(np.float32)
+    return graph, x, x.sum(axis=(2, 3), keepdims=True)
+
+
+def test_sharded_inference_through_shared_memory():
+    from fake_backends import FakeEngineBackend
+    graph, x, expect = _sharded_case()
+    with D.GpuWorkerPool([0, 1, 2], FakeEngineBackend) as pool:
+        with D.ShardedInference(pool, graph, x.shape[0]) as sharded:
+            assert [e - b for b, e in sharded.slices] == [6, 6, 6] and not sharded.pinned
+            assert np.allclose(sharded.run(x), expect, rtol=1e-5)
+            sharded.input[...] = 2.0 * x                      # written in place: no copy through run()
+            assert np.allclose(sharded.run(), 2.0 * expect, rtol=1e-5)
+            with pytest.raises(ValueError):
+                sharded.run(x[:5])
+
+
+def test_a_failed_shard_does_not_poison_the_next_run():
+    """Shard 0 raises once: the error surfaces, every other reply is collected, and the next run is right."""
+    from fake_backends import FakeEngineFailsOnceOnDeviceZero
+    graph, x, expect = _sharded_case()
+    with D.GpuWorkerPool([0, 1], FakeEngineFailsOnceOnDeviceZero) as pool:
+        with D.ShardedInference(pool, graph, x.shape[0]) as sharded:
+            with pytest.raises(RuntimeError, match='injected'):
+                sharded.run(x)
+            assert np.allclose(sharded.run(3.0 * x), 3.0 * expect, rtol=1e-4, atol=1e-3)
+            assert pool.call(1, 'echo', 'still in step') == (1, 'still in step')
+
+
+def test_stale_replies_are_discarded_by_task_id():
+    with D.GpuWorkerPool([0], FakeBackend) as pool:
+        abandoned = pool.send(0, 'echo', ('old',))            # a request whose reply nobody collects
+        assert pool.call(0, 'echo', 'new') == (0, 'new')       # the leftover reply is skipped, not returned
+        assert abandoned != pool.new_task_id()
+
+
+def test_farm_calibration_is_applied_to_the_measurements():
+    from fake_backends import SlowOnDeviceOne
+    graph = sample_block()
+    with D.GpuWorkerPool([0, 1, 2], SlowOnDeviceOne) as pool:
+        farm = D.FarmCostModel(pool, calibrate=True)
+        ios.optimize(graph, batch_size=1, cost_model=farm, opt_type='dp_parallel_merge')
+        assert abs(farm.scale[1] - 0.5) < 1e-9 and abs(farm.scale[0] - 1.0) < 1e-9
+        for key, value in farm.memo.items():
+            stage_json, input_json, batch = json.loads(key)[:3]
+            assert abs(value[0] - fake_latency(stage_json, input_json, batch)) < 1e-9

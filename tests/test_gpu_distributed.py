@@ -26,13 +26,17 @@ def test_sharded_inference_matches_oracle():
     config, weights = seeded(graph, 0)
     batch = 18
     x = oracle.normal_input(config, batch, 3)
-    with D.GpuWorkerPool(_devices()) as pool:
-        sharded = D.ShardedInference(pool, graph, batch)
-        assert sum(e - b for b, e in sharded.slices) == batch and len(sharded.slices) == len(pool.devices)
-        y = sharded.run(x)
     ref = oracle.run_config(config, weights, x)
-    assert y.shape == ref.shape
-    assert oracle.max_rel_err(y, ref) <= TOL_TF32
+    with D.GpuWorkerPool(_devices()) as pool:
+        with D.ShardedInference(pool, graph, batch) as sharded:
+            assert sum(e - b for b, e in sharded.slices) == batch and len(sharded.slices) == len(pool.devices)
+            assert sharded.pinned                   # every worker page-locked its slice of the shared arrays
+            y = sharded.run(x)
+            assert y.shape == ref.shape
+            assert oracle.max_rel_err(y, ref) <= TOL_TF32
+            sharded.input[...] = x[::-1]            # written in place; three pipelined passes over the same batch
+            y = sharded.run(repeats=3)
+            assert oracle.max_rel_err(y, ref[::-1]) <= TOL_TF32
 
 
 def test_stage_farm_drives_the_search():
