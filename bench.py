@@ -78,6 +78,9 @@ class ClockSampler:
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._drain, daemon=True)
             self.thread.start()
+            deadline = time.time() + 5.0          # the timed region starts once the sampler is really running
+            while not self.lines and time.time() < deadline:
+                time.sleep(0.01)
         except OSError:
             self.proc = None
         return self
@@ -115,6 +118,16 @@ class ClockSampler:
         return {'sm_mhz': statistics.median(sm), 'sm_max_mhz': max(mx), 'reasons': sorted(reasons), 'samples': len(sm)}
 
 
+def kernel_sources_sha16():
+    """Identifies the build: a hash over the CUDA sources of the convolution kernels."""
+    import hashlib
+    digest = hashlib.sha256()
+    for name in ('conv_tc.cu', 'conv_direct.cu', 'kernels.h', 'plan.cu'):
+        with open(os.path.join(ROOT, 'inter-operator-scheduler_b200', 'csrc', name), 'rb') as fh:
+            digest.update(fh.read())
+    return digest.hexdigest()[:16]
+
+
 def build_graph(model):
     import ios
     if model == 'sample_block':
@@ -141,7 +154,7 @@ def seeded_weights(graph, seed=0):
     return weights
 
 
-def schedule_graph(graph, schedule, batch, cost_model=None):
+def schedule_graph(graph, schedule, batch, cost_model=None, warmup=2, number=6, repeat=3):
     """Returns the graph to execute and the seconds the schedule search took."""
     import ios
     t0 = time.time()
@@ -152,7 +165,7 @@ def schedule_graph(graph, schedule, batch, cost_model=None):
         graph.greedy_schedule()
         return graph, 0.0
     opt = ios.optimize(graph, batch_size=batch, cost_model=cost_model, opt_type='dp_parallel_merge',
-                       compute_weight=True, max_part_size=50, number=4, repeat=2)
+                       compute_weight=True, max_part_size=50, warmup=warmup, number=number, repeat=repeat)
     return opt, time.time() - t0
 
 
@@ -221,7 +234,15 @@ def run_ours(args):
     weights = seeded_weights(graph, 0)
     base_config = graph.export_config()
     exec_graph, search_s = schedule_graph(graph, args.schedule, args.batch)
-    log(f'[rank {ranks.rank}] schedule "{args.schedule}": {sum(len(b.stages) for b in exec_graph.blocks)} stages, '
+    schedule_note = args.schedule
+    if args.schedule == 'dp':
+        # the search adds up stage latencies measured one by one; the whole schedules are timed too and the
+        # heuristic one is kept if it is faster (both numbers are reported)
+        graph.greedy_schedule()          # (the search returned a new graph; the original is free to carry this one)
+        exec_graph, whole = rt.pick_faster([exec_graph, graph], args.batch, warmup=3, number=10, repeat=5)
+        schedule_note = (f'dp ({whole[0]:.4f} ms whole) vs greedy ({whole[1]:.4f} ms whole): '
+                         f'{"dp" if whole[0] <= whole[1] else "greedy"} kept')
+    log(f'[rank {ranks.rank}] schedule "{schedule_note}": {sum(len(b.stages) for b in exec_graph.blocks)} stages, '
         f'search took {search_s:.1f} s')
 
     engine = rt.Engine(exec_graph, args.batch)
@@ -242,11 +263,12 @@ def run_ours(args):
         engine.time(1)
     ranks.barrier()
     with ClockSampler(device) as sampler:
-        device_ms = 0.0
+        step_ms = []
         t_wall = time.perf_counter()
         for _ in range(args.steps):
             flush_l2()
-            device_ms += engine.time(1)
+            step_ms.append(engine.time(1))
+        device_ms = sum(step_ms)
         ranks.barrier()
         wall_s = time.perf_counter() - t_wall
         warm_ms = engine.time(max(10, args.steps))          # back-to-back replays, weights stay in L2
@@ -254,14 +276,27 @@ def run_ours(args):
         for _ in range(args.warmup):
             engine.run(host_in.data_ptr(), host_out.data_ptr())
         ranks.barrier()
-        e2e_s = 0.0
+        e2e_steps = []
         for _ in range(args.steps):
             flush_l2()
             t0 = time.perf_counter()
             engine.run(host_in.data_ptr(), host_out.data_ptr())
-            e2e_s += time.perf_counter() - t0
+            e2e_steps.append(time.perf_counter() - t0)
+        e2e_s = sum(e2e_steps)
         ranks.barrier()
+        # the same K steps through the pipelined host-buffer entry point: upload of step i + 1 and download
+        # of step i - 1 beside the forward of step i (throughput, not latency; reported beside e2e)
+        engine.run_pipelined([host_in.data_ptr()] * args.warmup, [host_out.data_ptr()] * args.warmup)
+        ranks.barrier()
+        t0 = time.perf_counter()
+        engine.run_pipelined([host_in.data_ptr()] * args.steps, [host_out.data_ptr()] * args.steps)
+        pipelined_s = time.perf_counter() - t0
+        ranks.barrier()
+        sharded = None
+        if args.sharded_sweep and args.model == 'inception_v3' and args.batch == 1:
+            sharded = sharded_sweep(graph, base_config, weights, ranks, peaks, peak_kind, args)
     clocks = sampler.summary()
+    pipelined_ms = ranks.max_over_ranks(1e3 * pipelined_s / args.steps)
     ms_per_step = ranks.max_over_ranks(device_ms / args.steps)
     e2e_ms = ranks.max_over_ranks(1e3 * e2e_s / args.steps)
     images = args.batch * ranks.world
@@ -302,15 +337,20 @@ def run_ours(args):
                               'GB/s': round(v['work'] / (v['ms'] * 1e-3) / 1e9, 1) if v['ms'] > 0 else None}
                           for k, v in by_kind.items() if k != 'conv_tc'},
     }
-    # DRAM bytes of the convolution launches of one forward, from the committed ncu summary
-    summary = os.path.join(ROOT, 'profiles', 'conv_tc_inception_v3_b1_sequential.md')
-    if args.model == 'inception_v3' and args.batch == 1 and os.path.exists(summary):
-        with open(summary) as fh:
-            for text in fh:
-                if text.startswith('dram_bytes_per_step:'):
-                    roofline['traffic'] = int(text.split(':')[1])
-                    roofline['traffic_source'] = 'ncu dram__bytes_read+write over the conv launches of one forward, ' \
-                                                 'sequential schedule (profiles/conv_tc_inception_v3_b1_sequential.md)'
+    # DRAM bytes of the convolution launches of one forward: an ncu capture cannot run inside the bench, so the
+    # figure is looked up in the table committed beside the profile summaries, by workload, and only used when
+    # the kernel sources are still the ones it was captured with
+    table = os.path.join(ROOT, 'profiles', 'conv_tc_traffic.json')
+    if os.path.exists(table):
+        with open(table) as fh:
+            entries = json.load(fh)
+        key = f'{args.model}/batch{args.batch}/{precision}'
+        entry = entries.get(key)
+        if entry:
+            roofline['traffic'] = entry['dram_bytes_per_forward'] if entry.get('sources_sha16') == kernel_sources_sha16() else None
+            roofline['traffic_source'] = (f"ncu dram__bytes_read+write over the convolution launches of one forward, "
+                                          f"{entry.get('schedule')} schedule, kernel sources {entry.get('sources_sha16')} "
+                                          f"(profiles/conv_tc_traffic.json; this build: {kernel_sources_sha16()})")
 
     line = {
         'metric': METRIC, 'value': round(value, 2), 'unit': 'images/s', 'n_gpus': ranks.world, 'steps': args.steps,
@@ -325,17 +365,30 @@ def run_ours(args):
                        'single GPU' if ranks.world == 1 else
                        (f'{ranks.world} independent replicas (batch 1 does not shard)' if args.batch == 1 else
                         f'global batch {images} sharded evenly, {args.batch} images per GPU, no collective on the data path'),
-                   'l2': 'flushed between steps by a 256 MiB write', 'schedule_search_s': round(search_s, 1)},
+                   'l2': 'flushed between steps by a 256 MiB write', 'schedule_search_s': round(search_s, 1),
+                   'schedule_choice': schedule_note},
         'e2e': {'value': round(e2e_value, 2), 'unit': 'images/s', 'ms_per_step': round(e2e_ms, 5),
                 'h2d_bytes_per_step': int(x.nbytes), 'd2h_bytes_per_step': int(y.nbytes)},
-        'gpu_launches': (info['launches'] + 2) * args.steps * 2 + info['launches'] * max(10, args.steps),
+        'gpu_launches': info['launches'] * args.steps + (info['launches'] + 2) * args.steps * 2 +
+                        info['launches'] * max(10, args.steps),
         'warm_l2_ms_per_step': round(warm_ms, 5),
+        'ms_per_step_spread': {'median': round(statistics.median(step_ms), 5), 'p10': round(float(np.percentile(step_ms, 10)), 5),
+                               'p90': round(float(np.percentile(step_ms, 90)), 5), 'note': 'rank 0, device time per step'},
+        'e2e_ms_per_step_spread': {'median': round(1e3 * statistics.median(e2e_steps), 5),
+                                   'p10': round(1e3 * float(np.percentile(e2e_steps, 10)), 5),
+                                   'p90': round(1e3 * float(np.percentile(e2e_steps, 90)), 5)},
+        'e2e_pipelined': {'value': round(images / (pipelined_ms * 1e-3), 2), 'unit': 'images/s',
+                          'ms_per_step': round(pipelined_ms, 5),
+                          'note': 'same host buffers and copies, K steps through ios_engine_run_pipelined '
+                                  '(copies overlap compute)'},
         'wall_s_timed_region': round(wall_s, 3),
         'clocks': clocks, 'roofline': roofline,
     }
 
+    if sharded is not None:
+        line['sharded_sweep'] = sharded
     if ranks.world == 1 and args.sweep and args.model == 'inception_v3' and args.batch == 1:
-        line['throughput_sweep'] = throughput_sweep(graph, peaks, peak_kind)
+        line['throughput_sweep'] = throughput_sweep(graph, base_config, weights, peaks, peak_kind)
 
     if ranks.rank == 0:
         ref = oracle.run_config(base_config, weights, x)
@@ -347,23 +400,49 @@ def run_ours(args):
     ranks.finish()
 
 
-def throughput_sweep(graph, peaks, peak_kind):
+def conv_flops_per_image(graph):
+    return 2.0 * sum(c.output_shape[0] * c.output_shape[1] * c.output_shape[2] * c.kernel[0] * c.kernel[1] *
+                     (c.input_shape[0] // c.groups) for c in graph.convs())
+
+
+def tensor_peak(peaks, precision):
+    return peaks['bf16_tflops'] if precision == 'bf16' else peaks['bf16_tflops'] / 2.0
+
+
+PARITY_BOUND = {'tf32x3': 1e-3, 'tf32': 6e-3, 'bf16': 2e-2}     # tf32: the known growth over 47 layers, see the tests
+
+
+def checked_images(engine_out, config, weights, x, count=2):
+    """Max relative error of the first ``count`` images of a batch against the CPU oracle (every image is independent)."""
+    import ios_oracle as oracle
+    ref = oracle.run_config(config, weights, x[:count])
+    return float(f'{oracle.max_rel_err(engine_out[:count], ref):.3e}')
+
+
+def throughput_sweep(graph, config, weights, peaks, peak_kind):
     """
-    Images/s of the same network at batch 16 / 64 / 256 on one GPU (greedy schedule, device-resident,
-    CUDA events over back-to-back replays; the activations alone exceed L2 from batch 16 on), for the
-    default precision and for bf16, each with its fraction of the measured tensor peak.
+    Images/s of the same network at batch 16 / 64 / 256 on one GPU (greedy schedule, seeded weights,
+    device-resident, CUDA events over back-to-back replays; the activations alone exceed L2 from batch
+    16 on) for three-pass TF32, single-pass TF32 and bfloat16, each with its fraction of the measured
+    tensor peak.  The batch-16 run of every precision is checked against the CPU oracle.
     """
+    import ios_oracle as oracle
     from ios.contrib import ios_runtime as rt
     saved = rt.get_option('precision')
-    flops_per_image = 2.0 * sum(c.output_shape[0] * c.output_shape[1] * c.output_shape[2] * c.kernel[0] * c.kernel[1] *
-                                (c.input_shape[0] // c.groups) for c in graph.convs())
-    graph.greedy_schedule()
-    out = []
-    for precision in (saved, 'bf16'):
+    flops_per_image = conv_flops_per_image(graph)
+    greedy = graph
+    greedy.greedy_schedule()
+    out, parity = [], {}
+    for precision in ('tf32x3', 'tf32', 'bf16'):
         rt.set_option('precision', precision)
-        peak = peaks['bf16_tflops'] if precision == 'bf16' else peaks['bf16_tflops'] / 2.0
+        peak = tensor_peak(peaks, precision)
         for batch in (16, 64, 256):
-            engine = rt.Engine(graph, batch, synthetic_weights=True)
+            engine = rt.Engine(greedy, batch)
+            if batch == 16:
+                x = oracle.normal_input(config, batch, 1)
+                parity[precision] = checked_images(engine.run(x), config, weights, x)
+                if parity[precision] > PARITY_BOUND[precision]:
+                    raise RuntimeError(f'throughput sweep: {precision} batch 16 is off by {parity[precision]}')
             engine.time(2)
             ms = engine.time(5)
             engine.close()
@@ -371,7 +450,81 @@ def throughput_sweep(graph, peaks, peak_kind):
             out.append({'precision': precision, 'batch': batch, 'ms': round(ms, 3), 'images_per_s': round(batch / ms * 1e3, 1),
                         'conv_tflops': round(tflops, 1), 'frac_of_tensor_peak': round(tflops / peak, 4)})
     rt.set_option('precision', saved)
-    return {'schedule': 'greedy', 'peak_source': f'{peak_kind} bf16 burst (bf16) or half of it (tf32)', 'points': out}
+    return {'schedule': 'greedy', 'peak_source': f'{peak_kind} bf16 burst (bf16) or half of it (tf32)',
+            'parity_max_rel_err_batch16': parity, 'points': out}
+
+
+def sharded_sweep(graph, config, weights, ranks, peaks, peak_kind, args):
+    """
+    The batch-sharded configuration: a global batch of 256 (and 64) images split evenly over the ranks,
+    one engine per GPU on its shard, no collective on the data path.  Every rank searches the schedule for
+    ITS shard's batch size and precision on its own GPU (ios.optimize, dp_parallel_merge, measured stage
+    latencies) and keeps the greedy schedule instead if that is faster when timed whole.  Reported per
+    point: device-resident images/s (CUDA events over K back-to-back forwards, max over ranks), end-to-end
+    images/s (K steps through ios_engine_run_pipelined from / to page-locked host buffers, wall clock, max
+    over ranks) and the convolution TFLOP/s as a fraction of N x the measured tensor peak.
+    """
+    import torch
+    import ios
+    import ios_oracle as oracle
+    from ios.contrib import ios_runtime as rt
+    saved = rt.get_option('precision')
+    flops_per_image = conv_flops_per_image(graph)
+    points = []
+    steps = max(args.steps, 10)
+    for precision in ('bf16', 'tf32x3'):
+        rt.set_option('precision', precision)
+        for global_batch in (256, 64):
+            if global_batch % ranks.world:
+                continue
+            shard = global_batch // ranks.world
+            t0 = time.time()
+            dp = ios.optimize(graph, batch_size=shard, opt_type='dp_parallel_merge', compute_weight=True, max_part_size=50,
+                              warmup=1, number=2, repeat=1)
+            search_s = time.time() - t0
+            graph.greedy_schedule()
+            chosen, whole = rt.pick_faster([dp, graph], shard, warmup=1, number=3, repeat=2)
+            engine = rt.Engine(chosen, shard)
+            x = oracle.normal_input(config, shard, 100 + ranks.rank)
+            host_in = torch.from_numpy(x).pin_memory()
+            host_out = torch.empty(engine.output_shape, dtype=torch.float32).pin_memory()
+            parity = checked_images(engine.run(host_in.data_ptr(), host_out.numpy()), config, weights, x)
+            if parity > PARITY_BOUND[precision]:
+                raise RuntimeError(f'sharded sweep: {precision} shard batch {shard} is off by {parity}')
+            engine.set_input(x)
+            engine.time(3)
+            ranks.barrier()
+            device_ms = ranks.max_over_ranks(engine.time(steps))
+            engine.run_pipelined([host_in.data_ptr()] * 3, [host_out.data_ptr()] * 3)
+            ranks.barrier()
+            t0 = time.perf_counter()
+            engine.run_pipelined([host_in.data_ptr()] * steps, [host_out.data_ptr()] * steps)
+            e2e_ms = ranks.max_over_ranks(1e3 * (time.perf_counter() - t0) / steps)
+            t0 = time.perf_counter()
+            for _ in range(steps):
+                engine.run(host_in.data_ptr(), host_out.data_ptr())
+            serial_ms = ranks.max_over_ranks(1e3 * (time.perf_counter() - t0) / steps)
+            ranks.barrier()
+            info = engine.describe()
+            engine.close()
+            tflops = flops_per_image * global_batch / (device_ms * 1e-3) / 1e12
+            points.append({
+                'precision': precision, 'global_batch': global_batch, 'shard_batch': shard,
+                'schedule': 'dp' if whole[0] <= whole[1] else 'greedy', 'stages': info['stages'],
+                'whole_ms_dp_vs_greedy': [round(v, 4) for v in whole], 'schedule_search_s': round(search_s, 1),
+                'device_ms_per_step': round(device_ms, 4), 'images_per_s': round(global_batch / device_ms * 1e3, 1),
+                'e2e_ms_per_step': round(e2e_ms, 4), 'e2e_images_per_s': round(global_batch / e2e_ms * 1e3, 1),
+                'e2e_unpipelined_images_per_s': round(global_batch / serial_ms * 1e3, 1),
+                'h2d_bytes_per_step_per_gpu': int(x.nbytes), 'd2h_bytes_per_step_per_gpu': int(host_out.numel() * 4),
+                'conv_tflops': round(tflops, 1),
+                'frac_of_tensor_peak': round(tflops / (ranks.world * tensor_peak(peaks, precision)), 4),
+                'parity_max_rel_err': parity})
+            del host_in, host_out
+    rt.set_option('precision', saved)
+    return {'note': 'global batch split evenly over the ranks, no collective on the data path; schedule searched per rank '
+                    'for the shard batch; steps per point: %d' % steps,
+            'peak_source': f'{peak_kind} bf16 burst (bf16) or half of it (tf32x3), times the number of GPUs',
+            'points': points}
 
 
 def cpu_baseline(config, weights, x, batch, budget_s=15.0):
@@ -439,7 +592,7 @@ def run_reference(args):
             def get_stage_latency(self, stage, batch_size, warmup, number, repeat, profile_stage=False):
                 return ref.stage_latency(stage, batch_size, warmup, number, repeat)
 
-        exec_graph, search_s = schedule_graph(graph, args.schedule, args.batch, cost_model=RefCost())
+        exec_graph, search_s = schedule_graph(graph, args.schedule, args.batch, cost_model=RefCost(), number=4, repeat=2)
         samples = ref.graph_latency(exec_graph, args.batch, args.warmup, 1, args.steps)
         ms = float(np.mean(samples))
         value = args.batch / (ms * 1e-3)
@@ -477,6 +630,8 @@ def main():
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-sweep', dest='sweep', action='store_false',
                     help='skip the batch 16/64/256 throughput sweep that the default single-GPU run appends')
+    ap.add_argument('--no-sharded-sweep', dest='sharded_sweep', action='store_false',
+                    help='skip the batch-sharded configuration (global batch 256 and 64 split over the ranks)')
     ap.add_argument('--executor', default='graph', choices=['graph', 'streams'],
                     help='streams: plain launches instead of a CUDA graph (used for kernel-level profiling)')
     ap.add_argument('--precision', default=None, help='runtime precision option (default: the library default)')

@@ -275,6 +275,7 @@ void issue_forward(StreamSet &ctx, const Plan &plan, const std::vector<cudaEvent
 
 struct GraphExec {
     cudaGraphExec_t exec = nullptr;
+    bool programmatic = false;   // its kernel -> kernel edges were all made programmatic
     ~GraphExec() {
         if (exec) cudaGraphExecDestroy(exec);
     }
@@ -336,6 +337,8 @@ void capture(StreamSet &ctx, GraphExec *out, F &&body, bool programmatic_edges =
             if (err != cudaSuccess) {
                 cudaGetLastError();
                 out->exec = nullptr;
+            } else {
+                out->programmatic = true;
             }
         }
     }
@@ -1099,12 +1102,12 @@ int ios_engine_describe(ios_engine *engine, char *text, int capacity) {
                       "\"conv_depthwise\": %d, "
                       "\"sum_act\": %d, \"pool\": %d, \"stages\": %zu, \"arena_bytes\": %zu, \"workspace_bytes\": %zu, "
                       "\"weight_bytes\": %zu, \"conv_flops\": %.0f, \"output_shape\": [%d, %d, %d, %d], \"executor\": \"%s\", "
-                      "\"stage_barriers\": %d, \"pdl_edges\": %d, \"device\": %d, \"precision\": \"%s\"}",
+                      "\"stage_barriers\": %d, \"pdl_edges\": %d, \"pdl_edges_applied\": %d, \"device\": %d, \"precision\": \"%s\"}",
                       p.launches_per_forward, n_tc, n_split, n_persistent, n_half, n_direct_store, n_direct, n_few, n_dw, n_sum,
                       n_pool, p.model.stages.size(), e.bytes,
                       p.workspace_bytes, weight_bytes, p.model.conv_flops(), p.model.batch, out.C, out.H, out.W,
                       p.options.use_graph ? "graph" : "streams", p.options.stage_barriers ? 1 : 0, p.options.pdl_edges ? 1 : 0,
-                      e.device,
+                      e.exec_core.programmatic ? 1 : 0, e.device,
                       p.options.bf16 ? "bf16" : !p.options.tf32 ? "fp32" : p.options.three_pass ? "tf32x3" : "tf32");
     });
 }

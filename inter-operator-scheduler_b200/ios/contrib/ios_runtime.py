@@ -163,11 +163,49 @@ def stage_config(stage: List[List[Node]]):
     return json.dumps(groups), json.dumps({name: list(shape) for name, shape in producers.items()})
 
 
+def canonical_stage_key(stage_text: str, input_text: str) -> str:
+    """
+    A key that is equal for candidate stages of the same structure whatever their operators are called:
+    names are replaced by their order of first appearance and hint names dropped.  Networks repeat their
+    blocks (three Inception-A, four Inception-C ...), so a search meets every such stage several times
+    and needs to measure it once.
+    """
+    groups, producers = json.loads(stage_text), json.loads(input_text)
+    order = {}
+
+    def canon(name):
+        return order.setdefault(name, f'n{len(order)}')
+
+    def walk(node):
+        node = dict(node)
+        node['hint_name'] = ''
+        node['inputs'] = [[[canon(v[0]), v[1], v[2]] for v in term] for term in node.get('inputs', [])]
+        if 'nodes' in node:
+            node['nodes'] = [walk(sub) for sub in node['nodes']]
+        node['name'] = canon(node['name'])
+        return node
+
+    body = [[walk(node) for node in group] for group in groups]
+    shapes = sorted((canon(name), list(shape)) for name, shape in producers.items() if name in order)
+    return json.dumps([body, shapes])
+
+
 def stage_latency(stage: List[List[Node]], batch_size, warmup, number, repeat, profile_stage=False):
     """Latency of one candidate stage (groups x operators) on synthetic inputs; what the DP search calls."""
     stage_text, input_text = stage_config(stage)
     return _timed(_library().ios_stage_latency, (stage_text.encode(), input_text.encode()), batch_size, warmup,
                   number, repeat, profile_stage, repeat)
+
+
+def pick_faster(graphs, batch_size, warmup=2, number=6, repeat=6):
+    """
+    Time each scheduled graph with ``graph_latency`` and return ``(best graph, [mean latency ms of each])``.
+    A DP schedule is assembled from stage latencies measured one by one; where those do not add up (wide
+    graphs of tiny operators) a heuristic schedule can still win, and a caller that wants the fastest
+    schedule it has should measure the candidates whole.
+    """
+    means = [float(np.mean(graph_latency(g, batch_size, warmup, number, repeat))) for g in graphs]
+    return graphs[int(np.argmin(means))], means
 
 
 def _conv_arrays(graph: Graph):

@@ -9,7 +9,8 @@ from typing import List
 import numpy as np
 
 from ios.ir import Graph, Block, Node
-from ios.contrib.ios_runtime import graph_latency, stage_latency, block_latency
+from ios.contrib.ios_runtime import (graph_latency, stage_latency, block_latency, stage_config, canonical_stage_key,
+                                     get_option)
 
 
 class CostModel:
@@ -42,7 +43,16 @@ class RandomCostModel(CostModel):
 
 
 class IOSCostModel(CostModel):
-    """Measure by executing on the GPU (reference ``cost_model.py:36-49``)."""
+    """
+    Measure by executing on the GPU (reference ``cost_model.py:36-49``).  With ``dedup`` (default) a
+    candidate stage whose structure was measured before -- the same operators under other names, as the
+    repeated blocks of a network produce them -- is answered from a memo instead of being timed again.
+    """
+
+    def __init__(self, dedup=True):
+        self.dedup = dedup
+        self.memo = {}
+        self.measured = 0
 
     def get_graph_latency(self, graph, batch_size, warmup, number, repeat, profile_stage=False):
         return graph_latency(graph, batch_size, warmup, number, repeat, profile_stage)
@@ -51,4 +61,12 @@ class IOSCostModel(CostModel):
         return block_latency(block, batch_size, warmup, number, repeat, profile_stage)
 
     def get_stage_latency(self, stage, batch_size, warmup, number, repeat, profile_stage=False):
-        return stage_latency(stage, batch_size, warmup, number, repeat, profile_stage)
+        if not self.dedup or profile_stage:
+            self.measured += 1
+            return stage_latency(stage, batch_size, warmup, number, repeat, profile_stage)
+        key = (canonical_stage_key(*stage_config(stage)), int(batch_size), warmup, number, repeat,
+               get_option('precision'))
+        if key not in self.memo:
+            self.measured += 1
+            self.memo[key] = stage_latency(stage, batch_size, warmup, number, repeat)
+        return list(self.memo[key])

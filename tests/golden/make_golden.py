@@ -35,8 +35,11 @@ def sha(config):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument('--ref', default='/root/reference')
+    ap.add_argument('--ref', default=os.environ.get('IOS_REFERENCE', os.path.join(os.path.dirname(ROOT), 'reference')),
+                    help='the reference checkout (default: $IOS_REFERENCE, else a folder named reference beside this repository)')
     args = ap.parse_args()
+    if not os.path.isdir(os.path.join(args.ref, 'python', 'ios')):
+        raise SystemExit(f'no reference checkout at {args.ref}: pass --ref or set IOS_REFERENCE')
     sys.modules.setdefault('pydot', types.ModuleType('pydot'))   # the visualizer imports it; nothing here draws
     sys.path.insert(0, os.path.join(args.ref, 'python'))
     import ios                                   # the reference package
@@ -114,6 +117,21 @@ def main():
     g = ios.Graph('randwire_small', pv.node, blocks)
     g.sequential_schedule()
     record('randwire_small', g, 0, 0)
+
+    # -- the rest of the reference's model zoo: residual adds (element nodes), a block searched in parts --
+    from ios.models import nasnet as ref_nasnet, resnet as ref_resnet
+    # (resnet50 is exported and hashed only: the reference builds its bottleneck with a last convolution of
+    #  `channels` outputs that is added to a shortcut of 4 x `channels`, which its own executor rejects)
+    for case, maker in (('resnet18', ref_resnet.resnet18), ('resnet34', ref_resnet.resnet34),
+                        ('nasnet_large', ref_nasnet.nasnet_large)):
+        g = maker()
+        g.sequential_schedule()
+        record(case, g, 0, 0)
+        block = g.blocks[0]
+        if block.parts is not None:
+            manifest[case]['parts'] = [[node.name for node in part] for part in block.parts]
+    for case, maker in (('resnet50', ref_resnet.resnet50), ('vgg_16', ios.models.vgg_16), ('alexnet', ios.models.alexnet)):
+        manifest[case + '_config'] = {'config_sha256': sha(maker().export_config())}
 
     # -- a small graph that touches every operator type ---------------------------------------
     common.reset_name()

@@ -60,7 +60,7 @@ def test_executor_variants_reproduce_the_reference_outputs(golden, model, option
     try:
         info = engine.describe()
         assert info['stage_barriers'] == (0 if option == 'stage_barriers' else 1)
-        assert info['pdl_edges'] == (1 if option == 'pdl_edges' else 0)
+        assert info['pdl_edges'] == info['pdl_edges_applied'] == (1 if option == 'pdl_edges' else 0)
         for _ in range(3):
             assert np.array_equal(engine.run(x), base)
         assert engine.time(5) > 0
@@ -114,7 +114,7 @@ def test_global_max_and_global_avg_pooling(precision, tol):
     v = ios.placeholder(output_shape=(40, 9, 7))
     block = ios.Block(enter_node=v.node)
     c = ios.conv2d(block, [[v]], out_channels=24, kernel=(3, 3), padding=(1, 1), act='tanh')
-    gm = ios.pool2d(block, [[c]], pool_type='global_max')
+    gm = ios.pool2d(block, [[c]], pool_type='global_max', kernel=(9, 7))     # the IR infers the window of global_avg only (reference ir.py:531-535)
     ga = ios.pool2d(block, [[c]], pool_type='global_avg')
     ios.identity(block, [[gm], [ga]], is_exit=True)
     graph = ios.Graph('pools', v.node, [block])

@@ -180,6 +180,9 @@ def test_all_operator_types_graph(golden):
     ('inception_v3_uniform_b2', 'inception_v3', 'uniform', 1, 1, 2),
     ('squeezenet', 'squeezenet', 'he', 0, 0, 1),
     ('randwire_small', 'randwire_small', 'he', 0, 0, 1),
+    ('resnet18', 'resnet18', 'he', 0, 0, 1),
+    ('resnet34', 'resnet34', 'he', 0, 0, 1),
+    ('nasnet_large', 'nasnet_large', 'he', 0, 0, 1),
 ])
 def test_networks_match_reference_outputs(golden, case, model, law, wseed, xseed, batch):
     graph = sample_block() if model == 'sample_block' else getattr(ios.models, model)()
@@ -193,7 +196,7 @@ def test_networks_match_reference_outputs(golden, case, model, law, wseed, xseed
 @pytest.mark.parametrize('case,model,batch,law,wseed,xseed', [
     ('sample_block', 'sample_block', 1, 'he', 0, 0), ('inception_v3', 'inception_v3', 1, 'he', 0, 0),
     ('inception_v3_uniform_b2', 'inception_v3', 2, 'uniform', 1, 1), ('squeezenet', 'squeezenet', 1, 'he', 0, 0),
-    ('randwire_small', 'randwire_small', 1, 'he', 0, 0)])
+    ('randwire_small', 'randwire_small', 1, 'he', 0, 0), ('resnet18', 'resnet18', 1, 'he', 0, 0)])
 def test_networks_in_bfloat16(golden, case, model, batch, law, wseed, xseed):
     """precision=bf16: bfloat16 storage and products, fp32 accumulation; the bar is 2e-2."""
     rt.set_option('precision', 'bf16')

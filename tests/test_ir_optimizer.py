@@ -48,6 +48,28 @@ def test_model_shapes():
     assert [b.exit_node.output_shape for b in g.blocks[1:4]] == [(78, 28, 28), (156, 14, 14), (312, 7, 7)]
 
 
+def test_model_zoo_exports_equal_the_reference_exports(golden):
+    """Graphs that are only hashed (resnet50 cannot execute in the reference either: its bottleneck adds 64 to 256 channels)."""
+    for case, maker in (('resnet50', ios.models.resnet50), ('vgg_16', ios.models.vgg_16), ('alexnet', ios.models.alexnet)):
+        assert sha(maker().export_config()) == golden.meta(case + '_config')['config_sha256'], case
+    g = ios.models.resnet18()
+    assert g.exit_node.output_shape == (512, 7, 7) or list(g.exit_node.output_shape) == [512, 7, 7]
+    assert g.blocks[0].stages is not None            # the reference hands its ResNets back with the sequential schedule
+
+
+def test_nasnet_parts_follow_the_cells(golden):
+    g = ios.models.nasnet_large()
+    block = g.blocks[0]
+    assert [[n.name for n in part] for part in block.parts] == golden.meta('nasnet_large')['parts']
+    assert sum(len(p) for p in block.parts) == len(block.inner_nodes) + 1
+    # the search works part by part: a random cost model is enough to see that every operator is scheduled once
+    np.random.seed(1)
+    opt = ios.optimize(g, batch_size=1, cost_model=ios.RandomCostModel(), opt_type='dp_parallel_merge', max_group_size=1,
+                       max_num_groups=3)
+    names = [n for stage in opt.blocks[0].stages for group in stage for n in group]
+    assert len(names) == len(set(names)) == len(opt.blocks[0].inner_nodes) + 1
+
+
 def test_greedy_schedule_covers_every_operator():
     g = ios.models.inception_v3()
     g.greedy_schedule(max_num_stream=4)

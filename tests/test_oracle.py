@@ -29,6 +29,9 @@ def _model(name):
     ('inception_v3_uniform_b2', 'inception_v3', 'uniform', 1, 1, 2),
     ('squeezenet', 'squeezenet', 'he', 0, 0, 1),
     ('randwire_small', 'randwire_small', 'he', 0, 0, 1),
+    ('resnet18', 'resnet18', 'he', 0, 0, 1),            # residual adds are element nodes
+    ('resnet34', 'resnet34', 'he', 0, 0, 1),
+    ('nasnet_large', 'nasnet_large', 'he', 0, 0, 1),    # one block of 370 schedule units, ReLU-separable convolutions
 ])
 def test_oracle_matches_reference_outputs(golden, case, model, law, wseed, xseed, batch):
     graph = _model(model)

@@ -71,8 +71,16 @@ def test_static_scratch_conv_against_the_oracle(cout, split, offset):
     n, h, w, cin = 1, 17, 17, 192
     pixels = n * h * w
     rng = np.random.default_rng(cout + split)
-    x = rng.standard_normal((n, cin, h, w)).astype(np.float32)
-    wt = (rng.standard_normal((cout, cin, 1, 1)) / np.sqrt(cin)).astype(np.float32)
+
+    def tf32(a):
+        """Keep the 10 mantissa bits a TF32 operand has: the tensor core then multiplies exactly what the oracle does."""
+        return (a.astype(np.float32).view(np.uint32) & np.uint32(0xFFFFE000)).view(np.float32)
+
+    # this entry point takes the caller's weights as they are (nothing is packed or rounded on the way in), so the
+    # tensor core drops the low 13 bits of both operands; with operands that have none, only the order of the
+    # fp32 additions differs from the oracle
+    x = tf32(rng.standard_normal((n, cin, h, w)))
+    wt = tf32(rng.standard_normal((cout, cin, 1, 1)) / np.sqrt(cin))
     b = (rng.standard_normal(cout) * 0.1).astype(np.float32)
     ref = oracle.conv2d_numpy(x, wt, b, (1, 1), (0, 0), 1, 'tanh')
     x_dev = torch.from_numpy(np.ascontiguousarray(x.transpose(0, 2, 3, 1))).cuda()
@@ -86,7 +94,7 @@ def test_static_scratch_conv_against_the_oracle(cout, split, offset):
         assert status == 0, lib.ios_last_error().decode()
         assert lib.ios_static_scratch_status(None) == 0, lib.ios_last_error().decode()
         got = y_dev.cpu().numpy().reshape(n, h, w, cout).transpose(0, 3, 1, 2)
-        assert oracle.max_rel_err(got, ref) <= TOL_TF32
+        assert oracle.max_rel_err(got, ref) <= 2e-5
     assert torch.isnan(y_all[offset + pixels * cout:]).all()          # nothing was written past the output
 
 
