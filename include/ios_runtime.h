@@ -155,6 +155,30 @@ IOS_API int ios_conv2d(const float *x, const float *w, const float *bias, float 
                        int wdt, int cout, int kh, int kw, int sh, int sw, int ph, int pw, int groups,
                        int act, int impl);
 
+/* ---- the schedule search (replaces ending_iterator / dop / get_stage_list of the reference,
+ *      python/ios/optimizer.py:450-606, which run in Python) ------------------------------------------
+ * One handle per part of a block.  Operators are numbered 0..n-1 in topological order; succ_lo/succ_hi hold,
+ * per operator, the bit set of its direct successors inside the part (bits 0-63 / 64-127); merge_key is -1
+ * for an operator that is no convolution, else (class << 1) | plain, where convolutions of one class read the
+ * same value at the same resolution with equal stride and activation and plain means groups == 1 and a single
+ * input value; chains (chain_offsets[num_chains + 1] into chain_nodes) are a chain decomposition of the part.
+ * ios_dp_enumerate lists every candidate stage the search will ask a latency for, in the order of the first
+ * request; ios_dp_stage returns one (kind 0 = merged convolution, 1 = parallel groups; group_offsets has
+ * num_groups + 1 entries into nodes; both arrays need room for n + 1 / n ints); after ios_dp_set_latency for
+ * every stage, ios_dp_solve evaluates cost(s) = min over endings (cost(s - e) + latency(e)) and ios_dp_chosen
+ * returns the chosen stage indices, first stage first. */
+typedef struct ios_dp ios_dp;
+IOS_API int ios_dp_create(int n, const unsigned long long *succ_lo, const unsigned long long *succ_hi,
+                          const int *merge_key, int num_chains, const int *chain_offsets, const int *chain_nodes,
+                          int use_merge, int use_parallel, int max_group_size, int max_num_groups, ios_dp **out);
+IOS_API int ios_dp_enumerate(ios_dp *search, int *num_stages);
+IOS_API int ios_dp_stage(ios_dp *search, int index, int *kind, int *num_groups, int *group_offsets, int *nodes);
+IOS_API int ios_dp_set_latency(ios_dp *search, int index, double latency);
+IOS_API int ios_dp_solve(ios_dp *search, int *num_chosen, double *best_cost, long long *num_states,
+                         long long *num_transitions);
+IOS_API int ios_dp_chosen(ios_dp *search, int *stage_indices);
+IOS_API int ios_dp_destroy(ios_dp *search);
+
 /* ---- allocation-free entry point (it has no counterpart in the reference) --------------------
  * y[pixels][cout] = act(x[pixels][cin] * w[cout][cin]^T + bias): a 1x1 convolution over NHWC data
  * (pixels = N*H*W), single-pass TF32 products with fp32 accumulation, for callers that are not

@@ -17,7 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, 'csrc')
 OBJ = os.path.join(HERE, 'build')
 TARGET = os.path.join(HERE, 'ios', 'libios_runtime.so')
-SOURCES = ['graph.cc', 'bandwidth_ops.cu', 'conv_direct.cu', 'conv_tc.cu', 'plan.cu', 'runtime.cu', 'no_alloc.cu']
+SOURCES = ['graph.cc', 'dp_search.cc', 'bandwidth_ops.cu', 'conv_direct.cu', 'conv_tc.cu', 'conv_tc_patch.cu', 'plan.cu', 'runtime.cu', 'no_alloc.cu']
 NVCC = os.environ.get('NVCC', '/usr/local/cuda/bin/nvcc')
 FLAGS = ['-gencode', 'arch=compute_100a,code=sm_100a', '-lineinfo', '-O3', '-std=c++17',
          '-Xcompiler', '-fPIC,-fvisibility=hidden,-Wall,-Wno-unused-function', '-x', 'cu']

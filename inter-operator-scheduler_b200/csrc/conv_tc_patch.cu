@@ -1,0 +1,527 @@
+// Stride-1 convolutions with a window (3x3, 5x5, 1x7, 7x1 ...) on the tensor cores, every input pixel
+// fetched ONCE per tile instead of once per filter tap.
+//
+// The implicit-GEMM kernel of conv_tc.cu loads, for each of the kh*kw taps, a fresh 128-pixel activation
+// tile through the TMA unit; on B200 that unit, not the tensor pipe, bounds such layers (about 1.2
+// cycles per 128-byte row plus 1 cycle per 100 bytes, measured).  Here a tile's input PATCH -- ph x pw
+// pixels per image, the tile's outputs plus the window's halo -- lands in shared memory once per channel
+// chunk as rows in (image, row, column) order, and GEMM row m is the output pixel
+//     m = (image * ph + y) * pw + x,
+// so that tap (r, s) of EVERY output pixel of the tile is patch row m + r*pw + s: the A operand of tap
+// (r, s) is the same shared-memory tile read from a start address (r*pw + s) rows further on.  (The
+// 128-byte swizzle is a function of the shared-memory address, so an operand may start at any row.)
+// Rows whose x >= box_w or y >= box_h are halo positions: their accumulators are garbage and are simply
+// not stored.  Padding is the zero fill of the TMA unit for coordinates outside the image.
+//
+// A tile therefore costs ph*pw rows of activations (instead of taps*128) plus taps*bn rows of weights per
+// channel chunk; when the whole packed weight matrix is small (the first layers of a network) it is
+// loaded once per CTA and stays resident.  In three-pass TF32 mode the residual of the activations is
+// computed once per patch instead of once per tap.
+//
+// Persistent CTAs (one or two per SM) walk the tiles; warp 0 lane 0 loads patches, lane 1 weight tiles,
+// warp 1 issues tcgen05.mma into one of two accumulators in tensor memory, the other warps finish the
+// previous tile (bias, activation, stores of the valid rows).  Every wait is bounded.
+//
+// Replaces cudnnConvolutionBiasActivationForward (reference src/ios/ios_runtime.cu:313-331) for these shapes.
+#include "kernels.h"
+#include "tc_device.h"
+
+#include <algorithm>
+#include <cstring>
+
+namespace ios {
+namespace {
+
+constexpr int kPatchThreads = 320;
+
+struct PatchGeom {
+    int bn, cchunks, taps, kw, chunk;
+    int pw, ph;                       // patch extent per image, input pixels
+    int box_w, box_h, box_n;          // valid output extent of a tile
+    int tiles_w, tiles_h, n_tiles, total_tiles;
+    int a_rows;                       // rows of one plane of an activation stage (multiple of 8)
+    int a_stages, b_stages;
+    int a_tx_bytes;                   // bytes one patch load delivers
+    int b_resident;                   // 1: every weight tile is loaded once and kept (b_stages = taps * cchunks)
+    int tmem_cols, acc_stride;
+    int wide, round_tf32, cout_pad;
+    int pad_w, pad_h;
+};
+
+template <int MODE>      // 0: TF32, 1: three-pass TF32, 2: BF16
+__global__ void __launch_bounds__(kPatchThreads, 1)
+conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                     const ConvTcParams p, const PatchGeom t) {
+    constexpr bool kX3 = MODE == 1, kBf16 = MODE == 2;
+    constexpr int kRow = 128;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ float bias_s[2][256];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
+    const int planes = kX3 ? 2 : 1;
+    const int a_plane = t.a_rows * kRow;
+    const int a_stage_bytes = planes * a_plane;
+    const int b_bytes = t.bn * kRow;
+    const int b_stage_bytes = planes * b_bytes;
+    const uint32_t a0 = smem_base;
+    const uint32_t b0 = a0 + uint32_t(t.a_stages) * a_stage_bytes;
+    const uint32_t bars = b0 + uint32_t(t.b_stages) * b_stage_bytes;
+    const uint32_t a_full0 = bars, a_empty0 = a_full0 + 8u * t.a_stages, a_ready0 = a_empty0 + 8u * t.a_stages;
+    const uint32_t b_full0 = a_ready0 + 8u * t.a_stages, b_empty0 = b_full0 + 8u * t.b_stages;
+    const uint32_t acc_full0 = b_empty0 + 8u * t.b_stages, acc_empty0 = acc_full0 + 16u;
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(generic_base + (acc_empty0 + 16u - smem_base));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const ConvGeom &g = p.g;
+    const int epi_warps = kX3 ? 4 : 8;
+    const int my_tiles = (t.total_tiles - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x);
+
+    if (warp == 0) {
+        for (int i = lane; i < t.a_stages; i += 32) {
+            mbar_init(a_full0 + 8u * i, 1);
+            mbar_init(a_empty0 + 8u * i, 1);
+            mbar_init(a_ready0 + 8u * i, 128);
+        }
+        for (int i = lane; i < t.b_stages; i += 32) {
+            mbar_init(b_full0 + 8u * i, 1);
+            mbar_init(b_empty0 + 8u * i, 1);
+        }
+        if (lane < 2) {
+            mbar_init(acc_full0 + 8u * lane, 1);
+            mbar_init(acc_empty0 + 8u * lane, uint32_t(epi_warps));
+        }
+        if (lane == 31) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 2) {
+        tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), uint32_t(t.tmem_cols));
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if ((warp == 0 && lane >= 2) || (warp == 1 && lane != 0)) return;
+
+    // tile -> coordinates: output-channel tile fastest, then tiles along w, h, n
+    auto decode = [&](int tile, int &cout0, int &ow0, int &oh0, int &n0) {
+        const int m_tile = tile / t.n_tiles;
+        cout0 = (tile - m_tile * t.n_tiles) * t.bn;
+        const int tw = m_tile % t.tiles_w;
+        const int rest = m_tile / t.tiles_w;
+        ow0 = tw * t.box_w;
+        oh0 = (rest % t.tiles_h) * t.box_h;
+        n0 = (rest / t.tiles_h) * t.box_n;
+    };
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- activation patches: one load per (tile, channel chunk) ----------------
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        int s = 0, phase = 1, issued = 0;
+        bool ok = true;
+#pragma unroll 1
+        for (int ti = 0; ti < my_tiles && ok; ++ti) {
+            int cout0, ow0, oh0, n0;
+            decode(int(blockIdx.x) + ti * int(gridDim.x), cout0, ow0, oh0, n0);
+#pragma unroll 1
+            for (int cc = 0; cc < t.cchunks; ++cc) {
+                ok = mbar_wait(a_empty0 + 8u * s, uint32_t(phase), p.error_flag);
+                if (!ok) break;
+                const uint32_t bar = a_full0 + 8u * s;
+                mbar_expect_tx(bar, uint32_t(t.a_tx_bytes));
+                tma_load_4d(a0 + uint32_t(s) * a_stage_bytes, &tmap_a, bar, cc * t.chunk, ow0 - t.pad_w, oh0 - t.pad_h, n0);
+                ++issued;
+                if (++s == t.a_stages) { s = 0; phase ^= 1; }
+            }
+        }
+        if (!ok) {
+            atomicExch(p.error_flag, 1);
+            // the loads already issued still land here: wait for the latest one of every stage
+            for (int j = issued - 1, k = 0; j >= 0 && k < t.a_stages; --j, ++k)
+                mbar_wait(a_full0 + 8u * (j % t.a_stages), uint32_t((j / t.a_stages) & 1), nullptr);
+        }
+        return;
+    }
+    if (warp == 0) {
+        // ---------------- weight tiles: one load per (tile, channel chunk, tap), or once if they stay ----------------
+        int s = 0, phase = 1, issued = 0;
+        bool ok = true;
+        const int rounds = t.b_resident ? 1 : my_tiles;
+#pragma unroll 1
+        for (int ti = 0; ti < rounds && ok; ++ti) {
+            int cout0, ow0, oh0, n0;
+            decode(int(blockIdx.x) + ti * int(gridDim.x), cout0, ow0, oh0, n0);
+#pragma unroll 1
+            for (int cc = 0; cc < t.cchunks && ok; ++cc) {
+#pragma unroll 1
+                for (int tap = 0; tap < t.taps; ++tap) {
+                    ok = mbar_wait(b_empty0 + 8u * s, uint32_t(phase), p.error_flag);
+                    if (!ok) break;
+                    const uint32_t bar = b_full0 + 8u * s, dst = b0 + uint32_t(s) * b_stage_bytes;
+                    const int kcol = (tap * t.cchunks + cc) * t.chunk;
+                    mbar_expect_tx(bar, uint32_t(b_stage_bytes));
+                    tma_load_2d(dst, &tmap_b, bar, kcol, cout0);
+                    if (kX3) tma_load_2d(dst + uint32_t(b_bytes), &tmap_b, bar, kcol, t.cout_pad + cout0);
+                    ++issued;
+                    if (++s == t.b_stages) { s = 0; phase ^= 1; }
+                }
+            }
+        }
+        if (!ok) {
+            atomicExch(p.error_flag, 1);
+            for (int j = issued - 1, k = 0; j >= 0 && k < t.b_stages; --j, ++k)
+                mbar_wait(b_full0 + 8u * (j % t.b_stages), uint32_t((j / t.b_stages) & 1), nullptr);
+        }
+        return;
+    }
+    if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        const uint32_t fmt = kBf16 ? 1u : 2u;
+        const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(t.bn >> 3) << 17) | (uint32_t(kTileM >> 4) << 24);
+        const uint32_t idesc_wide = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(t.bn >> 2) << 17) | (uint32_t(kTileM >> 4) << 24);
+        const uint32_t a_wait0 = kX3 ? a_ready0 : a_full0;
+        int sa = 0, sb = 0;
+        uint32_t pa = 0, pb = 0;
+        bool ok = true;
+#pragma unroll 1
+        for (int ti = 0; ti < my_tiles && ok; ++ti) {
+            const uint32_t a = uint32_t(ti) & 1u;
+            ok = mbar_wait(acc_empty0 + 8u * a, ((uint32_t(ti) >> 1) & 1u) ^ 1u, p.error_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t tmem_d = tmem_base + a * uint32_t(t.acc_stride);
+            uint32_t first = 0u;        // 0 until the tile's first instruction has been issued
+#pragma unroll 1
+            for (int cc = 0; cc < t.cchunks && ok; ++cc) {
+                ok = mbar_wait(a_wait0 + 8u * sa, pa, p.error_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_hi = a0 + uint32_t(sa) * a_stage_bytes;
+                int r = 0, sx = 0;
+#pragma unroll 1
+                for (int tap = 0; tap < t.taps; ++tap) {
+                    const int slot = t.b_resident ? cc * t.taps + tap : sb;
+                    ok = mbar_wait(b_full0 + 8u * slot, t.b_resident ? 0u : pb, p.error_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_tap = a_hi + uint32_t(r * t.pw + sx) * kRow;
+                    const uint64_t da = smem_desc_kmajor(a_tap, kRow), dal = smem_desc_kmajor(a_tap + uint32_t(a_plane), kRow);
+                    const uint32_t b_hi = b0 + uint32_t(slot) * b_stage_bytes;
+                    const uint64_t db = smem_desc_kmajor(b_hi, kRow), dbl = smem_desc_kmajor(b_hi + uint32_t(b_bytes), kRow);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const uint32_t acc = first | (k > 0 ? 1u : 0u);
+                        if (kX3 && t.wide) {
+                            umma_tf32(tmem_d, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc_wide, acc);
+                            umma_tf32(tmem_d, dal + uint64_t(k * 2), db + uint64_t(k * 2), idesc, 1u);
+                        } else if (kX3) {
+                            umma_tf32(tmem_d, dal + uint64_t(k * 2), db + uint64_t(k * 2), idesc, acc);
+                            umma_tf32(tmem_d, da + uint64_t(k * 2), dbl + uint64_t(k * 2), idesc, 1u);
+                            umma_tf32(tmem_d, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, 1u);
+                        } else if (kBf16) {
+                            umma_f16(tmem_d, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, acc);
+                        } else {
+                            umma_tf32(tmem_d, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, acc);
+                        }
+                    }
+                    first = 1u;
+                    if (!t.b_resident) {
+                        umma_commit(b_empty0 + 8u * sb);
+                        if (++sb == t.b_stages) { sb = 0; pb ^= 1u; }
+                    }
+                    if (++sx == t.kw) { sx = 0; ++r; }
+                }
+                if (!ok) break;
+                umma_commit(a_empty0 + 8u * sa);          // the patch is free once these instructions have read it
+                if (++sa == t.a_stages) { sa = 0; pa ^= 1u; }
+            }
+            if (ok) umma_commit(acc_full0 + 8u * a);
+        }
+        if (!ok) atomicExch(p.error_flag, 2);
+        return;
+    }
+    if (kX3 && warp >= 6) {
+        // ---------------- warps 6..9 (three-pass mode): residual of every landed patch ----------------
+        const int tid = threadIdx.x - 192;
+        const int n_vec = t.a_tx_bytes >> 4;
+        const long steps = long(my_tiles) * t.cchunks;
+        int s = 0;
+        uint32_t phase = 0;
+#pragma unroll 1
+        for (long i = 0; i < steps; ++i) {
+            if (!mbar_wait(a_full0 + 8u * s, phase, p.error_flag)) {
+                atomicExch(p.error_flag, 4);
+                break;
+            }
+            uint8_t *stage = generic_base + size_t(s) * a_stage_bytes;
+            const float4 *hi = reinterpret_cast<const float4 *>(stage);
+            float4 *lo = reinterpret_cast<float4 *>(stage + a_plane);
+#pragma unroll 2
+            for (int v = tid; v < n_vec; v += 128) {
+                const float4 x = hi[v];
+                float4 l;
+                l.x = x.x - __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u);
+                l.y = x.y - __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u);
+                l.z = x.z - __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u);
+                l.w = x.w - __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u);
+                lo[v] = l;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(a_ready0 + 8u * s) : "memory");
+            if (++s == t.a_stages) { s = 0; phase ^= 1u; }
+        }
+        return;
+    }
+    // ---------------- epilogue warps ----------------
+    const int e = warp - 2;
+    const int etid = threadIdx.x - 64;
+    const int epi_threads = epi_warps * 32;
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const int cols_per_warp = epi_warps == 8 ? t.bn / 2 : t.bn;
+    const int c_begin = (e >> 2) * cols_per_warp, c_end = c_begin + cols_per_warp;
+    const uint32_t pair = t.wide ? uint32_t(t.bn) : 0u;
+    // which output pixel of a tile this thread's row is (the same for every tile)
+    const int per_image = t.ph * t.pw;
+    const int img = row / per_image;
+    const int rem = row - img * per_image;
+    const int ry = rem / t.pw, rx = rem - ry * t.pw;
+    const bool row_in_box = img < t.box_n && ry < t.box_h && rx < t.box_w;
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // the output window may still be read by the previous kernel
+#pragma unroll 1
+    for (int ti = 0; ti < my_tiles; ++ti) {
+        int cout0, ow0, oh0, n0;
+        decode(int(blockIdx.x) + ti * int(gridDim.x), cout0, ow0, oh0, n0);
+        const uint32_t a = uint32_t(ti) & 1u;
+        float *bias = bias_s[a];
+        for (int j = etid; j < t.bn; j += epi_threads) bias[j] = (p.bias && cout0 + j < g.Cout) ? p.bias[cout0 + j] : 0.0f;
+        bool ok = mbar_wait(acc_full0 + 8u * a, (uint32_t(ti) >> 1) & 1u, p.error_flag);
+        ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
+        if (!ok && lane == 0) atomicExch(p.error_flag, 3);
+        tc_fence_after();
+        asm volatile("bar.sync 1, %0;" ::"r"(epi_threads) : "memory");      // bias complete
+        const int valid = min(t.bn, g.Cout - cout0);
+        const int n = n0 + img, oh = oh0 + ry, ow = ow0 + rx;
+        const bool live = ok && row_in_box && n < g.N && oh < g.OH && ow < g.OW;
+        const long pix_off = ((long(n) * g.OH + oh) * g.OW + ow) * p.out.pitch;
+        if (ok) {
+            const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + a * uint32_t(t.acc_stride);
+#pragma unroll 1
+            for (int c = c_begin; c < c_end; c += 16) {
+                float v[16];
+                acc_ld16(taddr + c, pair, v);              // (a warp-wide instruction: every lane takes part)
+                if (!live || c >= valid) continue;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float z = act_apply(v[j] + bias[c + j], g.act);
+                    v[j] = t.round_tf32 ? round_tf32(z) : z;
+                }
+#pragma unroll
+                for (int j = 0; j < 16; j += 4)
+                    if (c + j < valid)
+                        store4_direct(p.out.ptr, kBf16, pix_off + cout0 + c + j, make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]),
+                                      valid - (c + j));
+            }
+        }
+        // hand the accumulator back to the MMA issuer: one arrival per epilogue warp
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty0 + 8u * a) : "memory");
+    }
+    tc_fence_before();
+    asm volatile("bar.sync 1, %0;" ::"r"(epi_threads) : "memory");
+    if (warp == 2) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, uint32_t(t.tmem_cols));
+    }
+}
+
+}  // namespace
+
+// ---- host side -------------------------------------------------------------------------------
+namespace {
+
+int ceil_div_i(int a, int b) { return (a + b - 1) / b; }
+
+// Cycles the TMA unit of an SM spends on a load of `rows` rows of 128 bytes (measured on B200: a layer
+// bound by its loads takes about 1.15 cycles per row plus one cycle per 100 bytes, whatever the mode).
+double tma_cycles(double rows) { return rows * 1.15 + rows * 128.0 / 100.0; }
+
+}  // namespace
+
+// Decides whether a convolution that conv_tc_choose gave to the resident-CTA kernel should run as a patch
+// convolution instead, and if so rewrites the plan (tile width, geometry, shared memory, grid).
+void conv_tc_patch_consider(const ConvGeom &g, int sm_count, ConvTcPlan *plan) {
+    ConvTcPlan &q = *plan;
+    q.patch = 0;
+    if (q.no_patch || !q.persistent || q.split_k != 1) return;
+    if (g.sh != 1 || g.sw != 1 || g.kh * g.kw < 2 || g.groups != 1) return;
+    const int taps = g.kh * g.kw;
+    if (g.kw > 64 || g.kh > 64) return;
+    // a window of one row never looks across image rows: images and rows become one axis
+    const bool merged = g.kh == 1 && g.ph == 0;
+    const int OHm = merged ? g.N * g.OH : g.OH, Nm = merged ? 1 : g.N;
+    // output-channel tile: as wide as tensor memory allows (a patch is loaded once per output-channel tile)
+    const int bn_step = q.bf16 ? 64 : 32;
+    const int bn_cap = 256;
+    const int n_tiles = ceil_div_i(g.Cout, bn_cap);
+    const int bn = std::min(bn_cap, ceil_div_i(ceil_div_i(g.Cout, n_tiles), bn_step) * bn_step);
+    const bool wide = q.x3 && bn <= 128;
+    const int acc_cols = (wide ? 2 : 1) * ceil_div_i(bn, 32) * 32;
+    if (2 * acc_cols > 512) return;
+    const int planes = q.x3 ? 2 : 1;
+    const int chunk = q.bf16 ? 64 : 32;
+    const int cchunks = ceil_div_i(g.Cin, chunk);
+    const int b_stage = planes * bn * 128;
+    // weights that fit stay resident (the first layers of a network: a few dozen KiB)
+    const bool b_resident = n_tiles == 1 && taps * cchunks <= 48 && long(taps) * cchunks * b_stage <= 72 * 1024;
+    auto fixed_bytes = [](int as, int bs) { return 1024 + 8 * (3 * as + 2 * bs) + 128; };   // alignment slack, barriers, slot
+    const double tensor_col = 2.1 * 1.15 * (q.x3 ? 3.0 : 1.0);
+    const double issue_tap = (q.x3 ? (wide ? 8 : 12) : 4) * 50.0 + 60.0;
+
+    // tile extent: output rows cut into `parts` even segments of box_w pixels, as many rows (and, where a whole
+    // image fits, images) as 128 GEMM rows hold beside the halo columns; the cheapest candidate wins
+    struct Cand { int box_w, box_h, box_n, pw, ph, a_rows, tiles_w, tiles_h, tiles_n, resident, a_stages, b_stages; double cost; };
+    Cand best = {};
+    best.cost = 1e30;
+    const int min_parts = ceil_div_i(g.OW, kTileM - g.kw + 1);
+    for (int parts = min_parts; parts < min_parts + 8 && parts <= g.OW; ++parts) {
+        Cand c = {};
+        c.box_w = ceil_div_i(g.OW, parts);
+        c.pw = c.box_w + g.kw - 1;
+        c.box_h = std::min(OHm, (kTileM - c.box_w) / c.pw + 1);
+        c.box_h = ceil_div_i(OHm, ceil_div_i(OHm, c.box_h));
+        c.ph = c.box_h + g.kh - 1;
+        c.box_n = 1;
+        if (c.box_w == g.OW && c.box_h == OHm && Nm > 1) {
+            c.box_n = std::min(Nm, (kTileM - ((c.box_h - 1) * c.pw + c.box_w)) / (c.ph * c.pw) + 1);
+            c.box_n = ceil_div_i(Nm, ceil_div_i(Nm, c.box_n));
+        }
+        if (c.pw > 256 || c.ph > 256 || c.box_n > 256) continue;
+        const int patch_rows = c.box_n * c.ph * c.pw;
+        const int max_off = (g.kh - 1) * c.pw + g.kw - 1;
+        c.a_rows = (std::max(patch_rows, kTileM + max_off) + 7) / 8 * 8;
+        c.tiles_w = ceil_div_i(g.OW, c.box_w);
+        c.tiles_h = ceil_div_i(OHm, c.box_h);
+        c.tiles_n = ceil_div_i(Nm, c.box_n);
+        const long m_tiles = long(c.tiles_w) * c.tiles_h * c.tiles_n;
+        if (m_tiles * n_tiles > (1l << 24)) continue;
+        const int a_stage = planes * c.a_rows * 128;
+        for (int want = 2; want >= 1 && !c.resident; --want) {
+            if (want == 2 && 4 * acc_cols > 512) continue;
+            const int bs_min = b_resident ? taps * cchunks : 3;
+            const int as_min = (cchunks > 1 || m_tiles * n_tiles > long(sm_count) * want) ? 2 : 1;
+            const int budget = (want == 2 ? 110 : 210) * 1024;
+            if (as_min * a_stage + bs_min * b_stage + fixed_bytes(as_min, bs_min) > budget) continue;
+            c.resident = want;
+            c.b_stages = bs_min;
+            c.a_stages = as_min;
+            while (c.a_stages < 3 && (c.a_stages + 1) * a_stage + c.b_stages * b_stage + fixed_bytes(c.a_stages + 1, c.b_stages) <= budget)
+                ++c.a_stages;
+            while (!b_resident && c.b_stages < 8 &&
+                   c.a_stages * a_stage + (c.b_stages + 1) * b_stage + fixed_bytes(c.a_stages, c.b_stages + 1) <= budget)
+                ++c.b_stages;
+        }
+        if (!c.resident) continue;
+        // per SM: the TMA unit serves the resident CTAs in turn, the tensor pipe too, the issuing threads work side by side
+        const double chunk_cycles = std::max({tma_cycles(patch_rows) + (b_resident ? 0.0 : tma_cycles(double(taps) * bn * planes)),
+                                              taps * bn * tensor_col, taps * issue_tap / c.resident});
+        c.cost = double(m_tiles) * n_tiles * (cchunks * chunk_cycles + 400.0);
+        if (c.cost < best.cost) best = c;
+    }
+    if (best.cost >= 1e30) return;
+    // compare with what the plan has now (an activation tile per tap)
+    const long old_tiles = (long(g.N) * g.OH * g.OW + kTileM - 1) / kTileM * q.n_tiles;
+    const double old_step = std::max({tma_cycles(kTileM + double(q.bn) * planes), q.bn * tensor_col, (q.x3 ? 700.0 : 450.0) / 2.0});
+    const double old_cost = double(old_tiles) * (double(taps) * q.cchunks * old_step + 400.0);
+    if (best.cost > 0.92 * old_cost) return;
+    const int box_w = best.box_w, box_h = best.box_h, box_n = best.box_n, pw = best.pw, ph = best.ph, a_rows = best.a_rows;
+    const int tiles_w = best.tiles_w, tiles_h = best.tiles_h, tiles_n = best.tiles_n;
+    const int resident = best.resident, a_stages = best.a_stages, b_stages = best.b_stages;
+    const long m_tiles = long(tiles_w) * tiles_h * tiles_n;
+    const int a_stage = planes * a_rows * 128;
+    const int fixed = fixed_bytes(a_stages, b_stages);
+
+    q.patch = 1;
+    q.half_rows = 0;
+    q.cchunks = cchunks;
+    q.k_iters = taps * cchunks;
+    q.bn = bn;
+    q.n_tiles = n_tiles;
+    q.cout_pad = n_tiles * bn;
+    q.box_w = box_w; q.box_h = box_h; q.box_n = box_n;
+    q.tiles_w = tiles_w; q.tiles_h = tiles_h; q.tiles_n = tiles_n;
+    q.patch_pw = pw; q.patch_ph = ph; q.patch_a_rows = a_rows;
+    q.patch_a_stages = a_stages; q.patch_b_stages = b_stages; q.patch_b_resident = b_resident ? 1 : 0;
+    q.patch_merged = merged ? 1 : 0;
+    q.im2col = 0;
+    q.flat_1x1 = 0;
+    q.stages = b_stages;
+    q.persistent = 1;
+    q.grid_ctas = int(std::min<long>(m_tiles * n_tiles, long(sm_count) * resident));
+    q.smem_bytes = size_t(a_stages) * a_stage + size_t(b_stages) * b_stage + fixed;
+    // a CTA that needs the SM to itself also takes more than half of its shared memory
+    if (resident == 1) q.smem_bytes = std::max(q.smem_bytes, size_t(120 * 1024));
+    q.workspace_bytes = 0;
+    q.counter_bytes = 0;
+}
+
+cudaError_t conv_tc_patch_prepare() {
+    const void *forms[] = {reinterpret_cast<const void *>(conv_tc_patch_kernel<0>), reinterpret_cast<const void *>(conv_tc_patch_kernel<1>),
+                           reinterpret_cast<const void *>(conv_tc_patch_kernel<2>)};
+    for (const void *form : forms) {
+        cudaError_t err = cudaFuncSetAttribute(form, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024);
+        if (err != cudaSuccess) return err;
+    }
+    return cudaSuccess;
+}
+
+void launch_conv_tc_patch(const ConvTcParams &p, const ConvTcPlan &q, cudaStream_t stream) {
+    PatchGeom t;
+    const ConvGeom &g = p.g;
+    t.bn = q.bn; t.cchunks = q.cchunks; t.taps = g.kh * g.kw; t.kw = g.kw; t.chunk = q.bf16 ? 64 : 32;
+    t.pw = q.patch_pw; t.ph = q.patch_ph;
+    t.box_w = q.box_w; t.box_h = q.box_h; t.box_n = q.box_n;
+    t.tiles_w = q.tiles_w; t.tiles_h = q.tiles_h; t.n_tiles = q.n_tiles;
+    t.total_tiles = q.tiles_w * q.tiles_h * q.tiles_n * q.n_tiles;
+    t.a_rows = q.patch_a_rows; t.a_stages = q.patch_a_stages; t.b_stages = q.patch_b_stages;
+    t.a_tx_bytes = q.patch_pw * q.patch_ph * q.box_n * 128;
+    t.b_resident = q.patch_b_resident;
+    t.wide = (q.x3 && q.bn <= 128) ? 1 : 0;
+    t.acc_stride = (t.wide ? 2 : 1) * ceil_div_i(q.bn, 32) * 32;
+    int cols = 32;
+    while (cols < 2 * t.acc_stride) cols *= 2;
+    t.tmem_cols = cols;
+    t.round_tf32 = g.round_out;
+    t.cout_pad = q.cout_pad;
+    t.pad_w = g.pw; t.pad_h = g.ph;
+    ConvTcParams pp = p;
+    if (q.patch_merged) {               // images and rows as one axis (see conv_tc_patch_consider)
+        pp.g.H = g.N * g.H; pp.g.OH = g.N * g.OH; pp.g.N = 1;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(std::min(q.grid_ctas, t.total_tiles)));
+    cfg.blockDim = dim3(kPatchThreads);
+    cfg.dynamicSmemBytes = q.smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    int n_attr = 0;
+    if (q.pdl) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n_attr;
+    const CUtensorMap &ma = *reinterpret_cast<const CUtensorMap *>(q.tmap_a), &mb = *reinterpret_cast<const CUtensorMap *>(q.tmap_b);
+    if (q.x3) cudaLaunchKernelEx(&cfg, conv_tc_patch_kernel<1>, ma, mb, pp, t);
+    else if (q.bf16) cudaLaunchKernelEx(&cfg, conv_tc_patch_kernel<2>, ma, mb, pp, t);
+    else cudaLaunchKernelEx(&cfg, conv_tc_patch_kernel<0>, ma, mb, pp, t);
+}
+
+}  // namespace ios

@@ -137,6 +137,14 @@ struct ConvTcPlan {
     size_t workspace_bytes;        // split-K partial tiles (0 when split_k == 1)
     size_t counter_bytes;          // split-K arrival counters
     int cout_pad;                  // rows of the packed weight matrix
+    // patch convolution (conv_tc_patch.cu): stride-1 windows, every input pixel loaded once per tile
+    int patch;                     // 1: this plan runs as a patch convolution
+    int no_patch;                  // testing aid: never do
+    int patch_pw, patch_ph;        // patch extent per image (input pixels): tile outputs plus the window's halo
+    int patch_a_rows;              // rows of one activation stage
+    int patch_a_stages, patch_b_stages;
+    int patch_b_resident;          // 1: the packed weights are loaded once per CTA and stay in shared memory
+    int patch_merged;              // 1: one-row windows: images and rows are one axis
     alignas(64) unsigned char tmap_a[128];   // CUtensorMap over the input view
     alignas(64) unsigned char tmap_b[128];   // CUtensorMap over the packed weights
     alignas(64) unsigned char tmap_c[128];   // CUtensorMap over the output window (when tma_store)
@@ -167,6 +175,11 @@ const char *conv_tc_encode_dense_weights(const ConvTcParams &p, ConvTcPlan *plan
 // Raises the kernel's dynamic shared-memory limit; call once per device before the first launch.
 cudaError_t conv_tc_prepare();
 void launch_conv_tc(const ConvTcParams &p, const ConvTcPlan &plan, cudaStream_t stream);
+// Patch convolution: may take over a plan that conv_tc_choose gave to the resident-CTA kernel (call it right
+// after conv_tc_choose / conv_tc_set_split and before the weights are sized and packed).
+void conv_tc_patch_consider(const ConvGeom &g, int sm_count, ConvTcPlan *plan);
+cudaError_t conv_tc_patch_prepare();
+void launch_conv_tc_patch(const ConvTcParams &p, const ConvTcPlan &plan, cudaStream_t stream);
 size_t conv_tc_packed_bytes(const ConvGeom &g, const ConvTcPlan &plan);
 // Host-side packing of OIHW weights into the tensor-core layout (rounds to TF32 or bfloat16, nearest even).
 void conv_tc_pack_weights(const float *oihw, const ConvGeom &g, const ConvTcPlan &plan, void *packed);

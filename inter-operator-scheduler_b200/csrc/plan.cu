@@ -414,9 +414,11 @@ private:
             conv_tc_choose(g, sms_, width_, plan_.options.three_pass, &slot.tcplan, plan_.options.force_bn, plan_.options.bf16,
                            !plan_.options.no_im2col);
             if (plan_.options.force_split_k > 0) conv_tc_set_split(&slot.tcplan, plan_.options.force_split_k);
+            slot.tcplan.no_patch = plan_.options.no_patch ? 1 : 0;
+            conv_tc_patch_consider(g, sms_, &slot.tcplan);
             slot.tcplan.pdl = plan_.options.pdl ? 1 : 0;
             slot.tcplan.max_producers = plan_.options.producers;
-            if (plan_.options.force_stages > 0 && !slot.tcplan.persistent) {   // testing aid: shallower pipeline
+            if (plan_.options.force_stages > 0 && !slot.tcplan.persistent && !slot.tcplan.patch) {   // testing aid: shallower pipeline
                 ConvTcPlan &q = slot.tcplan;
                 const size_t stage_bytes = (q.smem_bytes - 24 * q.stages - 64 - 1024) / q.stages;   // (whatever the row width)
                 const int stages = std::max(2, std::min(q.stages, plan_.options.force_stages));

@@ -421,6 +421,28 @@ class FarmCostModel:
             self.measured += 1
         return self.memo[key]
 
+    def get_stage_latencies(self, stages, batch_size, warmup, number, repeat):
+        """
+        Many candidate stages at once (what the native search asks for): those not in the memo are measured in
+        parallel on the pool, structurally equal ones (same operators under other names) only once.
+        """
+        from ios.contrib.ios_runtime import stage_config, canonical_stage_key
+        configs = [stage_config(stage) for stage in stages]
+        keys = [self._key(canonical_stage_key(s, i), '', int(batch_size), warmup, number, repeat) for s, i in configs]
+        todo, first = [], {}
+        for key, (stage_json, input_json) in zip(keys, configs):
+            if key not in self.memo and key not in first:
+                first[key] = len(todo)
+                todo.append((stage_json, input_json, int(batch_size), warmup, number, repeat))
+        if todo:
+            values = self.pool.map('stage_latency', todo)
+            for key, index in first.items():
+                self.memo[key] = [float(v) for v in values[index]]
+            self.measured += len(todo)
+            if self.memo_path:
+                self.save(self.memo_path)
+        return [self.memo[key] for key in keys]
+
     def get_block_latency(self, block, batch_size, warmup, number, repeat, profile_stage=False):
         raise NotImplementedError('the DP search only asks for stage latencies')
 

@@ -316,6 +316,125 @@ def dop(s: int, block, chains, on_debug, debug_dp_info, idn, nid, dp, ep, opt_ty
     return best
 
 
+# --------------------------------------------------------------------------------------------
+# the same search in native code (csrc/dp_search.cc)
+# --------------------------------------------------------------------------------------------
+NATIVE_PART_LIMIT = 128
+
+
+def _native_library():
+    """The runtime library if it exports the native search, else None."""
+    try:
+        from ios.contrib import ios_runtime
+        lib = ios_runtime._library()
+        return lib if hasattr(lib, 'ios_dp_create') else None
+    except (OSError, FileNotFoundError):
+        return None
+
+
+def _merge_keys(part: List[Node]):
+    """
+    Per operator: -1 if it is no convolution, else ``(class << 1) | plain``.  Two convolutions are of one class
+    when they read the same first value at the same resolution with equal stride and activation; ``plain`` says
+    groups == 1 and a single input value (what ``check_merge`` asks of every operator but the first of a set).
+    """
+    classes, keys = {}, []
+    for node in part:
+        if not isinstance(node, Conv):
+            keys.append(-1)
+            continue
+        first = node.inputs[0][0]
+        signature = (tuple(node.input_shape[1:]), tuple(node.output_shape[1:]), tuple(node.stride), node.act,
+                     id(first.node), first.begin, first.end)
+        cls = classes.setdefault(signature, len(classes))
+        plain = node.groups == 1 and len(node.inputs) == 1 and len(node.inputs[0]) == 1
+        keys.append((cls << 1) | (1 if plain else 0))
+    return keys
+
+
+def search_part_native(lib, part: List[Node], block, nid, idn, opt_type, max_group_size, max_num_groups, cost_model,
+                       batch_size, warmup, number, repeat) -> List[Stage]:
+    """
+    One part of a block through the native search: enumerate the candidate stages (in the order the Python
+    search would first ask for them), measure each through ``cost_model`` -- all of them at once if the model
+    offers ``get_stage_latencies`` -- and let the native code evaluate the recurrence.  Returns the chosen
+    stages, first stage first, with operators as block indices.
+    """
+    import ctypes
+    n = len(part)
+    local = {node: i for i, node in enumerate(part)}
+    graph = build_graph(part, nid)
+    chains = graph_chain_decomposition(graph)
+    succ = []
+    for node in part:
+        mask = 0
+        for v in graph[nid[node]]:
+            mask |= 1 << local[idn[v]]
+        succ.append(mask)
+    lo = (ctypes.c_ulonglong * n)(*[m & 0xFFFFFFFFFFFFFFFF for m in succ])
+    hi = (ctypes.c_ulonglong * n)(*[m >> 64 for m in succ])
+    keys = (ctypes.c_int * n)(*_merge_keys(part))
+    flat = [local[idn[u]] for chain in chains for u in chain]
+    offsets = list(itertools.accumulate([0] + [len(chain) for chain in chains]))
+    handle = ctypes.c_void_p(None)
+
+    def check(status):
+        if status != 0:
+            lib.ios_last_error.restype = ctypes.c_char_p
+            raise RuntimeError(f'native search error {status}: {lib.ios_last_error().decode(errors="replace")}')
+
+    lib.ios_dp_create.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p,
+                                  ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                  ctypes.POINTER(ctypes.c_void_p)]
+    lib.ios_dp_set_latency.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_double]
+    for name in ('ios_dp_enumerate', 'ios_dp_stage', 'ios_dp_solve', 'ios_dp_chosen', 'ios_dp_destroy'):
+        getattr(lib, name).argtypes = None
+    check(lib.ios_dp_create(n, lo, hi, keys, len(chains), (ctypes.c_int * len(offsets))(*offsets),
+                            (ctypes.c_int * max(1, len(flat)))(*flat), 1 if 'merge' in opt_type else 0,
+                            1 if 'parallel' in opt_type else 0, int(max_group_size), int(max_num_groups), ctypes.byref(handle)))
+    try:
+        count = ctypes.c_int(0)
+        check(lib.ios_dp_enumerate(handle, ctypes.byref(count)))
+        kind, groups_n = ctypes.c_int(0), ctypes.c_int(0)
+        group_offsets, nodes = (ctypes.c_int * (n + 1))(), (ctypes.c_int * n)()
+        candidates: List[Stage] = []
+        for index in range(count.value):
+            check(lib.ios_dp_stage(handle, index, ctypes.byref(kind), ctypes.byref(groups_n), group_offsets, nodes))
+            groups = [[nid[part[nodes[k]]] for k in range(group_offsets[g], group_offsets[g + 1])]
+                      for g in range(groups_n.value)]
+            candidates.append((groups, 'merge' if kind.value == 0 else 'parallel'))
+        # the measurements, in the order of first request
+        probes = [_stage_probe(stage, block, idn, nid) for stage in candidates]
+        many = getattr(cost_model, 'get_stage_latencies', None)
+        if many is not None:
+            values = many(probes, batch_size, warmup, number, repeat)
+        else:
+            values = [cost_model.get_stage_latency(probe, batch_size, warmup, number, repeat) for probe in probes]
+        for index, value in enumerate(values):
+            check(lib.ios_dp_set_latency(handle, index, ctypes.c_double(float(np.mean(value)))))
+        chosen_n = ctypes.c_int(0)
+        check(lib.ios_dp_solve(handle, ctypes.byref(chosen_n), None, None, None))
+        chosen = (ctypes.c_int * max(1, chosen_n.value))()
+        check(lib.ios_dp_chosen(handle, chosen))
+        return [candidates[chosen[i]] for i in range(chosen_n.value)]
+    finally:
+        lib.ios_dp_destroy(handle)
+
+
+def _stage_probe(stage: Stage, block, idn, nid) -> List[List[Node]]:
+    """The operators handed to the cost model for one candidate stage (reference ``optimizer.py:297-340``)."""
+    groups, kind = stage
+    if kind == 'parallel':
+        return [[idn[u] for u in group] for group in groups]
+    nodes = [idn[group[0]] for group in groups]
+    if len(nodes) == 1:
+        return [[nodes[0]]]
+    out_channels, kernel, stride, padding = _merged_conv_params(nodes)
+    probe = Conv('c', '', inputs=get_input(nodes, block, nid, idn), out_channels=out_channels, kernel=kernel,
+                 stride=stride, padding=padding, groups=nodes[0].groups, act=nodes[0].act, output_shape=None)
+    return [[probe]]
+
+
 def get_stage_list(ep, s):
     """Follow the recorded best endings from the full state down to the empty one; first stage first."""
     picked = []
@@ -477,7 +596,7 @@ def optimize(graph: Graph,
              opt_type: str = 'dp_parallel_merge',
              warmup=2, number=6, repeat=6,
              max_num_groups=8, max_part_size=100, compute_weight=False, max_group_size=3,
-             debug_dp_info=None, verbose=False) -> Graph:
+             debug_dp_info=None, verbose=False, native=None) -> Graph:
     """
     Search an execution schedule for ``graph`` and return a NEW graph named ``{name}_{opt_type}``
     that carries it (signature and defaults of the reference, ``optimizer.py:37-43``).
@@ -485,6 +604,11 @@ def optimize(graph: Graph,
     ``opt_type`` must contain ``parallel`` and/or ``merge`` (``dp_parallel``, ``dp_merge``,
     ``dp_parallel_merge``).  With ``compute_weight`` the convolutions of the new graph receive
     weights (merged ones zero-embedded); without it they have none and the graph can only be timed.
+
+    ``native`` (not in the reference): run the enumeration and the recurrence in the runtime library
+    (csrc/dp_search.cc) instead of in Python -- same candidate stages, same order of measurements, same
+    schedule.  Default: whenever the library is there, no statistics are asked for and a part has at most
+    128 operators.
     """
     if cost_model is None:
         cost_model = IOSCostModel()
@@ -511,6 +635,12 @@ def optimize(graph: Graph,
                              max_num_groups=max_num_groups, max_part_size=max_part_size,
                              max_group_size=max_group_size))
 
+    native_lib = None
+    if native is not False and not on_debug and bar_state is None:
+        native_lib = _native_library()
+        if native and native_lib is None:
+            raise RuntimeError('the native search was asked for but libios_runtime.so does not provide it')
+
     graph_enter = Placeholder(graph.input.name, graph.input.hint_name, graph.input.output_shape)
     graph_enter.output_shape = graph.enter_node.output_shape
     new_blocks: List[Block] = []
@@ -526,6 +656,10 @@ def optimize(graph: Graph,
 
         stage_list: List[Stage] = []
         for part in parts:
+            if native_lib is not None and len(part) <= NATIVE_PART_LIMIT:
+                stage_list.extend(search_part_native(native_lib, part, block, nid, idn, opt_type, max_group_size,
+                                                     max_num_groups, cost_model, batch_size, warmup, number, repeat))
+                continue
             dp: Dict[int, float] = {}
             ep: Dict[int, Stage] = {}
             merge_latency: Dict[int, float] = {}

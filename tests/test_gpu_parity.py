@@ -104,6 +104,34 @@ def test_conv_many_tiles_vs_oracle(shape, persistent):
     assert _conv_case(shape, 'bf16') <= TOL_BF16
 
 
+# stride-1 windows over many tiles: one input patch per tile, taps read it at shifted rows (conv_tc_patch.cu)
+PATCH_SHAPES = [
+    (8, 48, 35, 35, 64, 5, 5, 1, 1, 2, 2, 1),       # 5x5 pad 2: three output rows per tile
+    (8, 96, 35, 35, 96, 3, 3, 1, 1, 1, 1, 1),       # two channel chunks in bfloat16, three in float32
+    (6, 32, 149, 149, 32, 3, 3, 1, 1, 0, 0, 1),     # rows wider than a tile: cut into segments; resident weights
+    (40, 160, 17, 17, 192, 1, 7, 1, 1, 0, 3, 1),    # one-row window: images and rows are one axis
+    (40, 160, 17, 17, 192, 7, 1, 1, 1, 3, 0, 1),    # one-column window
+    (64, 448, 8, 8, 384, 3, 3, 1, 1, 1, 1, 1),      # small images, two output-channel tiles
+    (200, 40, 5, 6, 48, 3, 3, 1, 1, 1, 1, 1),       # several whole images per tile
+    (16, 24, 20, 20, 30, 3, 3, 1, 1, 2, 2, 1),      # padding wider than the window needs; Cout not a multiple of 4
+    (16, 64, 30, 31, 72, 1, 3, 1, 1, 0, 1, 1),      # 1x3
+    (16, 64, 30, 31, 72, 3, 1, 1, 1, 1, 0, 1),      # 3x1
+    (12, 80, 73, 73, 192, 3, 3, 1, 1, 0, 0, 1),     # Inception stem 80 -> 192
+]
+
+
+@pytest.mark.parametrize('patch', ['1', '0'])
+@pytest.mark.parametrize('shape', PATCH_SHAPES)
+def test_conv_patch_vs_oracle(shape, patch):
+    rt.set_option('patch', patch)
+    try:
+        assert _conv_case(shape, 'tensor') <= TOL_FP32
+        assert _conv_case(shape, 'tensor1') <= TOL_TF32
+        assert _conv_case(shape, 'bf16') <= TOL_BF16
+    finally:
+        rt.set_option('patch', '1')
+
+
 # at most 4 input channels and many pixels: the CUDA-core kernel that keeps the filter in shared memory
 @pytest.mark.parametrize('shape', [
     (8, 3, 299, 299, 32, 3, 3, 2, 2, 0, 0, 1),     # Inception stem at batch 8

@@ -144,3 +144,61 @@ def test_iter_subset_and_counters():
     assert list(iter_subset(0b11, include_emtpy_set=True)) == [3, 2, 1, 0]
     g = sample_block()
     assert g.flops() > 0 and g.schedule_operators() == 5
+
+
+@pytest.mark.parametrize('model,opt_type,kwargs', [
+    ('sample_block', 'dp_parallel_merge', {}), ('squeezenet', 'dp_parallel_merge', {}), ('squeezenet', 'dp_merge', {}),
+    ('inception_v3', 'dp_parallel_merge', {'max_part_size': 50}), ('inception_v3', 'dp_parallel', {'max_part_size': 50}),
+    ('resnet18', 'dp_parallel_merge', {}), ('randwire_small', 'dp_parallel_merge', {'max_group_size': 1, 'max_num_groups': 3}),
+])
+def test_native_search_equals_the_python_search(model, opt_type, kwargs):
+    """Same candidate stages, same order of measurements, same schedule: the exported graphs are identical."""
+    results = []
+    for native in (False, True):
+        graph = sample_block() if model == 'sample_block' else getattr(ios.models, model)()
+        np.random.seed(11)
+        opt = ios.optimize(graph, batch_size=1, cost_model=ios.RandomCostModel(), opt_type=opt_type, native=native, **kwargs)
+        results.append(json.dumps(opt.export_config()))
+    assert results[0] == results[1]
+
+
+def test_native_search_asks_for_all_stages_at_once_when_the_cost_model_can():
+    class Batched(ios.cost_model.CostModel):
+        calls = 0
+
+        def get_stage_latencies(self, stages, batch_size, warmup, number, repeat):
+            Batched.calls += 1
+            return [[float(sum(len(group) for group in stage)) + 0.25 * len(stage)] * repeat for stage in stages]
+
+    graph = ios.models.squeezenet()
+    opt = ios.optimize(graph, batch_size=1, cost_model=Batched(), opt_type='dp_parallel_merge', native=True)
+    assert Batched.calls == len(graph.blocks)             # one request per block (each block is one part)
+    names = [n for block in opt.blocks for stage in block.stages for group in stage for n in group]
+    assert len(names) == len(set(names))
+
+
+def test_native_search_rejects_bad_input():
+    import ctypes
+    from ios.contrib import ios_runtime as rt
+    lib = rt.load_ios_library()
+    handle = ctypes.c_void_p(None)
+    lo, hi, keys = (ctypes.c_ulonglong * 2)(1, 0), (ctypes.c_ulonglong * 2)(0, 0), (ctypes.c_int * 2)(-1, -1)
+    offsets, nodes = (ctypes.c_int * 2)(0, 2), (ctypes.c_int * 2)(0, 1)
+    # operator 0 lists itself as a successor: not a topological order
+    assert lib.ios_dp_create(2, lo, hi, keys, 1, offsets, nodes, 1, 1, 3, 8, ctypes.byref(handle)) == 3
+    assert lib.ios_dp_create(200, lo, hi, keys, 1, offsets, nodes, 1, 1, 3, 8, ctypes.byref(handle)) == 6
+    lo = (ctypes.c_ulonglong * 2)(2, 0)
+    assert lib.ios_dp_create(2, lo, hi, keys, 1, offsets, nodes, 0, 1, 3, 8, ctypes.byref(handle)) == 0
+    count = ctypes.c_int(0)
+    assert lib.ios_dp_enumerate(handle, ctypes.byref(count)) == 0 and count.value == 3      # {0,1}, then {0} (met while descending), then {1}
+    chosen = ctypes.c_int(0)
+    assert lib.ios_dp_solve(handle, ctypes.byref(chosen), None, None, None) == 3            # latencies are missing
+    lib.ios_dp_set_latency.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_double]
+    for index, value in enumerate((2.0, 0.5, 0.75)):
+        assert lib.ios_dp_set_latency(handle, index, value) == 0
+    best = ctypes.c_double(0.0)
+    assert lib.ios_dp_solve(handle, ctypes.byref(chosen), ctypes.byref(best), None, None) == 0
+    assert chosen.value == 2 and abs(best.value - 1.25) < 1e-12                            # two stages beat the joint one
+    order = (ctypes.c_int * 2)()
+    assert lib.ios_dp_chosen(handle, order) == 0 and list(order) == [1, 2]                  # {0} first, then {1}
+    lib.ios_dp_destroy(handle)
