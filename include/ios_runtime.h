@@ -118,6 +118,16 @@ typedef struct ios_engine ios_engine;
 IOS_API int ios_engine_create(const char *graph_json, int batch_size, int num_convs, char **conv_names,
                               float **filter_data, float **bias_data, ios_engine **engine);
 IOS_API int ios_engine_destroy(ios_engine *engine);
+/* Engine artefact: the scheduled graph, the options it was built under, and every convolution's parameters
+ * already packed for the kernel and tiling that run it, in one file.  ios_engine_load rebuilds the engine
+ * from it on the current device without the float32 weights, without packing and without a schedule
+ * search -- what a serving process wants at start-up.  The tiling is re-derived and compared with the
+ * stored one: an artefact written by another library version, under other options or for a GPU with another
+ * SM count is refused (IOS_ERR_ARGUMENT), never misread.  Replaces the reference's conv2alg.txt side file
+ * (src/ios/ios_runtime.cu:91-125), which only remembers cuDNN algorithm numbers, and its per-call weight
+ * upload (:1252-1272). */
+IOS_API int ios_engine_save(ios_engine *engine, const char *path);
+IOS_API int ios_engine_load(const char *path, ios_engine **engine);
 /* Host in -> host out.  input[batch, C, H, W], output[batch, Cexit, Hexit, Wexit]. */
 IOS_API int ios_engine_run(ios_engine *engine, const float *input, float *output);
 /* Host in -> host out for `count` batches in a row, copies overlapped with compute: while batch i runs,

@@ -19,20 +19,27 @@
 // computed once per patch instead of once per tap.
 //
 // Persistent CTAs (one or two per SM) walk the tiles; warp 0 lane 0 loads patches, lane 1 weight tiles,
-// warp 1 issues tcgen05.mma into one of two accumulators in tensor memory, the other warps finish the
-// previous tile (bias, activation, stores of the valid rows).  Every wait is bounded.
+// the other warps finish the previous tile (bias, activation, stores of the valid rows) while up to four
+// ISSUER warps (warp 1 and warps 10..12) feed the tensor pipe: one thread gets a tcgen05.mma out about
+// every 140 cycles (measured: whatever its shape), the pipe takes one of N <= 128 every 60, so the taps
+// of a tile are dealt round-robin to the issuers, which all accumulate into the same accumulator in
+// tensor memory -- the issuer of tap 0 signals (an mbarrier) once its first, initialising instruction is
+// out, the others start after that.  Two accumulators alternate between tiles.  Every wait is bounded.
 //
 // Replaces cudnnConvolutionBiasActivationForward (reference src/ios/ios_runtime.cu:313-331) for these shapes.
 #include "kernels.h"
 #include "tc_device.h"
 
 #include <algorithm>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 namespace ios {
 namespace {
 
-constexpr int kPatchThreads = 320;
+constexpr int kPatchThreads = 416;       // 13 warps: producers, issuer, 8 epilogue / split warps, 3 more issuers
+constexpr int kMaxIssuers = 4;
 
 struct PatchGeom {
     int bn, cchunks, taps, kw, chunk;
@@ -46,6 +53,7 @@ struct PatchGeom {
     int tmem_cols, acc_stride;
     int wide, round_tf32, cout_pad;
     int pad_w, pad_h;
+    int issuers;                      // warps that issue tcgen05.mma: tap i of every chunk belongs to issuer i % issuers
 };
 
 template <int MODE>      // 0: TF32, 1: three-pass TF32, 2: BF16
@@ -68,8 +76,8 @@ conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     const uint32_t bars = b0 + uint32_t(t.b_stages) * b_stage_bytes;
     const uint32_t a_full0 = bars, a_empty0 = a_full0 + 8u * t.a_stages, a_ready0 = a_empty0 + 8u * t.a_stages;
     const uint32_t b_full0 = a_ready0 + 8u * t.a_stages, b_empty0 = b_full0 + 8u * t.b_stages;
-    const uint32_t acc_full0 = b_empty0 + 8u * t.b_stages, acc_empty0 = acc_full0 + 16u;
-    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(generic_base + (acc_empty0 + 16u - smem_base));
+    const uint32_t acc_full0 = b_empty0 + 8u * t.b_stages, acc_empty0 = acc_full0 + 16u, started0 = acc_empty0 + 16u;
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(generic_base + (started0 + 16u - smem_base));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const ConvGeom &g = p.g;
@@ -79,7 +87,7 @@ conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     if (warp == 0) {
         for (int i = lane; i < t.a_stages; i += 32) {
             mbar_init(a_full0 + 8u * i, 1);
-            mbar_init(a_empty0 + 8u * i, 1);
+            mbar_init(a_empty0 + 8u * i, uint32_t(t.issuers));
             mbar_init(a_ready0 + 8u * i, 128);
         }
         for (int i = lane; i < t.b_stages; i += 32) {
@@ -87,8 +95,9 @@ conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             mbar_init(b_empty0 + 8u * i, 1);
         }
         if (lane < 2) {
-            mbar_init(acc_full0 + 8u * lane, 1);
+            mbar_init(acc_full0 + 8u * lane, uint32_t(t.issuers));
             mbar_init(acc_empty0 + 8u * lane, uint32_t(epi_warps));
+            mbar_init(started0 + 8u * lane, 1);
         }
         if (lane == 31) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
@@ -106,7 +115,8 @@ conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    if ((warp == 0 && lane >= 2) || (warp == 1 && lane != 0)) return;
+    const int issuer = warp == 1 ? 0 : warp - 9;          // warps 10, 11, 12 are issuers 1, 2, 3
+    if ((warp == 0 && lane >= 2) || ((warp == 1 || warp >= 10) && (lane != 0 || issuer >= t.issuers))) return;
 
     // tile -> coordinates: output-channel tile fastest, then tiles along w, h, n
     auto decode = [&](int tile, int &cout0, int &ow0, int &oh0, int &n0) {
@@ -140,7 +150,7 @@ conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             }
         }
         if (!ok) {
-            atomicExch(p.error_flag, 1);
+            atomicCAS(p.error_flag, 0, 11);
             // the loads already issued still land here: wait for the latest one of every stage
             for (int j = issued - 1, k = 0; j >= 0 && k < t.a_stages; --j, ++k)
                 mbar_wait(a_full0 + 8u * (j % t.a_stages), uint32_t((j / t.a_stages) & 1), nullptr);
@@ -173,40 +183,54 @@ conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             }
         }
         if (!ok) {
-            atomicExch(p.error_flag, 1);
+            atomicCAS(p.error_flag, 0, 12);
             for (int j = issued - 1, k = 0; j >= 0 && k < t.b_stages; --j, ++k)
                 mbar_wait(b_full0 + 8u * (j % t.b_stages), uint32_t((j / t.b_stages) & 1), nullptr);
         }
         return;
     }
-    if (warp == 1) {
-        // ---------------- MMA issuer ----------------
+    if (warp == 1 || warp >= 10) {
+        // ---------------- MMA issuers: taps issuer, issuer + W, ... of every channel chunk ----------------
+        const int W = t.issuers;
         const uint32_t fmt = kBf16 ? 1u : 2u;
         const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(t.bn >> 3) << 17) | (uint32_t(kTileM >> 4) << 24);
         const uint32_t idesc_wide = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(t.bn >> 2) << 17) | (uint32_t(kTileM >> 4) << 24);
         const uint32_t a_wait0 = kX3 ? a_ready0 : a_full0;
-        int sa = 0, sb = 0;
-        uint32_t pa = 0, pb = 0;
+        int sa = 0;
+        uint32_t pa = 0;
+        long q0 = 0;                    // weight tiles requested before this chunk (ring position of its tap 0)
         bool ok = true;
 #pragma unroll 1
         for (int ti = 0; ti < my_tiles && ok; ++ti) {
             const uint32_t a = uint32_t(ti) & 1u;
-            ok = mbar_wait(acc_empty0 + 8u * a, ((uint32_t(ti) >> 1) & 1u) ^ 1u, p.error_flag);
+            const uint32_t tile_parity = (uint32_t(ti) >> 1) & 1u;
+            // issuer 0 waits until the epilogue has emptied this accumulator; the others until issuer 0 has begun the tile
+            ok = issuer == 0 ? mbar_wait(acc_empty0 + 8u * a, tile_parity ^ 1u, p.error_flag)
+                             : mbar_wait(started0 + 8u * a, tile_parity, p.error_flag);
             if (!ok) break;
             tc_fence_after();
             const uint32_t tmem_d = tmem_base + a * uint32_t(t.acc_stride);
-            uint32_t first = 0u;        // 0 until the tile's first instruction has been issued
+            uint32_t first = issuer == 0 ? 0u : 1u;        // 0 until the tile's initialising instruction is out
 #pragma unroll 1
             for (int cc = 0; cc < t.cchunks && ok; ++cc) {
                 ok = mbar_wait(a_wait0 + 8u * sa, pa, p.error_flag);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t a_hi = a0 + uint32_t(sa) * a_stage_bytes;
-                int r = 0, sx = 0;
+                int r = issuer / t.kw, sx = issuer - r * t.kw;
 #pragma unroll 1
-                for (int tap = 0; tap < t.taps; ++tap) {
-                    const int slot = t.b_resident ? cc * t.taps + tap : sb;
-                    ok = mbar_wait(b_full0 + 8u * slot, t.b_resident ? 0u : pb, p.error_flag);
+                for (int tap = issuer; tap < t.taps; tap += W) {
+                    int slot;
+                    uint32_t pb = 0u;
+                    if (t.b_resident) {
+                        slot = cc * t.taps + tap;
+                    } else {
+                        const long q = q0 + tap;
+                        const long lap = q / t.b_stages;
+                        slot = int(q - lap * t.b_stages);
+                        pb = uint32_t(lap) & 1u;
+                    }
+                    ok = mbar_wait(b_full0 + 8u * slot, pb, p.error_flag);
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t a_tap = a_hi + uint32_t(r * t.pw + sx) * kRow;
@@ -228,21 +252,24 @@ conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                         } else {
                             umma_tf32(tmem_d, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, acc);
                         }
+                        if (k == 0 && first == 0u) {
+                            // the accumulator now holds this instruction's result alone: the other issuers may add to it
+                            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(started0 + 8u * a) : "memory");
+                            first = 1u;
+                        }
                     }
-                    first = 1u;
-                    if (!t.b_resident) {
-                        umma_commit(b_empty0 + 8u * sb);
-                        if (++sb == t.b_stages) { sb = 0; pb ^= 1u; }
-                    }
-                    if (++sx == t.kw) { sx = 0; ++r; }
+                    if (!t.b_resident) umma_commit(b_empty0 + 8u * slot);
+                    sx += W;
+                    while (sx >= t.kw) { sx -= t.kw; ++r; }
                 }
                 if (!ok) break;
-                umma_commit(a_empty0 + 8u * sa);          // the patch is free once these instructions have read it
+                umma_commit(a_empty0 + 8u * sa);          // one arrival per issuer: the patch is free once all have read it
                 if (++sa == t.a_stages) { sa = 0; pa ^= 1u; }
+                q0 += t.taps;
             }
             if (ok) umma_commit(acc_full0 + 8u * a);
         }
-        if (!ok) atomicExch(p.error_flag, 2);
+        if (!ok) atomicCAS(p.error_flag, 0, 20 + issuer);
         return;
     }
     if (kX3 && warp >= 6) {
@@ -255,7 +282,7 @@ conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 #pragma unroll 1
         for (long i = 0; i < steps; ++i) {
             if (!mbar_wait(a_full0 + 8u * s, phase, p.error_flag)) {
-                atomicExch(p.error_flag, 4);
+                atomicCAS(p.error_flag, 0, 50);
                 break;
             }
             uint8_t *stage = generic_base + size_t(s) * a_stage_bytes;
@@ -302,7 +329,7 @@ conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         for (int j = etid; j < t.bn; j += epi_threads) bias[j] = (p.bias && cout0 + j < g.Cout) ? p.bias[cout0 + j] : 0.0f;
         bool ok = mbar_wait(acc_full0 + 8u * a, (uint32_t(ti) >> 1) & 1u, p.error_flag);
         ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
-        if (!ok && lane == 0) atomicExch(p.error_flag, 3);
+        if (!ok && lane == 0) atomicCAS(p.error_flag, 0, 60);
         tc_fence_after();
         asm volatile("bar.sync 1, %0;" ::"r"(epi_threads) : "memory");      // bias complete
         const int valid = min(t.bn, g.Cout - cout0);
@@ -322,10 +349,8 @@ conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                     v[j] = t.round_tf32 ? round_tf32(z) : z;
                 }
 #pragma unroll
-                for (int j = 0; j < 16; j += 4)
-                    if (c + j < valid)
-                        store4_direct(p.out.ptr, kBf16, pix_off + cout0 + c + j, make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]),
-                                      valid - (c + j));
+                for (int j = 0; j < 16; j += 8)
+                    if (c + j < valid) store8_direct(p.out.ptr, kBf16, pix_off + cout0 + c + j, v + j, valid - (c + j));
             }
         }
         // hand the accumulator back to the MMA issuer: one arrival per epilogue warp
@@ -380,9 +405,10 @@ void conv_tc_patch_consider(const ConvGeom &g, int sm_count, ConvTcPlan *plan) {
     const int b_stage = planes * bn * 128;
     // weights that fit stay resident (the first layers of a network: a few dozen KiB)
     const bool b_resident = n_tiles == 1 && taps * cchunks <= 48 && long(taps) * cchunks * b_stage <= 72 * 1024;
-    auto fixed_bytes = [](int as, int bs) { return 1024 + 8 * (3 * as + 2 * bs) + 128; };   // alignment slack, barriers, slot
+    auto fixed_bytes = [](int as, int bs) { return 1024 + 8 * (3 * as + 2 * bs) + 160; };   // alignment slack, barriers, slot
     const double tensor_col = 2.1 * 1.15 * (q.x3 ? 3.0 : 1.0);
-    const double issue_tap = (q.x3 ? (wide ? 8 : 12) : 4) * 50.0 + 60.0;
+    // one thread issues an instruction about every 140 cycles; up to four threads take turns
+    const double issue_tap = ((q.x3 ? (wide ? 8 : 12) : 4) * 140.0 + 60.0) / std::min(kMaxIssuers, taps);
 
     // tile extent: output rows cut into `parts` even segments of box_w pixels, as many rows (and, where a whole
     // image fits, images) as 128 GEMM rows hold beside the halo columns; the cheapest candidate wins
@@ -500,6 +526,7 @@ void launch_conv_tc_patch(const ConvTcParams &p, const ConvTcPlan &q, cudaStream
     t.round_tf32 = g.round_out;
     t.cout_pad = q.cout_pad;
     t.pad_w = g.pw; t.pad_h = g.ph;
+    t.issuers = std::max(1, std::min({kMaxIssuers, t.taps, q.patch_issuers > 0 ? q.patch_issuers : kMaxIssuers}));
     ConvTcParams pp = p;
     if (q.patch_merged) {               // images and rows as one axis (see conv_tc_patch_consider)
         pp.g.H = g.N * g.H; pp.g.OH = g.N * g.OH; pp.g.N = 1;
@@ -519,6 +546,12 @@ void launch_conv_tc_patch(const ConvTcParams &p, const ConvTcPlan &q, cudaStream
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
     const CUtensorMap &ma = *reinterpret_cast<const CUtensorMap *>(q.tmap_a), &mb = *reinterpret_cast<const CUtensorMap *>(q.tmap_b);
+    if (std::getenv("IOS_DEBUG_PATCH"))
+        std::fprintf(stderr, "patch conv: N %d H %d W %d Cin %d Cout %d k %dx%d pad %d,%d | bn %d n_tiles %d cchunks %d box %dx%dx%d patch %dx%d "
+                     "a_rows %d a_stages %d b_stages %d resident_b %d tiles %d grid %u smem %zu tmem %d issuers %d x3 %d bf16 %d merged %d\n",
+                     pp.g.N, pp.g.H, pp.g.W, g.Cin, g.Cout, g.kh, g.kw, g.ph, g.pw, t.bn, t.n_tiles, t.cchunks, t.box_w, t.box_h, t.box_n, t.pw, t.ph,
+                     t.a_rows, t.a_stages, t.b_stages, t.b_resident, t.total_tiles, cfg.gridDim.x, q.smem_bytes, t.tmem_cols, t.issuers, q.x3, q.bf16,
+                     q.patch_merged);
     if (q.x3) cudaLaunchKernelEx(&cfg, conv_tc_patch_kernel<1>, ma, mb, pp, t);
     else if (q.bf16) cudaLaunchKernelEx(&cfg, conv_tc_patch_kernel<2>, ma, mb, pp, t);
     else cudaLaunchKernelEx(&cfg, conv_tc_patch_kernel<0>, ma, mb, pp, t);

