@@ -54,14 +54,16 @@ struct PatchGeom {
     int wide, round_tf32, cout_pad;
     int pad_w, pad_h;
     int issuers;                      // warps that issue tcgen05.mma: tap i of every chunk belongs to issuer i % issuers
+    int b_depth;                      // weight stages per issuer: issuer w owns stages [w * b_depth, (w + 1) * b_depth), so that
+                                      // every stage has ONE consumer, which sees each of its phases (b_stages = issuers * b_depth)
 };
 
-template <int MODE>      // 0: TF32, 1: three-pass TF32, 2: BF16
+template <int MODE>      // 0: TF32, 1: three-pass TF32, 2: BF16, 4: BF16 with 64-byte operand rows (at most 32 input channels)
 __global__ void __launch_bounds__(kPatchThreads, 1)
 conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const ConvTcParams p, const PatchGeom t) {
-    constexpr bool kX3 = MODE == 1, kBf16 = MODE == 2;
-    constexpr int kRow = 128;
+    constexpr bool kX3 = MODE == 1, kBf16 = MODE == 2 || MODE == 4;
+    constexpr int kRow = MODE == 4 ? 64 : 128;           // bytes of K per operand row; 32 bytes of it per instruction
     extern __shared__ uint8_t smem_raw[];
     __shared__ float bias_s[2][256];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -116,8 +118,12 @@ conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     const uint32_t tmem_base = *tmem_slot;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int issuer = warp == 1 ? 0 : warp - 9;          // warps 10, 11, 12 are issuers 1, 2, 3
-    if ((warp == 0 && lane >= 2) || ((warp == 1 || warp >= 10) && (lane != 0 || issuer >= t.issuers))) return;
+    if ((warp == 0 && lane >= 1 + t.issuers) || ((warp == 1 || warp >= 10) && (lane != 0 || issuer >= t.issuers))) return;
 
+    // where a role gave up (read back by the host beside the time-out word): word 1 + role = tile | chunk << 12 | tap << 18 | wait << 26
+    auto gave_up = [&](int role, int ti, int cc, int tap, int wait) {
+        p.error_flag[1 + role] = (ti & 0xFFF) | ((cc & 63) << 12) | ((tap & 255) << 18) | (wait << 26);
+    };
     // tile -> coordinates: output-channel tile fastest, then tiles along w, h, n
     auto decode = [&](int tile, int &cout0, int &ow0, int &oh0, int &n0) {
         const int m_tile = tile / t.n_tiles;
@@ -141,7 +147,7 @@ conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 #pragma unroll 1
             for (int cc = 0; cc < t.cchunks; ++cc) {
                 ok = mbar_wait(a_empty0 + 8u * s, uint32_t(phase), p.error_flag);
-                if (!ok) break;
+                if (!ok) { gave_up(0, ti, cc, 0, 1); break; }
                 const uint32_t bar = a_full0 + 8u * s;
                 mbar_expect_tx(bar, uint32_t(t.a_tx_bytes));
                 tma_load_4d(a0 + uint32_t(s) * a_stage_bytes, &tmap_a, bar, cc * t.chunk, ow0 - t.pad_w, oh0 - t.pad_h, n0);
@@ -158,7 +164,10 @@ conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         return;
     }
     if (warp == 0) {
-        // ---------------- weight tiles: one load per (tile, channel chunk, tap), or once if they stay ----------------
+        // ---------------- weight tiles: lane 1 + w loads the taps of issuer w (w, w + W, ... of every chunk) into that
+        // issuer's ring -- or, when the weights stay resident, once into stage chunk * taps + tap.  One thread gets a load
+        // out every few hundred cycles (wait, arm, issue), so every ring has a lane of its own.
+        const int W = t.issuers, w = lane - 1;
         int s = 0, phase = 1, issued = 0;
         bool ok = true;
         const int rounds = t.b_resident ? 1 : my_tiles;
@@ -169,23 +178,37 @@ conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 #pragma unroll 1
             for (int cc = 0; cc < t.cchunks && ok; ++cc) {
 #pragma unroll 1
-                for (int tap = 0; tap < t.taps; ++tap) {
-                    ok = mbar_wait(b_empty0 + 8u * s, uint32_t(phase), p.error_flag);
-                    if (!ok) break;
-                    const uint32_t bar = b_full0 + 8u * s, dst = b0 + uint32_t(s) * b_stage_bytes;
+                for (int tap = w; tap < t.taps; tap += W) {
+                    int slot;
+                    if (t.b_resident) {
+                        slot = cc * t.taps + tap;
+                    } else {
+                        slot = w * t.b_depth + s;
+                        ok = mbar_wait(b_empty0 + 8u * slot, uint32_t(phase), p.error_flag);
+                        if (!ok) { gave_up(1, ti, cc, tap, 2); break; }
+                        if (++s == t.b_depth) { s = 0; phase ^= 1; }
+                    }
+                    const uint32_t bar = b_full0 + 8u * slot, dst = b0 + uint32_t(slot) * b_stage_bytes;
                     const int kcol = (tap * t.cchunks + cc) * t.chunk;
                     mbar_expect_tx(bar, uint32_t(b_stage_bytes));
                     tma_load_2d(dst, &tmap_b, bar, kcol, cout0);
                     if (kX3) tma_load_2d(dst + uint32_t(b_bytes), &tmap_b, bar, kcol, t.cout_pad + cout0);
                     ++issued;
-                    if (++s == t.b_stages) { s = 0; phase ^= 1; }
                 }
             }
         }
         if (!ok) {
             atomicCAS(p.error_flag, 0, 12);
-            for (int j = issued - 1, k = 0; j >= 0 && k < t.b_stages; --j, ++k)
-                mbar_wait(b_full0 + 8u * (j % t.b_stages), uint32_t((j / t.b_stages) & 1), nullptr);
+            // the loads this lane has issued still land here: wait for the latest one of each of its stages
+            if (!t.b_resident)
+                for (int j = issued - 1, k = 0; j >= 0 && k < t.b_depth; --j, ++k)
+                    mbar_wait(b_full0 + 8u * (w * t.b_depth + j % t.b_depth), uint32_t((j / t.b_depth) & 1), nullptr);
+        }
+        if (t.b_resident && issued > 0) {
+            // (resident stages are waited for by the issuers; on a failure elsewhere this lane still owes the CTA the
+            //  arrival of what it asked for before the shared memory may be given up)
+            for (int cc = 0; cc < t.cchunks; ++cc)
+                for (int tap = w; tap < t.taps; tap += W) mbar_wait(b_full0 + 8u * (cc * t.taps + tap), 0u, nullptr);
         }
         return;
     }
@@ -196,9 +219,8 @@ conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(t.bn >> 3) << 17) | (uint32_t(kTileM >> 4) << 24);
         const uint32_t idesc_wide = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(t.bn >> 2) << 17) | (uint32_t(kTileM >> 4) << 24);
         const uint32_t a_wait0 = kX3 ? a_ready0 : a_full0;
-        int sa = 0;
-        uint32_t pa = 0;
-        long q0 = 0;                    // weight tiles requested before this chunk (ring position of its tap 0)
+        int sa = 0, sb = 0;
+        uint32_t pa = 0, pb = 0;
         bool ok = true;
 #pragma unroll 1
         for (int ti = 0; ti < my_tiles && ok; ++ti) {
@@ -207,38 +229,30 @@ conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             // issuer 0 waits until the epilogue has emptied this accumulator; the others until issuer 0 has begun the tile
             ok = issuer == 0 ? mbar_wait(acc_empty0 + 8u * a, tile_parity ^ 1u, p.error_flag)
                              : mbar_wait(started0 + 8u * a, tile_parity, p.error_flag);
-            if (!ok) break;
+            if (!ok) { gave_up(2 + issuer, ti, 0, 0, 3); break; }
             tc_fence_after();
             const uint32_t tmem_d = tmem_base + a * uint32_t(t.acc_stride);
             uint32_t first = issuer == 0 ? 0u : 1u;        // 0 until the tile's initialising instruction is out
 #pragma unroll 1
             for (int cc = 0; cc < t.cchunks && ok; ++cc) {
                 ok = mbar_wait(a_wait0 + 8u * sa, pa, p.error_flag);
-                if (!ok) break;
+                if (!ok) { gave_up(2 + issuer, ti, cc, 0, 4); break; }
                 tc_fence_after();
                 const uint32_t a_hi = a0 + uint32_t(sa) * a_stage_bytes;
                 int r = issuer / t.kw, sx = issuer - r * t.kw;
 #pragma unroll 1
                 for (int tap = issuer; tap < t.taps; tap += W) {
-                    int slot;
-                    uint32_t pb = 0u;
-                    if (t.b_resident) {
-                        slot = cc * t.taps + tap;
-                    } else {
-                        const long q = q0 + tap;
-                        const long lap = q / t.b_stages;
-                        slot = int(q - lap * t.b_stages);
-                        pb = uint32_t(lap) & 1u;
-                    }
-                    ok = mbar_wait(b_full0 + 8u * slot, pb, p.error_flag);
-                    if (!ok) break;
+                    // resident weights: a stage per (chunk, tap), filled once; else this issuer's own ring
+                    const int slot = t.b_resident ? cc * t.taps + tap : issuer * t.b_depth + sb;
+                    ok = mbar_wait(b_full0 + 8u * slot, t.b_resident ? 0u : pb, p.error_flag);
+                    if (!ok) { gave_up(2 + issuer, ti, cc, tap, 5); break; }
                     tc_fence_after();
                     const uint32_t a_tap = a_hi + uint32_t(r * t.pw + sx) * kRow;
                     const uint64_t da = smem_desc_kmajor(a_tap, kRow), dal = smem_desc_kmajor(a_tap + uint32_t(a_plane), kRow);
                     const uint32_t b_hi = b0 + uint32_t(slot) * b_stage_bytes;
                     const uint64_t db = smem_desc_kmajor(b_hi, kRow), dbl = smem_desc_kmajor(b_hi + uint32_t(b_bytes), kRow);
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
+                    for (int k = 0; k < kRow / 32; ++k) {
                         const uint32_t acc = first | (k > 0 ? 1u : 0u);
                         if (kX3 && t.wide) {
                             umma_tf32(tmem_d, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc_wide, acc);
@@ -258,14 +272,16 @@ conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                             first = 1u;
                         }
                     }
-                    if (!t.b_resident) umma_commit(b_empty0 + 8u * slot);
+                    if (!t.b_resident) {
+                        umma_commit(b_empty0 + 8u * slot);
+                        if (++sb == t.b_depth) { sb = 0; pb ^= 1u; }
+                    }
                     sx += W;
                     while (sx >= t.kw) { sx -= t.kw; ++r; }
                 }
                 if (!ok) break;
                 umma_commit(a_empty0 + 8u * sa);          // one arrival per issuer: the patch is free once all have read it
                 if (++sa == t.a_stages) { sa = 0; pa ^= 1u; }
-                q0 += t.taps;
             }
             if (ok) umma_commit(acc_full0 + 8u * a);
         }
@@ -329,7 +345,10 @@ conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         for (int j = etid; j < t.bn; j += epi_threads) bias[j] = (p.bias && cout0 + j < g.Cout) ? p.bias[cout0 + j] : 0.0f;
         bool ok = mbar_wait(acc_full0 + 8u * a, (uint32_t(ti) >> 1) & 1u, p.error_flag);
         ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
-        if (!ok && lane == 0) atomicCAS(p.error_flag, 0, 60);
+        if (!ok && lane == 0) {
+            atomicCAS(p.error_flag, 0, 60);
+            if (warp == 2) gave_up(7, ti, 0, 0, 6);
+        }
         tc_fence_after();
         asm volatile("bar.sync 1, %0;" ::"r"(epi_threads) : "memory");      // bias complete
         const int valid = min(t.bn, g.Cout - cout0);
@@ -375,7 +394,7 @@ int ceil_div_i(int a, int b) { return (a + b - 1) / b; }
 
 // Cycles the TMA unit of an SM spends on a load of `rows` rows of 128 bytes (measured on B200: a layer
 // bound by its loads takes about 1.15 cycles per row plus one cycle per 100 bytes, whatever the mode).
-double tma_cycles(double rows) { return rows * 1.15 + rows * 128.0 / 100.0; }
+double tma_cycles(double rows, int row_bytes) { return rows * 1.15 + rows * row_bytes / 100.0; }
 
 }  // namespace
 
@@ -400,19 +419,20 @@ void conv_tc_patch_consider(const ConvGeom &g, int sm_count, ConvTcPlan *plan) {
     const int acc_cols = (wide ? 2 : 1) * ceil_div_i(bn, 32) * 32;
     if (2 * acc_cols > 512) return;
     const int planes = q.x3 ? 2 : 1;
-    const int chunk = q.bf16 ? 64 : 32;
+    const int row = q.half_rows ? 64 : 128;              // bfloat16 layers of at most 32 input channels: 64-byte operand rows
+    const int chunk = q.bf16 ? (q.half_rows ? 32 : 64) : 32;
     const int cchunks = ceil_div_i(g.Cin, chunk);
-    const int b_stage = planes * bn * 128;
+    const int b_stage = planes * bn * row;
     // weights that fit stay resident (the first layers of a network: a few dozen KiB)
     const bool b_resident = n_tiles == 1 && taps * cchunks <= 48 && long(taps) * cchunks * b_stage <= 72 * 1024;
     auto fixed_bytes = [](int as, int bs) { return 1024 + 8 * (3 * as + 2 * bs) + 160; };   // alignment slack, barriers, slot
     const double tensor_col = 2.1 * 1.15 * (q.x3 ? 3.0 : 1.0);
     // one thread issues an instruction about every 140 cycles; up to four threads take turns
-    const double issue_tap = ((q.x3 ? (wide ? 8 : 12) : 4) * 140.0 + 60.0) / std::min(kMaxIssuers, taps);
+    const double issue_one = (q.x3 ? (wide ? 8 : 12) : row / 32) * 140.0 + 60.0;
 
     // tile extent: output rows cut into `parts` even segments of box_w pixels, as many rows (and, where a whole
     // image fits, images) as 128 GEMM rows hold beside the halo columns; the cheapest candidate wins
-    struct Cand { int box_w, box_h, box_n, pw, ph, a_rows, tiles_w, tiles_h, tiles_n, resident, a_stages, b_stages; double cost; };
+    struct Cand { int box_w, box_h, box_n, pw, ph, a_rows, tiles_w, tiles_h, tiles_n, resident, a_stages, b_stages, issuers, b_depth; double cost; };
     Cand best = {};
     best.cost = 1e30;
     const int min_parts = ceil_div_i(g.OW, kTileM - g.kw + 1);
@@ -437,44 +457,54 @@ void conv_tc_patch_consider(const ConvGeom &g, int sm_count, ConvTcPlan *plan) {
         c.tiles_n = ceil_div_i(Nm, c.box_n);
         const long m_tiles = long(c.tiles_w) * c.tiles_h * c.tiles_n;
         if (m_tiles * n_tiles > (1l << 24)) continue;
-        const int a_stage = planes * c.a_rows * 128;
+        const int a_stage = planes * c.a_rows * row;
+        // issuing warps: as many as there are taps, up to four (or the cap of the testing aid); when the weights are not
+        // resident every issuer has a ring of its own of at least two stages, so fewer issuers where memory is short
+        const int w_max = std::max(1, std::min({kMaxIssuers, taps, q.max_issuers > 0 ? q.max_issuers : kMaxIssuers}));
         for (int want = 2; want >= 1 && !c.resident; --want) {
             if (want == 2 && 4 * acc_cols > 512) continue;
-            const int bs_min = b_resident ? taps * cchunks : 3;
             const int as_min = (cchunks > 1 || m_tiles * n_tiles > long(sm_count) * want) ? 2 : 1;
             const int budget = (want == 2 ? 110 : 210) * 1024;
-            if (as_min * a_stage + bs_min * b_stage + fixed_bytes(as_min, bs_min) > budget) continue;
-            c.resident = want;
-            c.b_stages = bs_min;
-            c.a_stages = as_min;
-            while (c.a_stages < 3 && (c.a_stages + 1) * a_stage + c.b_stages * b_stage + fixed_bytes(c.a_stages + 1, c.b_stages) <= budget)
-                ++c.a_stages;
-            while (!b_resident && c.b_stages < 8 &&
-                   c.a_stages * a_stage + (c.b_stages + 1) * b_stage + fixed_bytes(c.a_stages, c.b_stages + 1) <= budget)
-                ++c.b_stages;
+            for (int w = w_max; w >= 1 && !c.resident; --w) {
+                const int bs_min = b_resident ? taps * cchunks : (w == 1 ? 3 : 2 * w);
+                if (as_min * a_stage + bs_min * b_stage + fixed_bytes(as_min, bs_min) > budget) continue;
+                c.resident = want;
+                c.issuers = w;
+                c.a_stages = as_min;
+                c.b_depth = b_resident ? 1 : bs_min / w;
+                c.b_stages = bs_min;
+                while (c.a_stages < 3 && (c.a_stages + 1) * a_stage + c.b_stages * b_stage + fixed_bytes(c.a_stages + 1, c.b_stages) <= budget)
+                    ++c.a_stages;
+                while (!b_resident && c.b_depth < 4 &&
+                       c.a_stages * a_stage + (c.b_depth + 1) * w * b_stage + fixed_bytes(c.a_stages, (c.b_depth + 1) * w) <= budget) {
+                    ++c.b_depth;
+                    c.b_stages = c.b_depth * w;
+                }
+            }
         }
         if (!c.resident) continue;
         // per SM: the TMA unit serves the resident CTAs in turn, the tensor pipe too, the issuing threads work side by side
-        const double chunk_cycles = std::max({tma_cycles(patch_rows) + (b_resident ? 0.0 : tma_cycles(double(taps) * bn * planes)),
-                                              taps * bn * tensor_col, taps * issue_tap / c.resident});
+        const double chunk_cycles = std::max({tma_cycles(patch_rows, row) + (b_resident ? 0.0 : tma_cycles(double(taps) * bn * planes, row)),
+                                              taps * bn * tensor_col, taps * issue_one / c.issuers / c.resident});
         c.cost = double(m_tiles) * n_tiles * (cchunks * chunk_cycles + 400.0);
         if (c.cost < best.cost) best = c;
     }
     if (best.cost >= 1e30) return;
     // compare with what the plan has now (an activation tile per tap)
     const long old_tiles = (long(g.N) * g.OH * g.OW + kTileM - 1) / kTileM * q.n_tiles;
-    const double old_step = std::max({tma_cycles(kTileM + double(q.bn) * planes), q.bn * tensor_col, (q.x3 ? 700.0 : 450.0) / 2.0});
+    const double old_step = std::max({tma_cycles(kTileM + double(q.bn) * planes, row), q.bn * tensor_col, (q.x3 ? 700.0 : 450.0) / 2.0});
     const double old_cost = double(old_tiles) * (double(taps) * q.cchunks * old_step + 400.0);
     if (best.cost > 0.92 * old_cost) return;
     const int box_w = best.box_w, box_h = best.box_h, box_n = best.box_n, pw = best.pw, ph = best.ph, a_rows = best.a_rows;
     const int tiles_w = best.tiles_w, tiles_h = best.tiles_h, tiles_n = best.tiles_n;
     const int resident = best.resident, a_stages = best.a_stages, b_stages = best.b_stages;
+    q.patch_issuers = best.issuers;
+    q.patch_b_depth = best.b_depth;
     const long m_tiles = long(tiles_w) * tiles_h * tiles_n;
-    const int a_stage = planes * a_rows * 128;
+    const int a_stage = planes * a_rows * row;
     const int fixed = fixed_bytes(a_stages, b_stages);
 
     q.patch = 1;
-    q.half_rows = 0;
     q.cchunks = cchunks;
     q.k_iters = taps * cchunks;
     q.bn = bn;
@@ -499,7 +529,7 @@ void conv_tc_patch_consider(const ConvGeom &g, int sm_count, ConvTcPlan *plan) {
 
 cudaError_t conv_tc_patch_prepare() {
     const void *forms[] = {reinterpret_cast<const void *>(conv_tc_patch_kernel<0>), reinterpret_cast<const void *>(conv_tc_patch_kernel<1>),
-                           reinterpret_cast<const void *>(conv_tc_patch_kernel<2>)};
+                           reinterpret_cast<const void *>(conv_tc_patch_kernel<2>), reinterpret_cast<const void *>(conv_tc_patch_kernel<4>)};
     for (const void *form : forms) {
         cudaError_t err = cudaFuncSetAttribute(form, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024);
         if (err != cudaSuccess) return err;
@@ -510,13 +540,14 @@ cudaError_t conv_tc_patch_prepare() {
 void launch_conv_tc_patch(const ConvTcParams &p, const ConvTcPlan &q, cudaStream_t stream) {
     PatchGeom t;
     const ConvGeom &g = p.g;
-    t.bn = q.bn; t.cchunks = q.cchunks; t.taps = g.kh * g.kw; t.kw = g.kw; t.chunk = q.bf16 ? 64 : 32;
+    const int row = q.half_rows ? 64 : 128;
+    t.bn = q.bn; t.cchunks = q.cchunks; t.taps = g.kh * g.kw; t.kw = g.kw; t.chunk = q.bf16 ? (q.half_rows ? 32 : 64) : 32;
     t.pw = q.patch_pw; t.ph = q.patch_ph;
     t.box_w = q.box_w; t.box_h = q.box_h; t.box_n = q.box_n;
     t.tiles_w = q.tiles_w; t.tiles_h = q.tiles_h; t.n_tiles = q.n_tiles;
     t.total_tiles = q.tiles_w * q.tiles_h * q.tiles_n * q.n_tiles;
     t.a_rows = q.patch_a_rows; t.a_stages = q.patch_a_stages; t.b_stages = q.patch_b_stages;
-    t.a_tx_bytes = q.patch_pw * q.patch_ph * q.box_n * 128;
+    t.a_tx_bytes = q.patch_pw * q.patch_ph * q.box_n * row;
     t.b_resident = q.patch_b_resident;
     t.wide = (q.x3 && q.bn <= 128) ? 1 : 0;
     t.acc_stride = (t.wide ? 2 : 1) * ceil_div_i(q.bn, 32) * 32;
@@ -526,7 +557,8 @@ void launch_conv_tc_patch(const ConvTcParams &p, const ConvTcPlan &q, cudaStream
     t.round_tf32 = g.round_out;
     t.cout_pad = q.cout_pad;
     t.pad_w = g.pw; t.pad_h = g.ph;
-    t.issuers = std::max(1, std::min({kMaxIssuers, t.taps, q.patch_issuers > 0 ? q.patch_issuers : kMaxIssuers}));
+    t.issuers = q.patch_issuers;
+    t.b_depth = q.patch_b_depth;
     ConvTcParams pp = p;
     if (q.patch_merged) {               // images and rows as one axis (see conv_tc_patch_consider)
         pp.g.H = g.N * g.H; pp.g.OH = g.N * g.OH; pp.g.N = 1;
@@ -548,11 +580,12 @@ void launch_conv_tc_patch(const ConvTcParams &p, const ConvTcPlan &q, cudaStream
     const CUtensorMap &ma = *reinterpret_cast<const CUtensorMap *>(q.tmap_a), &mb = *reinterpret_cast<const CUtensorMap *>(q.tmap_b);
     if (std::getenv("IOS_DEBUG_PATCH"))
         std::fprintf(stderr, "patch conv: N %d H %d W %d Cin %d Cout %d k %dx%d pad %d,%d | bn %d n_tiles %d cchunks %d box %dx%dx%d patch %dx%d "
-                     "a_rows %d a_stages %d b_stages %d resident_b %d tiles %d grid %u smem %zu tmem %d issuers %d x3 %d bf16 %d merged %d\n",
+                     "a_rows %d a_stages %d b_stages %d resident_b %d tiles %d grid %u smem %zu tmem %d issuers %d depth %d x3 %d bf16 %d merged %d\n",
                      pp.g.N, pp.g.H, pp.g.W, g.Cin, g.Cout, g.kh, g.kw, g.ph, g.pw, t.bn, t.n_tiles, t.cchunks, t.box_w, t.box_h, t.box_n, t.pw, t.ph,
-                     t.a_rows, t.a_stages, t.b_stages, t.b_resident, t.total_tiles, cfg.gridDim.x, q.smem_bytes, t.tmem_cols, t.issuers, q.x3, q.bf16,
+                     t.a_rows, t.a_stages, t.b_stages, t.b_resident, t.total_tiles, cfg.gridDim.x, q.smem_bytes, t.tmem_cols, t.issuers, t.b_depth, q.x3, q.bf16,
                      q.patch_merged);
     if (q.x3) cudaLaunchKernelEx(&cfg, conv_tc_patch_kernel<1>, ma, mb, pp, t);
+    else if (q.bf16 && q.half_rows) cudaLaunchKernelEx(&cfg, conv_tc_patch_kernel<4>, ma, mb, pp, t);
     else if (q.bf16) cudaLaunchKernelEx(&cfg, conv_tc_patch_kernel<2>, ma, mb, pp, t);
     else cudaLaunchKernelEx(&cfg, conv_tc_patch_kernel<0>, ma, mb, pp, t);
 }

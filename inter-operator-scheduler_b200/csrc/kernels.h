@@ -145,7 +145,9 @@ struct ConvTcPlan {
     int patch_a_stages, patch_b_stages;
     int patch_b_resident;          // 1: the packed weights are loaded once per CTA and stay in shared memory
     int patch_merged;              // 1: one-row windows: images and rows are one axis
-    int patch_issuers;             // testing aid: cap on the warps that issue tcgen05.mma (0: the default, 4)
+    int patch_issuers;             // warps that issue tcgen05.mma (1..4)
+    int patch_b_depth;             // weight stages per issuer (every issuer has a ring of its own)
+    int max_issuers;               // testing aid: cap on patch_issuers (0: none)
     alignas(64) unsigned char tmap_a[128];   // CUtensorMap over the input view
     alignas(64) unsigned char tmap_b[128];   // CUtensorMap over the packed weights
     alignas(64) unsigned char tmap_c[128];   // CUtensorMap over the output window (when tma_store)

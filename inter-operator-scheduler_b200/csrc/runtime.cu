@@ -371,10 +371,19 @@ void check_error_flag(const Plan &plan, char *base) {
     int flag = 0;
     CUDA_OK(cudaMemcpy(&flag, base + plan.error_flag_offset, sizeof flag, cudaMemcpyDeviceToHost));
     if (flag != 0) {
-        CUDA_OK(cudaMemset(base + plan.error_flag_offset, 0, sizeof(int)));
+        int where[16] = {0};
+        CUDA_OK(cudaMemcpy(where, base + plan.error_flag_offset, sizeof where, cudaMemcpyDeviceToHost));
+        std::string detail;
+        static const char *roles[] = {"patch loads", "weight loads", "issuer 0", "issuer 1", "issuer 2", "issuer 3", "split", "epilogue"};
+        for (int r = 0; r < 8; ++r)
+            if (where[1 + r])
+                detail += std::string("; ") + roles[r] + " gave up at tile " + std::to_string(where[1 + r] & 0xFFF) + " chunk " +
+                          std::to_string((where[1 + r] >> 12) & 63) + " tap " + std::to_string((where[1 + r] >> 18) & 255) + " wait " +
+                          std::to_string((where[1 + r] >> 26) & 31);
+        CUDA_OK(cudaMemset(base + plan.error_flag_offset, 0, 64));
         // a CTA that gave up never reached its tile's arrival counter: start the next run from zero again
         if (plan.zero_bytes) CUDA_OK(cudaMemset(base + plan.zero_begin, 0, plan.zero_bytes));
-        throw TimeoutError("a bounded wait inside the convolution kernel ran out (code " + std::to_string(flag) + ")");
+        throw TimeoutError("a bounded wait inside the convolution kernel ran out (code " + std::to_string(flag) + ")" + detail);
     }
 }
 

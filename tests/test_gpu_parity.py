@@ -117,6 +117,8 @@ PATCH_SHAPES = [
     (16, 64, 30, 31, 72, 1, 3, 1, 1, 0, 1, 1),      # 1x3
     (16, 64, 30, 31, 72, 3, 1, 1, 1, 1, 0, 1),      # 3x1
     (12, 80, 73, 73, 192, 3, 3, 1, 1, 0, 0, 1),     # Inception stem 80 -> 192
+    (64, 48, 35, 35, 64, 5, 5, 1, 1, 2, 2, 1),      # several tiles per CTA, 25 taps dealt to four issuers, weights streamed
+    (40, 96, 35, 35, 96, 3, 3, 1, 1, 1, 1, 1),      # the same with two channel chunks
 ]
 
 
