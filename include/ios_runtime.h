@@ -88,6 +88,10 @@ IOS_API const char *ios_last_error(void);
  * "im2col" "1"/"0" (pixel tiles over the flattened pixel axis by im2col-mode loads / boxes of the image),
  * "stem" "1"/"0" (a convolution over at most 4 input channels runs on CUDA cores / on the tensor cores like the rest),
  * "half_rows" "1"/"0" (bfloat16 layers of at most 32 input channels use 64-byte / 128-byte operand rows),
+ * "patch" "1"/"0"/"all" (stride-1 windows over many tiles whose packed weights fit in shared memory load one input patch per
+ * tile and read every tap from it / never / also layers that stream their weights), "patch_store" "direct"/"bulk"
+ * (finished patch tiles leave from registers / through one bulk tensor store per row segment), "issuers" (cap on the
+ * warps that issue tcgen05.mma in the patch convolution),
  * "persistent" "1"/"0" (grids of several waves run as resident CTAs that walk the tiles / one CTA per tile),
  * "bulk_store" "1"/"0" (results leave through a bulk tensor store / straight from registers),
  * "split_k", "bn", "stages", "producers" (a positive number overrides the K split, the output-channel tile

@@ -1275,9 +1275,21 @@ const char *conv_tc_encode(const ConvTcParams &p, ConvTcPlan *plan) {
     // and a window whose end is 16-byte aligned too, so that clipping never lands inside a 16-byte unit
     const int per16 = int(16 / esize);
     q.tma_store = ((reinterpret_cast<uintptr_t>(p.out.ptr) & 15) == 0 && p.out.pitch % per16 == 0 && g.Cout % per16 == 0) ? 1 : 0;
-    if (q.patch) q.tma_store = 0;          // a patch tile's valid rows are not a box: they are stored from registers
+    if (q.patch && !q.patch_staging) q.tma_store = 0;   // (tiles of many short row segments are stored from registers)
     std::memcpy(q.tmap_c, q.tmap_a, sizeof q.tmap_c);
-    if (q.tma_store) {
+    if (q.tma_store && q.patch) {
+        // one store per output row segment of a patch tile: a box of box_w pixels of one row, 128 bytes of channels
+        const cuuint64_t rows = q.patch_merged ? cuuint64_t(g.N) * g.OH : cuuint64_t(g.OH);
+        const cuuint64_t pix_bytes = cuuint64_t(p.out.pitch) * esize;
+        cuuint64_t dims[4] = {cuuint64_t(g.Cout), cuuint64_t(g.OW), rows, q.patch_merged ? 1 : cuuint64_t(g.N)};
+        cuuint64_t strides[3] = {pix_bytes, pix_bytes * g.OW, pix_bytes * g.OW * rows};
+        cuuint32_t box[4] = {slab, cuuint32_t(q.box_w), 1, 1};
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        CUresult r = encode(reinterpret_cast<CUtensorMap *>(q.tmap_c), dtype, 4, p.out.ptr, dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail("output, row segments", r);
+    } else if (q.tma_store) {
         cuuint64_t dims[4];
         cuuint64_t strides[3];
         cuuint32_t box[4];

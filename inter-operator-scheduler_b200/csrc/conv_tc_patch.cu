@@ -54,6 +54,8 @@ struct PatchGeom {
     int wide, round_tf32, cout_pad;
     int pad_w, pad_h;
     int issuers;                      // warps that issue tcgen05.mma: tap i of every chunk belongs to issuer i % issuers
+    int tma_store;                    // 1: finished tiles leave through bulk tensor stores, one per output row segment
+    int slab;                         // output channels per 128-byte staging row: 32 (float32) or 64 (bfloat16)
     int b_depth;                      // weight stages per issuer: issuer w owns stages [w * b_depth, (w + 1) * b_depth), so that
                                       // every stage has ONE consumer, which sees each of its phases (b_stages = issuers * b_depth)
 };
@@ -61,7 +63,7 @@ struct PatchGeom {
 template <int MODE>      // 0: TF32, 1: three-pass TF32, 2: BF16, 4: BF16 with 64-byte operand rows (at most 32 input channels)
 __global__ void __launch_bounds__(kPatchThreads, 1)
 conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                     const ConvTcParams p, const PatchGeom t) {
+                     const __grid_constant__ CUtensorMap tmap_c, const ConvTcParams p, const PatchGeom t) {
     constexpr bool kX3 = MODE == 1, kBf16 = MODE == 2 || MODE == 4;
     constexpr int kRow = MODE == 4 ? 64 : 128;           // bytes of K per operand row; 32 bytes of it per instruction
     extern __shared__ uint8_t smem_raw[];
@@ -75,7 +77,11 @@ conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     const int b_stage_bytes = planes * b_bytes;
     const uint32_t a0 = smem_base;
     const uint32_t b0 = a0 + uint32_t(t.a_stages) * a_stage_bytes;
-    const uint32_t bars = b0 + uint32_t(t.b_stages) * b_stage_bytes;
+    // store staging: [slab][128 rows][128 B], swizzled like a TMA box; pw is a multiple of 8, so that every output row
+    // segment of a tile starts on a 1024-byte boundary of it
+    const int slabs = (t.bn + t.slab - 1) / t.slab;
+    const uint32_t staging0 = b0 + uint32_t(t.b_stages) * b_stage_bytes;
+    const uint32_t bars = staging0 + (t.tma_store ? uint32_t(slabs) * kATileBytes : 0u);
     const uint32_t a_full0 = bars, a_empty0 = a_full0 + 8u * t.a_stages, a_ready0 = a_empty0 + 8u * t.a_stages;
     const uint32_t b_full0 = a_ready0 + 8u * t.a_stages, b_empty0 = b_full0 + 8u * t.b_stages;
     const uint32_t acc_full0 = b_empty0 + 8u * t.b_stages, acc_empty0 = acc_full0 + 16u, started0 = acc_empty0 + 16u;
@@ -104,6 +110,7 @@ conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         if (lane == 31) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
+            if (t.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_c) : "memory");
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -335,6 +342,7 @@ conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     const int rem = row - img * per_image;
     const int ry = rem / t.pw, rx = rem - ry * t.pw;
     const bool row_in_box = img < t.box_n && ry < t.box_h && rx < t.box_w;
+    uint8_t *staging = generic_base + (staging0 - smem_base);
     asm volatile("griddepcontrol.wait;" ::: "memory");   // the output window may still be read by the previous kernel
 #pragma unroll 1
     for (int ti = 0; ti < my_tiles; ++ti) {
@@ -350,7 +358,9 @@ conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             if (warp == 2) gave_up(7, ti, 0, 0, 6);
         }
         tc_fence_after();
-        asm volatile("bar.sync 1, %0;" ::"r"(epi_threads) : "memory");      // bias complete
+        // the bulk stores of the previous tile must have read the staging area before it is written again
+        if (t.tma_store && etid == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"r"(epi_threads) : "memory");      // bias complete, staging free
         const int valid = min(t.bn, g.Cout - cout0);
         const int n = n0 + img, oh = oh0 + ry, ow = ow0 + rx;
         const bool live = ok && row_in_box && n < g.N && oh < g.OH && ow < g.OW;
@@ -361,22 +371,43 @@ conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             for (int c = c_begin; c < c_end; c += 16) {
                 float v[16];
                 acc_ld16(taddr + c, pair, v);              // (a warp-wide instruction: every lane takes part)
-                if (!live || c >= valid) continue;
+                if (!t.tma_store && (!live || c >= valid)) continue;
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const float z = act_apply(v[j] + bias[c + j], g.act);
                     v[j] = t.round_tf32 ? round_tf32(z) : z;
+                }
+                if (t.tma_store) {
+                    // every row is staged, halo rows too: the stores below pick the row segments that are output
+#pragma unroll
+                    for (int j = 0; j < 16; j += 4)
+                        stage4(staging, row, c + j, make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]), kBf16);
+                    continue;
                 }
 #pragma unroll
                 for (int j = 0; j < 16; j += 8)
                     if (c + j < valid) store8_direct(p.out.ptr, kBf16, pix_off + cout0 + c + j, v + j, valid - (c + j));
             }
         }
-        // hand the accumulator back to the MMA issuer: one arrival per epilogue warp
+        // hand the accumulator back to the MMA issuers: one arrival per epilogue warp
         tc_fence_before();
         __syncwarp();
         if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty0 + 8u * a) : "memory");
+        if (t.tma_store) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("bar.sync 1, %0;" ::"r"(epi_threads) : "memory");  // the tile is staged
+            if (ok && etid == 0) {
+                for (int c = 0; c < valid; c += t.slab) {
+                    const uint32_t slab_base = staging0 + uint32_t(c / t.slab) * kATileBytes;
+                    for (int i = 0; i < t.box_n && n0 + i < g.N; ++i)
+                        for (int y = 0; y < t.box_h && oh0 + y < g.OH; ++y)
+                            tma_store_4d(&tmap_c, slab_base + uint32_t((i * t.ph + y) * t.pw) * 128u, cout0 + c, ow0, oh0 + y, n0 + i);
+                }
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+        }
     }
+    if (t.tma_store && etid == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
     tc_fence_before();
     asm volatile("bar.sync 1, %0;" ::"r"(epi_threads) : "memory");
     if (warp == 2) {
@@ -432,14 +463,16 @@ void conv_tc_patch_consider(const ConvGeom &g, int sm_count, ConvTcPlan *plan) {
 
     // tile extent: output rows cut into `parts` even segments of box_w pixels, as many rows (and, where a whole
     // image fits, images) as 128 GEMM rows hold beside the halo columns; the cheapest candidate wins
-    struct Cand { int box_w, box_h, box_n, pw, ph, a_rows, tiles_w, tiles_h, tiles_n, resident, a_stages, b_stages, issuers, b_depth; double cost; };
+    struct Cand { int box_w, box_h, box_n, pw, ph, a_rows, tiles_w, tiles_h, tiles_n, resident, a_stages, b_stages, issuers, b_depth, staging; double cost; };
+    const int slab_channels = q.bf16 ? 64 : 32;
+    const int staging_bytes = ceil_div_i(bn, slab_channels) * kATileBytes;
     Cand best = {};
     best.cost = 1e30;
     const int min_parts = ceil_div_i(g.OW, kTileM - g.kw + 1);
     for (int parts = min_parts; parts < min_parts + 8 && parts <= g.OW; ++parts) {
         Cand c = {};
         c.box_w = ceil_div_i(g.OW, parts);
-        c.pw = c.box_w + g.kw - 1;
+        c.pw = (c.box_w + g.kw - 1 + 7) / 8 * 8;        // a multiple of 8: output row segments start on whole swizzle atoms
         c.box_h = std::min(OHm, (kTileM - c.box_w) / c.pw + 1);
         c.box_h = ceil_div_i(OHm, ceil_div_i(OHm, c.box_h));
         c.ph = c.box_h + g.kh - 1;
@@ -451,13 +484,18 @@ void conv_tc_patch_consider(const ConvGeom &g, int sm_count, ConvTcPlan *plan) {
         if (c.pw > 256 || c.ph > 256 || c.box_n > 256) continue;
         const int patch_rows = c.box_n * c.ph * c.pw;
         const int max_off = (g.kh - 1) * c.pw + g.kw - 1;
-        c.a_rows = (std::max(patch_rows, kTileM + max_off) + 7) / 8 * 8;
+        c.a_rows = (std::max(patch_rows, kTileM + max_off) + 15) / 16 * 16;      // whole 1024-byte units also with 64-byte rows
         c.tiles_w = ceil_div_i(g.OW, c.box_w);
         c.tiles_h = ceil_div_i(OHm, c.box_h);
         c.tiles_n = ceil_div_i(Nm, c.box_n);
         const long m_tiles = long(c.tiles_w) * c.tiles_h * c.tiles_n;
         if (m_tiles * n_tiles > (1l << 24)) continue;
         const int a_stage = planes * c.a_rows * row;
+        // finished tiles leave through one bulk tensor store per output row segment and 128-byte channel slab, staged in
+        // shared memory -- unless a tile has so many short segments (small images) that plain stores are cheaper
+        // (measured on B200: with the patch loads queued ahead of them in the same TMA unit these small stores are
+        //  slower than 16-byte stores from registers for most layers, so they are a testing aid, off by default)
+        c.staging = (q.patch_bulk_store && ceil_div_i(bn, slab_channels) * c.box_h * c.box_n <= 16) ? staging_bytes : 0;
         // issuing warps: as many as there are taps, up to four (or the cap of the testing aid); when the weights are not
         // resident every issuer has a ring of its own of at least two stages, so fewer issuers where memory is short
         const int w_max = std::max(1, std::min({kMaxIssuers, taps, q.max_issuers > 0 ? q.max_issuers : kMaxIssuers}));
@@ -467,16 +505,17 @@ void conv_tc_patch_consider(const ConvGeom &g, int sm_count, ConvTcPlan *plan) {
             const int budget = (want == 2 ? 110 : 210) * 1024;
             for (int w = w_max; w >= 1 && !c.resident; --w) {
                 const int bs_min = b_resident ? taps * cchunks : (w == 1 ? 3 : 2 * w);
-                if (as_min * a_stage + bs_min * b_stage + fixed_bytes(as_min, bs_min) > budget) continue;
+                if (as_min * a_stage + bs_min * b_stage + c.staging + fixed_bytes(as_min, bs_min) > budget) continue;
                 c.resident = want;
                 c.issuers = w;
                 c.a_stages = as_min;
                 c.b_depth = b_resident ? 1 : bs_min / w;
                 c.b_stages = bs_min;
-                while (c.a_stages < 3 && (c.a_stages + 1) * a_stage + c.b_stages * b_stage + fixed_bytes(c.a_stages + 1, c.b_stages) <= budget)
+                while (c.a_stages < 3 &&
+                       (c.a_stages + 1) * a_stage + c.b_stages * b_stage + c.staging + fixed_bytes(c.a_stages + 1, c.b_stages) <= budget)
                     ++c.a_stages;
                 while (!b_resident && c.b_depth < 4 &&
-                       c.a_stages * a_stage + (c.b_depth + 1) * w * b_stage + fixed_bytes(c.a_stages, (c.b_depth + 1) * w) <= budget) {
+                       c.a_stages * a_stage + (c.b_depth + 1) * w * b_stage + c.staging + fixed_bytes(c.a_stages, (c.b_depth + 1) * w) <= budget) {
                     ++c.b_depth;
                     c.b_stages = c.b_depth * w;
                 }
@@ -490,6 +529,11 @@ void conv_tc_patch_consider(const ConvGeom &g, int sm_count, ConvTcPlan *plan) {
         if (c.cost < best.cost) best = c;
     }
     if (best.cost >= 1e30) return;
+    // Measured inside whole networks (Inception-v3, batch 64 and 256): layers whose weights stay resident gain (the
+    // first convolutions of a network, 3 % of a forward in bfloat16), except single-pass TF32 layers with wide float32
+    // outputs, which are bound by their stores; layers that stream their weights win when timed alone but lose a few
+    // per cent in the network, so they only take this path when asked to (option patch=all).
+    if (!q.patch_all && (!b_resident || (!q.bf16 && !q.x3 && g.Cout > 32))) return;
     // compare with what the plan has now (an activation tile per tap)
     const long old_tiles = (long(g.N) * g.OH * g.OW + kTileM - 1) / kTileM * q.n_tiles;
     const double old_step = std::max({tma_cycles(kTileM + double(q.bn) * planes, row), q.bn * tensor_col, (q.x3 ? 700.0 : 450.0) / 2.0});
@@ -500,6 +544,7 @@ void conv_tc_patch_consider(const ConvGeom &g, int sm_count, ConvTcPlan *plan) {
     const int resident = best.resident, a_stages = best.a_stages, b_stages = best.b_stages;
     q.patch_issuers = best.issuers;
     q.patch_b_depth = best.b_depth;
+    q.patch_staging = best.staging;
     const long m_tiles = long(tiles_w) * tiles_h * tiles_n;
     const int a_stage = planes * a_rows * row;
     const int fixed = fixed_bytes(a_stages, b_stages);
@@ -520,7 +565,7 @@ void conv_tc_patch_consider(const ConvGeom &g, int sm_count, ConvTcPlan *plan) {
     q.stages = b_stages;
     q.persistent = 1;
     q.grid_ctas = int(std::min<long>(m_tiles * n_tiles, long(sm_count) * resident));
-    q.smem_bytes = size_t(a_stages) * a_stage + size_t(b_stages) * b_stage + fixed;
+    q.smem_bytes = size_t(a_stages) * a_stage + size_t(b_stages) * b_stage + size_t(best.staging) + fixed;
     // a CTA that needs the SM to itself also takes more than half of its shared memory
     if (resident == 1) q.smem_bytes = std::max(q.smem_bytes, size_t(120 * 1024));
     q.workspace_bytes = 0;
@@ -559,6 +604,8 @@ void launch_conv_tc_patch(const ConvTcParams &p, const ConvTcPlan &q, cudaStream
     t.pad_w = g.pw; t.pad_h = g.ph;
     t.issuers = q.patch_issuers;
     t.b_depth = q.patch_b_depth;
+    t.tma_store = (q.patch_staging > 0 && q.tma_store) ? 1 : 0;
+    t.slab = q.bf16 ? 64 : 32;
     ConvTcParams pp = p;
     if (q.patch_merged) {               // images and rows as one axis (see conv_tc_patch_consider)
         pp.g.H = g.N * g.H; pp.g.OH = g.N * g.OH; pp.g.N = 1;
@@ -577,17 +624,18 @@ void launch_conv_tc_patch(const ConvTcParams &p, const ConvTcPlan &q, cudaStream
     }
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
-    const CUtensorMap &ma = *reinterpret_cast<const CUtensorMap *>(q.tmap_a), &mb = *reinterpret_cast<const CUtensorMap *>(q.tmap_b);
+    const CUtensorMap &ma = *reinterpret_cast<const CUtensorMap *>(q.tmap_a), &mb = *reinterpret_cast<const CUtensorMap *>(q.tmap_b),
+                      &mc = *reinterpret_cast<const CUtensorMap *>(q.tmap_c);
     if (std::getenv("IOS_DEBUG_PATCH"))
         std::fprintf(stderr, "patch conv: N %d H %d W %d Cin %d Cout %d k %dx%d pad %d,%d | bn %d n_tiles %d cchunks %d box %dx%dx%d patch %dx%d "
-                     "a_rows %d a_stages %d b_stages %d resident_b %d tiles %d grid %u smem %zu tmem %d issuers %d depth %d x3 %d bf16 %d merged %d\n",
+                     "a_rows %d a_stages %d b_stages %d resident_b %d tiles %d grid %u smem %zu tmem %d issuers %d depth %d tma_store %d x3 %d bf16 %d merged %d\n",
                      pp.g.N, pp.g.H, pp.g.W, g.Cin, g.Cout, g.kh, g.kw, g.ph, g.pw, t.bn, t.n_tiles, t.cchunks, t.box_w, t.box_h, t.box_n, t.pw, t.ph,
-                     t.a_rows, t.a_stages, t.b_stages, t.b_resident, t.total_tiles, cfg.gridDim.x, q.smem_bytes, t.tmem_cols, t.issuers, t.b_depth, q.x3, q.bf16,
+                     t.a_rows, t.a_stages, t.b_stages, t.b_resident, t.total_tiles, cfg.gridDim.x, q.smem_bytes, t.tmem_cols, t.issuers, t.b_depth, t.tma_store, q.x3, q.bf16,
                      q.patch_merged);
-    if (q.x3) cudaLaunchKernelEx(&cfg, conv_tc_patch_kernel<1>, ma, mb, pp, t);
-    else if (q.bf16 && q.half_rows) cudaLaunchKernelEx(&cfg, conv_tc_patch_kernel<4>, ma, mb, pp, t);
-    else if (q.bf16) cudaLaunchKernelEx(&cfg, conv_tc_patch_kernel<2>, ma, mb, pp, t);
-    else cudaLaunchKernelEx(&cfg, conv_tc_patch_kernel<0>, ma, mb, pp, t);
+    if (q.x3) cudaLaunchKernelEx(&cfg, conv_tc_patch_kernel<1>, ma, mb, mc, pp, t);
+    else if (q.bf16 && q.half_rows) cudaLaunchKernelEx(&cfg, conv_tc_patch_kernel<4>, ma, mb, mc, pp, t);
+    else if (q.bf16) cudaLaunchKernelEx(&cfg, conv_tc_patch_kernel<2>, ma, mb, mc, pp, t);
+    else cudaLaunchKernelEx(&cfg, conv_tc_patch_kernel<0>, ma, mb, mc, pp, t);
 }
 
 }  // namespace ios

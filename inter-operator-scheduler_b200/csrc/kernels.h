@@ -140,6 +140,7 @@ struct ConvTcPlan {
     // patch convolution (conv_tc_patch.cu): stride-1 windows, every input pixel loaded once per tile
     int patch;                     // 1: this plan runs as a patch convolution
     int no_patch;                  // testing aid: never do
+    int patch_all;                 // testing aid: every stride-1 window the cost model favours, not only resident-weight layers
     int patch_pw, patch_ph;        // patch extent per image (input pixels): tile outputs plus the window's halo
     int patch_a_rows;              // rows of one activation stage
     int patch_a_stages, patch_b_stages;
@@ -148,6 +149,8 @@ struct ConvTcPlan {
     int patch_issuers;             // warps that issue tcgen05.mma (1..4)
     int patch_b_depth;             // weight stages per issuer (every issuer has a ring of its own)
     int max_issuers;               // testing aid: cap on patch_issuers (0: none)
+    int patch_bulk_store;          // testing aid: 1 = finished patch tiles leave through bulk tensor stores (one per row segment)
+    int patch_staging;             // bytes of store staging in shared memory (0: finished tiles are stored from registers)
     alignas(64) unsigned char tmap_a[128];   // CUtensorMap over the input view
     alignas(64) unsigned char tmap_b[128];   // CUtensorMap over the packed weights
     alignas(64) unsigned char tmap_c[128];   // CUtensorMap over the output window (when tma_store)

@@ -415,7 +415,9 @@ private:
                            !plan_.options.no_im2col);
             if (plan_.options.force_split_k > 0) conv_tc_set_split(&slot.tcplan, plan_.options.force_split_k);
             slot.tcplan.no_patch = plan_.options.no_patch ? 1 : 0;
+            slot.tcplan.patch_all = plan_.options.patch_all ? 1 : 0;
             slot.tcplan.max_issuers = plan_.options.patch_issuers;
+            slot.tcplan.patch_bulk_store = plan_.options.patch_bulk_store ? 1 : 0;
             conv_tc_patch_consider(g, sms_, &slot.tcplan);
             slot.tcplan.pdl = plan_.options.pdl ? 1 : 0;
             slot.tcplan.max_producers = plan_.options.producers;

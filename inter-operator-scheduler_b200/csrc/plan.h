@@ -37,6 +37,8 @@ struct Options {
     bool no_stem_kernel = false; // testing aid: convolutions over at most 4 input channels take the tensor-core kernel too
     bool no_half_rows = false;  // testing aid: bfloat16 layers of at most 32 input channels keep 128-byte operand rows
     int patch_issuers = 0;      // testing aid: > 0 caps the warps that issue tcgen05.mma in the patch convolution
+    bool patch_bulk_store = false; // testing aid: patch convolutions store finished tiles with bulk tensor stores
+    bool patch_all = false;     // testing aid: patch convolutions also for layers that stream their weights
     bool no_patch = false;      // testing aid: stride-1 windows load an activation tile per tap instead of one patch per tile
     bool no_persistent = false; // testing aid: grids of several waves launch one CTA per tile instead of resident CTAs
     bool no_im2col = false;     // testing aid: windows with taps tile the image in boxes instead of the flat pixel axis

@@ -854,10 +854,14 @@ int ios_set_option(const char *key, const char *value) {
         else if (k == "stages") g_options.force_stages = std::atoi(value);
         else if (k == "producers") g_options.producers = std::atoi(value);
         else if (k == "issuers") g_options.patch_issuers = std::atoi(value);
+        else if (k == "patch_store" && (v == "bulk" || v == "direct")) g_options.patch_bulk_store = v == "bulk";
         else if (k == "bulk_store" && (v == "0" || v == "1")) g_options.no_bulk_store = v == "0";
         else if (k == "im2col" && (v == "0" || v == "1")) g_options.no_im2col = v == "0";
         else if (k == "persistent" && (v == "0" || v == "1")) g_options.no_persistent = v == "0";
-        else if (k == "patch" && (v == "0" || v == "1")) g_options.no_patch = v == "0";
+        else if (k == "patch" && (v == "0" || v == "1" || v == "all")) {
+            g_options.no_patch = v == "0";
+            g_options.patch_all = v == "all";
+        }
         else if (k == "stem" && (v == "0" || v == "1")) g_options.no_stem_kernel = v == "0";
         else if (k == "half_rows" && (v == "0" || v == "1")) g_options.no_half_rows = v == "0";
         else if (k == "timeline") g_options.timeline = v == "1";
@@ -879,7 +883,7 @@ int ios_get_option(const char *key, char *value, int capacity) {
         else if (k == "pdl_edges") v = g_options.pdl_edges ? "1" : "0";
         else if (k == "bulk_store") v = g_options.no_bulk_store ? "0" : "1";
         else if (k == "persistent") v = g_options.no_persistent ? "0" : "1";
-        else if (k == "patch") v = g_options.no_patch ? "0" : "1";
+        else if (k == "patch") v = g_options.no_patch ? "0" : g_options.patch_all ? "all" : "1";
         else if (k == "executor") v = g_options.use_graph ? "graph" : "streams";
         else if (k == "conv") v = g_options.allow_tc ? "auto" : "direct";
         else if (k == "split_k") v = std::to_string(g_options.force_split_k);

@@ -366,6 +366,7 @@ class FarmCostModel:
         self.memo: Dict[str, List[float]] = {}
         self.memo_path = memo_path
         self.calibrate = calibrate
+        self.scale: Dict[int, float] = {}
         self.measured = 0
         if memo_path and os.path.exists(memo_path):
             self.load(memo_path)
@@ -382,7 +383,38 @@ class FarmCostModel:
         with open(path) as fh:
             self.memo.update(json.load(fh))
 
+    def _canonical(self, stage_json, input_json, batch, warmup, number, repeat):
+        from ios.contrib.ios_runtime import canonical_stage_key
+        return self._key(canonical_stage_key(stage_json, input_json), '', int(batch), warmup, number, repeat)
+
+    def _measure(self, tasks):
+        """
+        Measure ``tasks`` -- tuples (stage json, input json, batch, warmup, number, repeat) -- in parallel on the pool,
+        structurally equal ones only once, and store them in the memo.  With ``calibrate`` one common stage is first
+        measured on every worker and each worker's numbers are multiplied by median / its own time for that stage.
+        """
+        todo, first = [], {}
+        for task in tasks:
+            key = self._canonical(*task)
+            if key not in self.memo and key not in first:
+                first[key] = len(todo)
+                todo.append(task)
+        if not todo:
+            return
+        if self.calibrate and not self.scale:
+            times = self.pool.broadcast('stage_latency', *todo[0])
+            ref = float(np.median([np.mean(t) for t in times.values()]))
+            self.scale = {d: ref / float(np.mean(t)) for d, t in times.items()}
+        values = self.pool.map('stage_latency', todo)
+        for key, index in first.items():
+            factor = self.scale.get(self.pool.last_devices[index], 1.0)
+            self.memo[key] = [float(v) * factor for v in values[index]]
+        self.measured += len(todo)
+        if self.memo_path:
+            self.save(self.memo_path)
+
     def prefetch_stages(self, graph, params):
+        """The Python search asks for stages one by one: replay its enumeration first and measure everything at once."""
         from ios.optimizer import optimize
         recorder = _Recorder()
         optimize(graph, batch_size=params['batch_size'], cost_model=recorder, opt_type=params['opt_type'],
@@ -390,58 +422,17 @@ class FarmCostModel:
                  max_num_groups=params['max_num_groups'], max_part_size=params['max_part_size'],
                  max_group_size=params['max_group_size'], compute_weight=False)
         w, n, r = params['warmup'], params['number'], params['repeat']
-        todo = [(s, i, b, w, n, r) for (s, i, b) in recorder.requests
-                if self._key(s, i, b, w, n, r) not in self.memo]
-        if not todo:
-            return
-        scale = {}
-        if self.calibrate and todo:
-            # one common stage on every worker: a worker's numbers are multiplied by median / its own
-            probe = todo[0]
-            times = self.pool.broadcast('stage_latency', *probe)
-            ref = float(np.median([np.mean(t) for t in times.values()]))
-            scale = {d: ref / float(np.mean(t)) for d, t in times.items()}
-        values = self.pool.map('stage_latency', todo)
-        for args, value, device in zip(todo, values, self.pool.last_devices):
-            factor = scale.get(device, 1.0)
-            self.memo[self._key(*args)] = [float(v) * factor for v in value]
-        self.measured += len(todo)
-        self.scale = scale
-        if self.memo_path:
-            self.save(self.memo_path)
+        self._measure([(s, i, b, w, n, r) for (s, i, b) in recorder.requests])
 
     def get_stage_latency(self, stage, batch_size, warmup, number, repeat, profile_stage=False):
-        from ios.contrib.ios_runtime import stage_config
-        stage_json, input_json = stage_config(stage)
-        key = self._key(stage_json, input_json, int(batch_size), warmup, number, repeat)
-        if key not in self.memo:
-            device = self.pool.devices[0]
-            self.memo[key] = self.pool.call(device, 'stage_latency', stage_json, input_json, int(batch_size), warmup,
-                                            number, repeat)
-            self.measured += 1
-        return self.memo[key]
+        return self.get_stage_latencies([stage], batch_size, warmup, number, repeat)[0]
 
     def get_stage_latencies(self, stages, batch_size, warmup, number, repeat):
-        """
-        Many candidate stages at once (what the native search asks for): those not in the memo are measured in
-        parallel on the pool, structurally equal ones (same operators under other names) only once.
-        """
-        from ios.contrib.ios_runtime import stage_config, canonical_stage_key
-        configs = [stage_config(stage) for stage in stages]
-        keys = [self._key(canonical_stage_key(s, i), '', int(batch_size), warmup, number, repeat) for s, i in configs]
-        todo, first = [], {}
-        for key, (stage_json, input_json) in zip(keys, configs):
-            if key not in self.memo and key not in first:
-                first[key] = len(todo)
-                todo.append((stage_json, input_json, int(batch_size), warmup, number, repeat))
-        if todo:
-            values = self.pool.map('stage_latency', todo)
-            for key, index in first.items():
-                self.memo[key] = [float(v) for v in values[index]]
-            self.measured += len(todo)
-            if self.memo_path:
-                self.save(self.memo_path)
-        return [self.memo[key] for key in keys]
+        """Many candidate stages at once (what the native search asks for)."""
+        from ios.contrib.ios_runtime import stage_config
+        tasks = [(*stage_config(stage), int(batch_size), warmup, number, repeat) for stage in stages]
+        self._measure(tasks)
+        return [list(self.memo[self._canonical(*task)]) for task in tasks]
 
     def get_block_latency(self, block, batch_size, warmup, number, repeat, profile_stage=False):
         raise NotImplementedError('the DP search only asks for stage latencies')

@@ -5,8 +5,16 @@ import time
 
 
 def fake_latency(stage_json, input_json, batch):
-    """Deterministic pseudo-latency in (0.01, 1.01) ms derived from the task's text."""
-    digest = hashlib.sha256((stage_json + input_json + str(batch)).encode()).digest()
+    """
+    Deterministic pseudo-latency in (0.01, 1.01) ms derived from the stage's STRUCTURE (operator names do not matter,
+    as on a real device: the farm measures structurally equal stages once).
+    """
+    from ios.contrib.ios_runtime import canonical_stage_key
+    return fake_latency_of_structure(canonical_stage_key(stage_json, input_json), batch)
+
+
+def fake_latency_of_structure(canonical, batch):
+    digest = hashlib.sha256((canonical + str(batch)).encode()).digest()
     return 0.01 + int.from_bytes(digest[:4], 'little') / 2 ** 32
 
 

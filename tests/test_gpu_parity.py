@@ -122,10 +122,12 @@ PATCH_SHAPES = [
 ]
 
 
-@pytest.mark.parametrize('patch', ['1', '0'])
+@pytest.mark.parametrize('patch', ['all', 'bulk', '1', '0'])
 @pytest.mark.parametrize('shape', PATCH_SHAPES)
 def test_conv_patch_vs_oracle(shape, patch):
-    rt.set_option('patch', patch)
+    """patch=all: every shape here takes the patch kernel; 1: the default rule (layers with resident weights); 0: none."""
+    rt.set_option('patch', 'all' if patch == 'bulk' else patch)
+    rt.set_option('patch_store', 'bulk' if patch == 'bulk' else 'direct')
     n, cin, h, w, cout, kh, kw = shape[:7]
     try:
         # (fp32 accumulation over K = kh*kw*Cin terms in another order than the oracle's: the bound grows slowly with K)
@@ -134,6 +136,7 @@ def test_conv_patch_vs_oracle(shape, patch):
         assert _conv_case(shape, 'bf16') <= TOL_BF16
     finally:
         rt.set_option('patch', '1')
+        rt.set_option('patch_store', 'direct')
 
 
 # at most 4 input channels and many pixels: the CUDA-core kernel that keeps the filter in shared memory
