@@ -22,9 +22,10 @@
 // the other warps finish the previous tile (bias, activation, stores of the valid rows) while up to four
 // ISSUER warps (warp 1 and warps 10..12) feed the tensor pipe: one thread gets a tcgen05.mma out about
 // every 140 cycles (measured: whatever its shape), the pipe takes one of N <= 128 every 60, so the taps
-// of a tile are dealt round-robin to the issuers, which all accumulate into the same accumulator in
-// tensor memory -- the issuer of tap 0 signals (an mbarrier) once its first, initialising instruction is
-// out, the others start after that.  Two accumulators alternate between tiles.  Every wait is bounded.
+// of a tile are dealt round-robin to the issuers.  Every issuer has an accumulator of its own in tensor
+// memory and the epilogue adds them in a fixed order: instructions of different warps are not ordered
+// among themselves, so a shared accumulator would make the result depend on timing in its last bits.
+// Two sets of accumulators alternate between tiles.  Every wait is bounded.
 //
 // Replaces cudnnConvolutionBiasActivationForward (reference src/ios/ios_runtime.cu:313-331) for these shapes.
 #include "kernels.h"
@@ -61,7 +62,7 @@ struct PatchGeom {
 };
 
 template <int MODE>      // 0: TF32, 1: three-pass TF32, 2: BF16, 4: BF16 with 64-byte operand rows (at most 32 input channels)
-__global__ void __launch_bounds__(kPatchThreads, 1)
+__global__ void __launch_bounds__(kPatchThreads, 2)
 conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_c, const ConvTcParams p, const PatchGeom t) {
     constexpr bool kX3 = MODE == 1, kBf16 = MODE == 2 || MODE == 4;
@@ -84,8 +85,8 @@ conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     const uint32_t bars = staging0 + (t.tma_store ? uint32_t(slabs) * kATileBytes : 0u);
     const uint32_t a_full0 = bars, a_empty0 = a_full0 + 8u * t.a_stages, a_ready0 = a_empty0 + 8u * t.a_stages;
     const uint32_t b_full0 = a_ready0 + 8u * t.a_stages, b_empty0 = b_full0 + 8u * t.b_stages;
-    const uint32_t acc_full0 = b_empty0 + 8u * t.b_stages, acc_empty0 = acc_full0 + 16u, started0 = acc_empty0 + 16u;
-    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(generic_base + (started0 + 16u - smem_base));
+    const uint32_t acc_full0 = b_empty0 + 8u * t.b_stages, acc_empty0 = acc_full0 + 16u;
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(generic_base + (acc_empty0 + 16u - smem_base));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const ConvGeom &g = p.g;
@@ -105,7 +106,6 @@ conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         if (lane < 2) {
             mbar_init(acc_full0 + 8u * lane, uint32_t(t.issuers));
             mbar_init(acc_empty0 + 8u * lane, uint32_t(epi_warps));
-            mbar_init(started0 + 8u * lane, 1);
         }
         if (lane == 31) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
@@ -233,13 +233,12 @@ conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         for (int ti = 0; ti < my_tiles && ok; ++ti) {
             const uint32_t a = uint32_t(ti) & 1u;
             const uint32_t tile_parity = (uint32_t(ti) >> 1) & 1u;
-            // issuer 0 waits until the epilogue has emptied this accumulator; the others until issuer 0 has begun the tile
-            ok = issuer == 0 ? mbar_wait(acc_empty0 + 8u * a, tile_parity ^ 1u, p.error_flag)
-                             : mbar_wait(started0 + 8u * a, tile_parity, p.error_flag);
+            // the epilogue must have emptied this set of accumulators (sets 0 and 1 start out free: parity 1 passes)
+            ok = mbar_wait(acc_empty0 + 8u * a, tile_parity ^ 1u, p.error_flag);
             if (!ok) { gave_up(2 + issuer, ti, 0, 0, 3); break; }
             tc_fence_after();
-            const uint32_t tmem_d = tmem_base + a * uint32_t(t.acc_stride);
-            uint32_t first = issuer == 0 ? 0u : 1u;        // 0 until the tile's initialising instruction is out
+            const uint32_t tmem_d = tmem_base + (a * uint32_t(t.issuers) + uint32_t(issuer)) * uint32_t(t.acc_stride);
+            uint32_t first = 0u;                            // 0 until this issuer's first instruction of the tile is out
 #pragma unroll 1
             for (int cc = 0; cc < t.cchunks && ok; ++cc) {
                 ok = mbar_wait(a_wait0 + 8u * sa, pa, p.error_flag);
@@ -273,11 +272,7 @@ conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                         } else {
                             umma_tf32(tmem_d, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, acc);
                         }
-                        if (k == 0 && first == 0u) {
-                            // the accumulator now holds this instruction's result alone: the other issuers may add to it
-                            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(started0 + 8u * a) : "memory");
-                            first = 1u;
-                        }
+                        first = 1u;
                     }
                     if (!t.b_resident) {
                         umma_commit(b_empty0 + 8u * slot);
@@ -366,11 +361,18 @@ conv_tc_patch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         const bool live = ok && row_in_box && n < g.N && oh < g.OH && ow < g.OW;
         const long pix_off = ((long(n) * g.OH + oh) * g.OW + ow) * p.out.pitch;
         if (ok) {
-            const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + a * uint32_t(t.acc_stride);
+            const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + a * uint32_t(t.issuers * t.acc_stride);
 #pragma unroll 1
             for (int c = c_begin; c < c_end; c += 16) {
                 float v[16];
                 acc_ld16(taddr + c, pair, v);              // (a warp-wide instruction: every lane takes part)
+#pragma unroll 1
+                for (int w = 1; w < t.issuers; ++w) {       // the other issuers' partial sums, always in this order
+                    float u[16];
+                    acc_ld16(taddr + uint32_t(w * t.acc_stride) + c, pair, u);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] += u[j];
+                }
                 if (!t.tma_store && (!live || c >= valid)) continue;
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
@@ -499,33 +501,44 @@ void conv_tc_patch_consider(const ConvGeom &g, int sm_count, ConvTcPlan *plan) {
         // issuing warps: as many as there are taps, up to four (or the cap of the testing aid); when the weights are not
         // resident every issuer has a ring of its own of at least two stages, so fewer issuers where memory is short
         const int w_max = std::max(1, std::min({kMaxIssuers, taps, q.max_issuers > 0 ? q.max_issuers : kMaxIssuers}));
-        for (int want = 2; want >= 1 && !c.resident; --want) {
-            if (want == 2 && 4 * acc_cols > 512) continue;
+        // one CTA per SM (all of its shared and tensor memory) or two smaller ones: whichever the model below prefers
+        const int patch_rows_c = patch_rows;
+        Cand pick = c;
+        pick.cost = 1e30;
+        for (int want = 2; want >= 1; --want) {       // (on a tie two CTAs: measured faster than one with twice the issuers)
+            Cand d = c;
             const int as_min = (cchunks > 1 || m_tiles * n_tiles > long(sm_count) * want) ? 2 : 1;
             const int budget = (want == 2 ? 110 : 210) * 1024;
-            for (int w = w_max; w >= 1 && !c.resident; --w) {
+            for (int w = w_max; w >= 1 && !d.resident; --w) {
+                // tensor memory: two sets (alternating tiles) of one accumulator per issuer, a power of two of columns
+                int tmem = 32;
+                while (tmem < 2 * w * acc_cols) tmem *= 2;
+                if (tmem > (want == 2 ? 256 : 512)) continue;
                 const int bs_min = b_resident ? taps * cchunks : (w == 1 ? 3 : 2 * w);
-                if (as_min * a_stage + bs_min * b_stage + c.staging + fixed_bytes(as_min, bs_min) > budget) continue;
-                c.resident = want;
-                c.issuers = w;
-                c.a_stages = as_min;
-                c.b_depth = b_resident ? 1 : bs_min / w;
-                c.b_stages = bs_min;
-                while (c.a_stages < 3 &&
-                       (c.a_stages + 1) * a_stage + c.b_stages * b_stage + c.staging + fixed_bytes(c.a_stages + 1, c.b_stages) <= budget)
-                    ++c.a_stages;
-                while (!b_resident && c.b_depth < 4 &&
-                       c.a_stages * a_stage + (c.b_depth + 1) * w * b_stage + c.staging + fixed_bytes(c.a_stages, (c.b_depth + 1) * w) <= budget) {
-                    ++c.b_depth;
-                    c.b_stages = c.b_depth * w;
+                if (as_min * a_stage + bs_min * b_stage + d.staging + fixed_bytes(as_min, bs_min) > budget) continue;
+                d.resident = want;
+                d.issuers = w;
+                d.a_stages = as_min;
+                d.b_depth = b_resident ? 1 : bs_min / w;
+                d.b_stages = bs_min;
+                while (d.a_stages < 3 &&
+                       (d.a_stages + 1) * a_stage + d.b_stages * b_stage + d.staging + fixed_bytes(d.a_stages + 1, d.b_stages) <= budget)
+                    ++d.a_stages;
+                while (!b_resident && d.b_depth < 4 &&
+                       d.a_stages * a_stage + (d.b_depth + 1) * w * b_stage + d.staging + fixed_bytes(d.a_stages, (d.b_depth + 1) * w) <= budget) {
+                    ++d.b_depth;
+                    d.b_stages = d.b_depth * w;
                 }
             }
+            if (!d.resident) continue;
+            // per SM: the TMA unit serves the resident CTAs in turn, the tensor pipe too, the issuing threads work side by side
+            const double chunk_cycles = std::max({tma_cycles(patch_rows_c, row) + (b_resident ? 0.0 : tma_cycles(double(taps) * bn * planes, row)),
+                                                  taps * bn * tensor_col, taps * issue_one / d.issuers / d.resident});
+            d.cost = double(m_tiles) * n_tiles * (cchunks * chunk_cycles + 400.0);
+            if (d.cost < pick.cost) pick = d;
         }
+        c = pick;
         if (!c.resident) continue;
-        // per SM: the TMA unit serves the resident CTAs in turn, the tensor pipe too, the issuing threads work side by side
-        const double chunk_cycles = std::max({tma_cycles(patch_rows, row) + (b_resident ? 0.0 : tma_cycles(double(taps) * bn * planes, row)),
-                                              taps * bn * tensor_col, taps * issue_one / c.issuers / c.resident});
-        c.cost = double(m_tiles) * n_tiles * (cchunks * chunk_cycles + 400.0);
         if (c.cost < best.cost) best = c;
     }
     if (best.cost >= 1e30) return;
@@ -597,7 +610,7 @@ void launch_conv_tc_patch(const ConvTcParams &p, const ConvTcPlan &q, cudaStream
     t.wide = (q.x3 && q.bn <= 128) ? 1 : 0;
     t.acc_stride = (t.wide ? 2 : 1) * ceil_div_i(q.bn, 32) * 32;
     int cols = 32;
-    while (cols < 2 * t.acc_stride) cols *= 2;
+    while (cols < 2 * q.patch_issuers * t.acc_stride) cols *= 2;
     t.tmem_cols = cols;
     t.round_tf32 = g.round_out;
     t.cout_pad = q.cout_pad;

@@ -127,3 +127,50 @@ def test_engine_artefact_files_are_validated(tmp_path):
     junk.write_bytes(b'not an engine artefact at all' * 10)
     with pytest.raises(RuntimeError, match='not an engine artefact'):
         rt.Engine.load(str(junk))
+
+
+def _reference_checkout():
+    path = os.environ.get('IOS_REFERENCE', os.path.join(os.path.dirname(ROOT), 'reference'))
+    return path if os.path.isdir(os.path.join(path, 'python', 'ios')) else None
+
+
+@pytest.mark.skipif(_reference_checkout() is None, reason='no reference checkout on this machine')
+def test_reference_front_end_drives_this_library(tmp_path):
+    """
+    Route 1 of the integration notes: the reference's own Python package, unmodified, bound to this
+    libios_runtime.so.  Its loader looks for the library relative to its own file, so the test hands it
+    the search list instead of copying anything.  Without a GPU the call comes back with NaN latencies
+    and a message that names the missing device -- proof that the symbol was found and that the graph
+    JSON crossed the boundary intact (a marshalling fault would report a JSON error, and the reference's
+    own runtime would have ended the interpreter); with a GPU it returns real latencies.
+    """
+    import subprocess
+    import sys
+    script = tmp_path / 'route1.py'
+    script.write_text(f'''
+import sys, types, math
+import torch                                      # before the stub: torch probes pydot too
+sys.modules.setdefault("pydot", types.ModuleType("pydot"))
+sys.path.insert(0, {os.path.join(_reference_checkout(), "python")!r})
+import ios
+from ios.contrib import ios_runtime
+ios_runtime.libname_list = [{rt.load_ios_library()._name!r}]
+v = ios.placeholder(output_shape=(375, 15, 15))
+block = ios.Block(enter_node=v.node)
+v1 = ios.conv2d(block, inputs=[[v]], out_channels=375, kernel=(3, 3), stride=(1, 1), padding=(1, 1), act="relu")
+v2 = ios.conv2d(block, inputs=[[v]], out_channels=750, kernel=(3, 3), stride=(1, 1), padding=(1, 1), act="relu")
+out = ios.identity(block, inputs=[[v1], [v2]], is_exit=True)
+graph = ios.Graph(name="demo", input=v.node, blocks=[block])
+graph.init_weights()
+graph.sequential_schedule()
+lat = ios.ios_runtime.graph_latency(graph, batch_size=1, repeat=3)
+print("LATENCY", " ".join("nan" if math.isnan(x) else "ok" if x > 0 else "bad" for x in lat))
+''')
+    done = subprocess.run([sys.executable, str(script)], capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr[-2000:]
+    line = [text for text in done.stdout.splitlines() if text.startswith('LATENCY')][0]
+    if has_gpu():
+        assert line == 'LATENCY ok ok ok'
+    else:
+        assert line == 'LATENCY nan nan nan'
+        assert 'no CUDA device' in done.stderr or 'device' in done.stderr
