@@ -1,30 +1,38 @@
 // Implicit-GEMM convolution on the 5th-generation tensor cores (sm_100a): tcgen05.mma with the
 // accumulator in tensor memory, both operands staged in shared memory by TMA, one CTA per
-// (pixel tile, output-channel tile, K split).
+// (pixel tile, output-channel tile, K split) -- or resident CTAs that walk the tiles.
 //
 // GEMM view of y = act(conv(x, w) + b), groups == 1:
 //     D[pixel, cout] = sum over taps (r, s) and input channels c of  X[pixel @ tap, c] * Wp[cout, tap, c]
-// * M (128 TMEM lanes) = a tile of output pixels: box_w x box_h x box_n pixels of the output,
-//   fetched for tap (r, s) by ONE tiled TMA load over the NHWC input whose box starts at
-//   (ow0*sw - pw + s, oh0*sh - ph + r) and walks with element strides (sw, sh).  Coordinates
-//   outside the image are filled with zeros by the TMA unit, which is the convolution's padding;
-//   channels beyond Cin are out of range too, so K needs no padded activation copy.
-// * N = bn output channels (16..256), K advances 32 floats (one 128-byte swizzle row) per step,
-//   four tcgen05.mma.kind::tf32 (K = 8) per step.
-// * split_k CTAs share an output tile when the layer is too small to fill 148 SMs (batch 1).
-//   Up to 8 of them form a thread-block cluster: each parks its fp32 partial tile in its own
-//   shared memory, and after a cluster barrier CTA r adds rows [r*128/S, (r+1)*128/S) of all S
-//   tiles through distributed shared memory, in split order, and stores them.  Larger splits (and
-//   the allocation-free entry point) go through a global workspace instead: the last CTA to arrive
-//   (one atomic ticket per tile) adds the partials in split order.  Either way the result does not
-//   depend on timing.
-// * Epilogue: tcgen05.ld (one thread per pixel row), + bias, activation, optional rounding to TF32
-//   for a consumer convolution, store into a channel window of the destination (NHWC, pitch), which
-//   is how concat-by-placement and merged convolutions are written without a copy.
+// * M (128 TMEM lanes) = 128 consecutive pixels of the flattened (n, oh, ow) axis.  A 1x1 stride-1
+//   convolution fetches them with a plain tiled TMA box over the NHWC input; every other window with an
+//   im2col-mode TMA load (bounding-box corners = -padding and the last window corner, element strides =
+//   the convolution's stride, the tap is the instruction's im2col offset).  Positions outside the image
+//   and channels beyond Cin read zeros, so K needs no padded activation copy.  (Option im2col=0 keeps the
+//   older form: a box_w x box_h x box_n rectangle of output pixels per tile, one tiled load per tap.)
+// * N = bn output channels (32..256), K advances one 128-byte swizzle row per step (32 floats, four
+//   tcgen05.mma.kind::tf32 of K = 8; 64 bfloat16, four kind::f16 of K = 16; bfloat16 layers of at most 32
+//   input channels use 64-byte rows, two instructions per step).  Three-pass TF32: the weight tile and its
+//   residual lie behind one another, one instruction of width 2 bn forms a_hi*w_hi | a_hi*w_lo, a second
+//   adds a_lo*w_hi; the activation residual is computed from the landed tile by the epilogue warps.
+// * split_k CTAs share an output tile when the layer is too small to fill 148 SMs (batch 1).  Up to 8
+//   of them form a thread-block cluster: each writes its fp32 partial tile to a workspace (it stays in
+//   L2), and after ONE cluster barrier CTA r adds rows [r*128/S, (r+1)*128/S) of all S tiles in split
+//   order, applies bias and activation and stores them.  Larger splits (a testing aid, and the
+//   allocation-free entry point) elect the last CTA to arrive by one atomic ticket per tile.  Either way
+//   the result does not depend on timing.
+// * Epilogue: tcgen05.ld (one thread per pixel row), + bias, activation, optional rounding to TF32 for a
+//   consumer convolution, then the tile is staged in shared memory (128-byte swizzle) and leaves through
+//   bulk tensor stores into a channel window of the destination (NHWC, pitch) -- which is how
+//   concat-by-placement and merged convolutions are written without a copy; windows that are not 16-byte
+//   aligned are stored from registers.
 //
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM allocator + MMA issuer,
-// warps 2..5 = epilogue.  Every wait on an mbarrier is bounded: when the bound is hit the kernel
-// records a code in *error_flag, drains its own loads, frees its tensor memory and returns.
+// Warp roles of conv_tc_kernel (192 threads): warp 0 = TMA producer lanes, warp 1 = MMA issuer, warps
+// 2..5 = operand split (three-pass mode) and epilogue; warp 2 allocates and frees tensor memory.
+// conv_tc_persistent_kernel (320 threads): the same with eight epilogue warps and two accumulators in
+// tensor memory, for grids of several waves.  Every wait on an mbarrier is bounded: when the bound is hit
+// the kernel records a code in *error_flag, drains its own loads, frees its tensor memory and returns.
+// Stride-1 windows whose weights fit in shared memory take conv_tc_patch.cu instead.
 //
 // Replaces cudnnConvolutionBiasActivationForward / cudnnConvolutionForward + cudnnAddTensor
 // (reference src/ios/ios_runtime.cu:313-331) and the algorithm search of :150-205.
