@@ -122,7 +122,7 @@ def kernel_sources_sha16():
     """Identifies the build: a hash over the CUDA sources of the convolution kernels."""
     import hashlib
     digest = hashlib.sha256()
-    for name in ('conv_tc.cu', 'conv_direct.cu', 'kernels.h', 'plan.cu'):
+    for name in ('conv_tc.cu', 'conv_tc_patch.cu', 'tc_device.h', 'conv_direct.cu', 'kernels.h', 'plan.cu'):
         with open(os.path.join(ROOT, 'inter-operator-scheduler_b200', 'csrc', name), 'rb') as fh:
             digest.update(fh.read())
     return digest.hexdigest()[:16]
@@ -333,8 +333,10 @@ def run_ours(args):
         'launches_per_step': conv['launches'], 'avg_launch_us': round(1e3 * conv['ms'] / max(1, conv['launches']), 3),
         'flops_per_step': conv['work'],
         'share_of_device_time': round(conv['ms'] / total_ms, 4) if total_ms else None,
+        # work is bytes for the bandwidth kernels and multiply-add flops for the CUDA-core convolution
         'other_kernels': {k: {'launches': v['launches'], 'ms': round(v['ms'], 4),
-                              'GB/s': round(v['work'] / (v['ms'] * 1e-3) / 1e9, 1) if v['ms'] > 0 else None}
+                              ('GFLOP/s' if k == 'conv_direct' else 'GB/s'):
+                                  round(v['work'] / (v['ms'] * 1e-3) / 1e9, 1) if v['ms'] > 0 else None}
                           for k, v in by_kind.items() if k != 'conv_tc'},
     }
     # DRAM bytes of the convolution launches of one forward: an ncu capture cannot run inside the bench, so the
