@@ -72,7 +72,22 @@ struct TileGeom {
     int producers;    // lanes of warp 0 that issue TMA loads; divides `stages`
     int wide;         // 1: (three-pass mode, bn <= 128) one instruction of width 2 bn covers the weight tile and its
                       //    residual; the residual's products accumulate in columns [bn, 2 bn)
+    int split_shift;  // log2(split_k) when it is a power of two, else -1
+    unsigned magic_ow, magic_cc, magic_kw;   // division by OW / cchunks / kw as a multiplication (0: divide)
+    int push;         // 1: (cluster) partial tiles are pushed into the shared memory of the CTA that finishes their rows
+    int recv_off;     // byte offset of the area those pushes land in (behind the pipeline stages and barriers)
 };
+
+// n / d for 0 <= n with n * d < 2^32, by the multiplier the host worked out (floor(2^32 / d) + 1); a CTA runs its
+// prologue once, one thread per scheduler, so a division there is 100-400 cycles that nothing hides.
+__device__ __forceinline__ int div_by(int n, int d, unsigned magic) {
+    if (d == 1) return n;
+    return magic ? int(__umulhi(unsigned(n), magic)) : n / d;
+}
+// n / d for n >= 0, d > 0, where d is most often a power of two
+__device__ __forceinline__ int div_pow2_likely(int n, int d) {
+    return (d & (d - 1)) == 0 ? n >> (31 - __clz(d)) : n / d;
+}
 
 // Optional diagnostics: CTA (0,0,0) stamps the SM clock at fixed points of its life.  The stamps sit
 // in the single-thread role loops, where the mere test for them was measured at 3 % of batch-1
@@ -176,6 +191,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const uint32_t bars = smem_base + uint32_t(t.stages) * stage_bytes;
     const uint32_t full0 = bars, empty0 = bars + 8u * t.stages, ready0 = bars + 16u * t.stages;
     const uint32_t accum_bar = bars + 24u * t.stages;
+    const uint32_t recv_bar = accum_bar + 16u;
     volatile uint32_t *tmem_slot =
         reinterpret_cast<volatile uint32_t *>(generic_base + size_t(t.stages) * stage_bytes + 24 * t.stages + 8);
     volatile int *ticket_slot = reinterpret_cast<volatile int *>(tmem_slot + 1);
@@ -183,6 +199,14 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const ConvGeom &g = p.g;
     if (threadIdx.x == 0) STAMP(0);
+    {
+        // Kernel parameters are new with every launch, so the first read of each of their cache lines misses.
+        // One word of every line is asked for here, all at once, instead of one miss at a time where the
+        // epilogue first needs them.
+        const int touch = p.in.pitch ^ p.out.pitch ^ int(reinterpret_cast<uintptr_t>(p.bias)) ^ int(reinterpret_cast<uintptr_t>(p.error_flag)) ^
+                          g.N ^ g.act ^ g.round_out ^ t.box_w ^ t.tmem_cols ^ t.wide ^ t.recv_off;
+        asm volatile("" ::"r"(touch));
+    }
 
     // tile coordinates
     const int m_tile = blockIdx.x, n_tile = blockIdx.y, split = blockIdx.z;
@@ -192,9 +216,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (t.im2col) {
             // the tile's first pixel, as the corner of its filter window in input coordinates
             const int per_image = g.OH * g.OW;
-            n0 = ow0 / per_image;
+            n0 = g.N == 1 ? 0 : ow0 / per_image;
             const int rem = ow0 - n0 * per_image;
-            oh0 = rem / g.OW;
+            oh0 = div_by(rem, g.OW, t.magic_ow);
             im_w = (rem - oh0 * g.OW) * g.sw - g.pw;
             im_h = oh0 * g.sh - g.ph;
         }
@@ -206,9 +230,21 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         n0 = (rest / t.tiles_h) * t.box_n;
     }
     const int cout0 = n_tile * t.bn;
-    const int it_begin = int(long(split) * t.k_iters / t.split_k);
-    const int it_end = int(long(split + 1) * t.k_iters / t.split_k);
+    // K steps [split * k_iters / split_k, (split + 1) * k_iters / split_k)
+    const int it_begin = t.split_shift >= 0 ? (split * t.k_iters) >> t.split_shift : int(unsigned(split * t.k_iters) / unsigned(t.split_k));
+    const int it_end = t.split_shift >= 0 ? ((split + 1) * t.k_iters) >> t.split_shift : int(unsigned((split + 1) * t.k_iters) / unsigned(t.split_k));
     const int n_it = it_end - it_begin;
+    // Push form of the cluster reduction: the tile's valid rows (a prefix of the 128 when the tile is a run of
+    // consecutive pixels) are dealt to the CTAs of the cluster, `push_rpr` rows each; this CTA finishes `push_rows`
+    // of them and receives, from every CTA of the cluster, those rows of that CTA's partial tile.
+    const bool push = kCluster && t.push != 0;
+    int push_vrows = 0, push_rpr = 0, push_rows = 0;
+    if (push) {
+        const long total = long(g.N) * g.OH * g.OW;
+        push_vrows = t.flat ? int(max(0l, min(long(min(t.box_w, kTileM)), total - ow0))) : kTileM;
+        push_rpr = t.split_shift >= 0 ? (push_vrows + t.split_k - 1) >> t.split_shift : (push_vrows + t.split_k - 1) / t.split_k;
+        push_rows = max(0, min(push_rpr, push_vrows - int(cluster_cta_rank()) * push_rpr));
+    }
 
     if (warp == 0) {
         // one lane per pipeline stage initialises its three barriers; lane 31 fetches the tensor maps
@@ -218,6 +254,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             mbar_init(ready0 + 8u * lane, 128);
         }
         if (lane == 30) mbar_init(accum_bar, 1);
+        if (lane == 29 && push) mbar_init(recv_bar, 1);
         if (lane == 31) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
@@ -225,6 +262,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        // the bytes this CTA will be sent: its rows of the partial tiles of all CTAs of the cluster
+        if (lane == 29 && push) mbar_expect_tx(recv_bar, uint32_t(t.split_k * push_rows * t.bn) * 4u);
     }
     if (warp == 2) {
         tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), uint32_t(t.tmem_cols));
@@ -233,6 +272,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    // Nothing may be pushed into a CTA before its barrier exists: every thread of the cluster arrives here and
+    // waits only where it needs the others (the epilogue before its first push, everyone else before leaving).
+    if (push) cluster_arrive_relaxed();
     const uint32_t tmem_base = *tmem_slot;
     if (threadIdx.x == 0) STAMP(1);
     // Everything above touches no global memory, so under programmatic dependent launch it overlaps
@@ -260,8 +302,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const int early = min(n_it, t.stages);
         if (lane < early) {
             const int it = it_begin + lane;
-            const int tap = it / t.cchunks, cc = it - tap * t.cchunks;
-            const int r = tap / g.kw, sx = tap - r * g.kw;
+            const int tap = div_by(it, t.cchunks, t.magic_cc), cc = it - tap * t.cchunks;
+            const int r = div_by(tap, g.kw, t.magic_kw), sx = tap - r * g.kw;
             const uint32_t stage = smem_base + uint32_t(lane) * stage_bytes;
             const uint32_t bar = full0 + 8u * lane;
             asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -345,7 +387,70 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const int quad = warp & 3;                  // TMEM lane group this warp may read
         const int row = quad * 32 + lane;
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        for (int j = tid; j < t.bn; j += 128) bias_s[j] = (p.bias && cout0 + j < g.Cout) ? p.bias[cout0 + j] : 0.0f;
+        // (the loads go out now; the values are put into shared memory further down, so that nothing waits for them here)
+        float bias_early[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int j = tid + u * 128;
+            bias_early[u] = (p.bias && j < t.bn && cout0 + j < g.Cout) ? __ldg(p.bias + cout0 + j) : 0.0f;
+        }
+        // Push form of the cluster reduction: everything that does not depend on the accumulator is worked out
+        // now, while the first tiles are on their way.  After the accumulator there are four warps, one per
+        // scheduler, each instruction waiting for the one before it: what is left on that path is the accumulator
+        // load, the pushes, and for the rows this CTA finishes the loads, adds and stores.
+        constexpr int kFast = 2;                    // items per thread with everything precomputed (covers 64 columns x 16 rows)
+        uint32_t push_dst = 0, push_bar = 0, push_stride = 0;
+        bool push_mine = false;
+        int fast_src[kFast];                        // float4 index of partial tile 0 of the item in the receive area
+        long fast_at[kFast];                        // element offset of the item's four outputs, or -1
+        int fast_count[kFast];                      // valid outputs of the four
+        float4 fast_bias[kFast];
+        if (kCluster && push) {
+            if (threadIdx.x == 64) STAMP(8);
+            cluster_wait();                                     // every CTA of the cluster has its barrier set up
+            if (threadIdx.x == 64) STAMP(13);
+            push_mine = row < push_vrows;
+            const int owner = push_mine ? div_pow2_likely(row, push_rpr) : 0;
+            const int lrow = row - owner * push_rpr;
+            push_dst = cluster_map(smem_base + uint32_t(t.recv_off) + uint32_t(split * (t.bn >> 2) * push_rpr + lrow) * 16u, uint32_t(owner));
+            push_bar = cluster_map(recv_bar, uint32_t(owner));
+            push_stride = uint32_t(push_rpr) * 16u;
+            if (threadIdx.x == 64) STAMP(14);
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+            if (tid + u * 128 < t.bn) bias_s[tid + u * 128] = bias_early[u];
+        // (the second half of the preparation: called once the operand work of the K loop is behind these warps)
+        auto prepare_rows = [&]() {
+            const int r0 = int(cluster_cta_rank()) * push_rpr;
+            const int valid = min(t.bn, g.Cout - cout0);
+            const int n_items = push_rows * (t.bn >> 2);
+#pragma unroll
+            for (int k = 0; k < kFast; ++k) {
+                const int item = tid + k * 128;
+                fast_src[k] = -1;
+                fast_at[k] = -1;
+                fast_count[k] = 0;
+                fast_bias[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (item < n_items) {
+                    const int q4 = div_pow2_likely(item, push_rows), lr = item - q4 * push_rows, c = q4 << 2;
+                    fast_src[k] = q4 * push_rpr + lr;
+                    const long pix = long(ow0) + r0 + lr;
+                    const long pix_off = t.flat ? ((r0 + lr < t.box_w && pix < long(g.N) * g.OH * g.OW) ? pix * p.out.pitch : -1)
+                                                : boxed_pixel_offset(r0 + lr, t.box_w, t.box_h, t.box_n, ow0, oh0, n0, g.N, g.OH, g.OW, p.out.pitch);
+                    if (pix_off >= 0 && c < valid) {
+                        fast_at[k] = pix_off + cout0 + c;
+                        fast_count[k] = valid - c;
+                        // (straight from global memory: the loads are in flight until the sums need them)
+                        float b[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) b[j] = (p.bias && c + j < valid) ? __ldg(p.bias + cout0 + c + j) : 0.0f;
+                        fast_bias[k] = make_float4(b[0], b[1], b[2], b[3]);
+                    }
+                }
+            }
+            if (threadIdx.x == 64) STAMP(15);
+        };
         bool ok = true;
         if (kX3) {
             // The tensor core reads the 19 leading bits of an fp32 operand (sign, exponent, 10 mantissa
@@ -378,19 +483,121 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 if (++s == t.stages) { s = 0; phase ^= 1u; }
             }
         }
+        if (kCluster && push) prepare_rows();
         if (ok) ok = mbar_wait(accum_bar, 0, p.error_flag);
         ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
         if (!ok && lane == 0) atomicExch(p.error_flag, 3);
         if (threadIdx.x == 64) STAMP(5);
         tc_fence_after();
-        asm volatile("bar.sync 1, 128;" ::: "memory");          // bias_s is complete
+        if (!(kCluster && push)) asm volatile("bar.sync 1, 128;" ::: "memory");          // bias_s is complete
         if (threadIdx.x == 64) STAMP(9);
         const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16);
         const uint32_t pair = t.wide ? uint32_t(t.bn) : 0u;
         const int tile_id = m_tile * gridDim.y + n_tile;
         bool finisher = true;
-        if (kCluster) {
-            // cluster reduction: this CTA's partial tile goes to the workspace as ws[tile][split][column quad][row]
+        if (kCluster && push) {
+            // cluster reduction, push form: row r of this CTA's partial tile goes, 16 bytes at a time, into the
+            // shared memory of the CTA that finishes row r, as recv[split][column quad][row of that CTA]; the
+            // bytes are counted on that CTA's barrier as they land, so no cluster barrier and no trip through L2
+            // follows.  (The accumulator load is warp-wide; rows past the tile's valid prefix are not sent.)
+            finisher = false;
+            if (ok) {
+#pragma unroll 1
+                for (int c = 0; c < t.bn; c += 32) {
+                    float v[32];
+                    acc_ld32_pair(taddr + c, pair, v);
+                    if (push_mine) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4)
+                            cluster_push16(push_dst + uint32_t((c + j) >> 2) * push_stride, push_bar, v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    }
+                }
+            }
+            if (threadIdx.x == 64) STAMP(6);
+            asm volatile("bar.sync 1, 128;" ::: "memory");      // bias_s is complete (every epilogue thread gets here)
+            // the rows this CTA finishes have landed once its barrier has counted their bytes
+            bool good = ok;
+            if (good && push_rows > 0) good = __all_sync(0xffffffffu, mbar_wait_cluster(recv_bar, 0, p.error_flag) ? 1 : 0) != 0;
+            if (threadIdx.x == 64) STAMP(10);
+            if (good) {
+                // partial tiles are added in split order, so the result does not depend on timing
+                const float4 *recv = reinterpret_cast<const float4 *>(generic_base + t.recv_off);
+                const int plane = (t.bn >> 2) * push_rpr;           // float4 from one partial tile to the next
+                auto finish_fast = [&](auto split_tag) {
+                    constexpr int S = decltype(split_tag)::value;
+                    float4 part[kFast][S];
+#pragma unroll
+                    for (int k = 0; k < kFast; ++k)
+#pragma unroll
+                        for (int sp = 0; sp < S; ++sp) part[k][sp] = recv[max(fast_src[k], 0) + sp * plane];
+                    if (threadIdx.x == 64) STAMP(11);
+#pragma unroll
+                    for (int k = 0; k < kFast; ++k) {
+                        float4 acc = part[k][0];
+#pragma unroll
+                        for (int sp = 1; sp < S; ++sp) {
+                            acc.x += part[k][sp].x; acc.y += part[k][sp].y; acc.z += part[k][sp].z; acc.w += part[k][sp].w;
+                        }
+                        float o[4] = {acc.x + fast_bias[k].x, acc.y + fast_bias[k].y, acc.z + fast_bias[k].z, acc.w + fast_bias[k].w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            o[j] = act_apply(o[j], g.act);
+                            if (t.round_tf32) o[j] = round_tf32(o[j]);
+                        }
+                        if (fast_at[k] >= 0) store4_direct(p.out.ptr, kBf16, fast_at[k], make_float4(o[0], o[1], o[2], o[3]), fast_count[k]);
+                        if (k == 0 && threadIdx.x == 64) STAMP(12);
+                    }
+                };
+                if (t.split_k == 8) finish_fast(std::integral_constant<int, 8>());
+                else if (t.split_k == 4) finish_fast(std::integral_constant<int, 4>());
+                else if (t.split_k == 2) finish_fast(std::integral_constant<int, 2>());
+                // items beyond the precomputed ones (wide tiles), and splits without a form of their own
+                const int quads = t.bn >> 2;
+                const int n_items = push_rows * quads;
+                const int r0 = int(cluster_cta_rank()) * push_rpr;
+                const int valid = min(t.bn, g.Cout - cout0);
+                const bool fast_done = t.split_k == 8 || t.split_k == 4 || t.split_k == 2;
+#pragma unroll 1
+                for (int item = tid + (fast_done ? kFast * 128 : 0); item < n_items; item += 128) {
+                    const int q4 = item / push_rows, lr = item - q4 * push_rows, c = q4 << 2;
+                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+                    for (int sp = 0; sp < t.split_k; ++sp) {
+                        const float4 x = recv[q4 * push_rpr + lr + sp * plane];
+                        acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+                    }
+                    const long pix = long(ow0) + r0 + lr;
+                    const long pix_off = t.flat ? ((r0 + lr < t.box_w && pix < long(g.N) * g.OH * g.OW) ? pix * p.out.pitch : -1)
+                                                : boxed_pixel_offset(r0 + lr, t.box_w, t.box_h, t.box_n, ow0, oh0, n0, g.N, g.OH, g.OW, p.out.pitch);
+                    if (pix_off < 0 || c >= valid) continue;
+                    float o[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float z = act_apply(o[j] + bias_s[c + j], g.act);
+                        o[j] = t.round_tf32 ? round_tf32(z) : z;
+                    }
+                    store4_direct(p.out.ptr, kBf16, pix_off + cout0 + c, make_float4(o[0], o[1], o[2], o[3]), valid - c);
+                }
+            }
+            if (threadIdx.x == 64) STAMP(7);
+            // the accumulator has been read by all four warps: TMEM goes back
+            tc_fence_before();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (warp == 2) {
+                tc_fence_after();
+                tmem_dealloc(tmem_base, uint32_t(t.tmem_cols));
+            }
+            if (!good) {
+                // A warp that gave up stays until every other thread of the cluster has left or given up too:
+                // a CTA must not vanish while others may still push into its shared memory.
+                if (lane == 0) atomicExch(p.error_flag, 4);
+                cluster_arrive();
+                cluster_wait();
+            }
+            return;
+        } else if (kCluster) {
+            // cluster reduction through L2 (when the push form's receive area does not fit): this CTA's partial tile
+            // goes to the workspace as ws[tile][split][column quad][row]
             // (float4 units; a warp writes 512 contiguous bytes).  It stays in L2: the CTAs of the cluster read it
             // back right after the cluster barrier below.  (Loads from another CTA's shared memory were measured
             // at a few bytes per cycle here, several times slower than this round trip through L2.)
@@ -538,9 +745,19 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
     }
     if (kCluster) {
-        // Every thread of every CTA of the cluster passes this barrier, whatever happened before; its
-        // release / acquire pair makes the partial tiles written above visible to the cluster.
-        cluster_sync_all();
+        if (push) {
+            // warps 0 and 1 pair their arrival at the set-up barrier with a wait and leave
+            if (warp < 2) {
+                __syncwarp();
+                cluster_wait();
+                return;
+            }
+            return;                 // (the epilogue warps have finished the tile inside their branch)
+        } else {
+            // Every thread of every CTA of the cluster passes this barrier, whatever happened before; its
+            // release / acquire pair makes the partial tiles written above visible to the cluster.
+            cluster_sync_all();
+        }
         if (threadIdx.x == 64) STAMP(10);
         if (warp >= 2) {
             // CTA r of the cluster finishes rows [r*128/S, (r+1)*128/S) of the tile: it adds the S partial
@@ -548,13 +765,16 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             // and writes its rows.  A thread puts all its loads in flight before it adds anything.
             const int tid = threadIdx.x - 64;
             const int rank = int(cluster_cta_rank());
-            const int r0 = rank * kTileM / t.split_k, r1 = (rank + 1) * kTileM / t.split_k;
-            const int rows = r1 - r0;
+            const int r0 = rank * kTileM / t.split_k;
+            const int rows = (rank + 1) * kTileM / t.split_k - r0;
             const int quads = t.bn >> 2;
             const int valid = min(t.bn, g.Cout - cout0);
             const int n_items = rows * quads;
             const int tile_id = m_tile * gridDim.y + n_tile;
-            const float4 *ws_tile = reinterpret_cast<const float4 *>(p.workspace) + size_t(tile_id) * t.split_k * size_t(quads) * kTileM;
+            // partial tile `sp`, column quad `q4`, row `lr` of this CTA's rows is at src0[(sp * quads + q4) * pitch + lr]
+            const float4 *src0 = reinterpret_cast<const float4 *>(p.workspace) + size_t(tile_id) * t.split_k * size_t(quads) * kTileM + r0;
+            const int pitch = kTileM;
+            auto fetch = [&](const float4 *src) -> float4 { return __ldcg(src); };
             // offset of the output pixel held by tile row `row`, or -1
             auto pixel_offset = [&](int row) -> long {
                 if (t.flat) {
@@ -584,9 +804,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     for (int k = 0; k < kItems; ++k) {
                         const int item = min(first + k * 128, n_items - 1);
                         const int q4 = item / rows;
-                        const float4 *src = ws_tile + size_t(q4) * kTileM + r0 + (item - q4 * rows);
+                        const float4 *src = src0 + size_t(q4) * pitch + (item - q4 * rows);
 #pragma unroll
-                        for (int sp = 0; sp < S; ++sp) part[k][sp] = __ldcg(src + size_t(sp) * quads * kTileM);
+                        for (int sp = 0; sp < S; ++sp) part[k][sp] = fetch(src + size_t(sp) * quads * pitch);
                     }
 #pragma unroll
                     for (int k = 0; k < kItems; ++k) {
@@ -609,11 +829,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll 1
             for (int item = tid; item < n_items; item += 128) {
                 const int q4 = item / rows;
-                const float4 *src = ws_tile + size_t(q4) * kTileM + r0 + (item - q4 * rows);
+                const float4 *src = src0 + size_t(q4) * pitch + (item - q4 * rows);
                 float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 1
                 for (int sp = 0; sp < t.split_k; ++sp) {
-                    const float4 x = __ldcg(src + size_t(sp) * quads * kTileM);
+                    const float4 x = fetch(src + size_t(sp) * quads * pitch);
                     acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
                 }
                 finish(r0 + (item - q4 * rows), q4 << 2, acc);
@@ -1143,6 +1363,25 @@ void conv_tc_set_split(ConvTcPlan *plan, int split) {
     // the store staging needs one 16 KiB slab per 32 output channels inside the pipeline buffers
     while (q.stages * stage_bytes < ceil_div(q.bn, slab_channels) * kATileBytes) ++q.stages;
     q.smem_bytes = size_t(q.stages) * stage_bytes + 24 * q.stages + 64 + 1024;
+    // A cluster exchanges its partial tiles through shared memory when an area for the rows a CTA finishes --
+    // one slice per CTA of the cluster -- fits behind the pipeline (at the price of a stage, down to three).
+    q.push = 0;
+    q.recv_off = 0;
+    if (split > 1 && q.cluster && !q.no_push) {
+        const int recv_bytes = split * ceil_div(kTileM, split) * q.bn * 4;
+        const int limit = 225 * 1024;                       // what a CTA may have, less the kernel's static shared memory
+        const int staging = ceil_div(q.bn, slab_channels) * kATileBytes;
+        auto recv_off = [&](int stages) { return (stages * stage_bytes + 24 * stages + 64 + 15) & ~15; };
+        int stages = q.stages;
+        while (stages > 3 && recv_off(stages) + recv_bytes + 1024 > limit) --stages;
+        if (stages == 5 || stages == 7) --stages;
+        if (recv_off(stages) + recv_bytes + 1024 <= limit && stages * stage_bytes >= staging) {
+            q.push = 1;
+            q.stages = stages;
+            q.recv_off = recv_off(stages);
+            q.smem_bytes = size_t(q.recv_off) + recv_bytes + 1024;
+        }
+    }
     // More tiles than CTAs that fit at once: persistent CTAs with two accumulators in TMEM, the store
     // staging in an area of its own behind the pipeline stages.
     q.persistent = 0;
@@ -1167,7 +1406,7 @@ void conv_tc_set_split(ConvTcPlan *plan, int split) {
     }
     // partial tiles meet in a workspace (one region per tile and split); splits of more than 8, which no
     // cluster covers, also need an arrival counter per tile
-    q.workspace_bytes = split > 1 ? size_t(base) * split * q.bn * kTileM * sizeof(float) : 0;
+    q.workspace_bytes = (split > 1 && !q.push) ? size_t(base) * split * q.bn * kTileM * sizeof(float) : 0;
     q.counter_bytes = (split > 1 && !q.cluster) ? size_t(base) * sizeof(unsigned int) : 0;
 }
 
@@ -1346,7 +1585,7 @@ cudaError_t conv_tc_prepare() {
 #undef IOS_FORMS
     };
     for (const void *form : forms) {
-        cudaError_t err = cudaFuncSetAttribute(form, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024);
+        cudaError_t err = cudaFuncSetAttribute(form, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
         if (err != cudaSuccess) return err;
     }
     const void *resident[] = {reinterpret_cast<const void *>(conv_tc_persistent_kernel<0>), reinterpret_cast<const void *>(conv_tc_persistent_kernel<1>),
@@ -1390,6 +1629,18 @@ void launch_conv_tc(const ConvTcParams &p, const ConvTcPlan &q, cudaStream_t str
     t.cout_pad = q.cout_pad;
     t.tma_store = q.tma_store;
     t.cluster = (q.split_k > 1 && q.cluster) ? 1 : 0;
+    t.push = (t.cluster && q.push) ? 1 : 0;
+    t.recv_off = q.recv_off;
+    t.split_shift = -1;
+    for (int sh = 0; sh < 8; ++sh)
+        if ((1 << sh) == q.split_k) t.split_shift = sh;
+    // multipliers for the prologue's divisions, where the dividend is small enough for them to be exact
+    auto magic = [](long n_max, int d) -> unsigned {
+        return (d > 1 && n_max * d < (1l << 32)) ? unsigned((1ull << 32) / unsigned(d)) + 1u : 0u;
+    };
+    t.magic_ow = magic(long(p.g.OH) * p.g.OW, p.g.OW);
+    t.magic_cc = magic(long(q.k_iters) + 64, q.cchunks);
+    t.magic_kw = magic(long(p.g.kh) * p.g.kw + 64, p.g.kw);
     cudaLaunchConfig_t cfg = {};
     PersistGeom pg = {};
     if (q.persistent) {

@@ -410,6 +410,7 @@ private:
         } else if (tc_wanted && conv_tc_supported(in, g)) {
             slot.impl = StepKind::ConvTc;
             slot.tcplan.no_persistent = plan_.options.no_persistent ? 1 : 0;
+            slot.tcplan.no_push = plan_.options.no_cluster_push ? 1 : 0;
             slot.tcplan.no_half_rows = plan_.options.no_half_rows ? 1 : 0;
             conv_tc_choose(g, sms_, width_, plan_.options.three_pass, &slot.tcplan, plan_.options.force_bn, plan_.options.bf16,
                            !plan_.options.no_im2col);
@@ -421,7 +422,7 @@ private:
             conv_tc_patch_consider(g, sms_, &slot.tcplan);
             slot.tcplan.pdl = plan_.options.pdl ? 1 : 0;
             slot.tcplan.max_producers = plan_.options.producers;
-            if (plan_.options.force_stages > 0 && !slot.tcplan.persistent && !slot.tcplan.patch) {   // testing aid: shallower pipeline
+            if (plan_.options.force_stages > 0 && !slot.tcplan.persistent && !slot.tcplan.patch && !slot.tcplan.push) {   // testing aid: shallower pipeline
                 ConvTcPlan &q = slot.tcplan;
                 const size_t stage_bytes = (q.smem_bytes - 24 * q.stages - 64 - 1024) / q.stages;   // (whatever the row width)
                 const int stages = std::max(2, std::min(q.stages, plan_.options.force_stages));

@@ -858,6 +858,7 @@ int ios_set_option(const char *key, const char *value) {
         else if (k == "bulk_store" && (v == "0" || v == "1")) g_options.no_bulk_store = v == "0";
         else if (k == "im2col" && (v == "0" || v == "1")) g_options.no_im2col = v == "0";
         else if (k == "persistent" && (v == "0" || v == "1")) g_options.no_persistent = v == "0";
+        else if (k == "cluster_push" && (v == "0" || v == "1")) g_options.no_cluster_push = v == "0";
         else if (k == "patch" && (v == "0" || v == "1" || v == "all")) {
             g_options.no_patch = v == "0";
             g_options.patch_all = v == "all";
@@ -883,6 +884,7 @@ int ios_get_option(const char *key, char *value, int capacity) {
         else if (k == "pdl_edges") v = g_options.pdl_edges ? "1" : "0";
         else if (k == "bulk_store") v = g_options.no_bulk_store ? "0" : "1";
         else if (k == "persistent") v = g_options.no_persistent ? "0" : "1";
+        else if (k == "cluster_push") v = g_options.no_cluster_push ? "0" : "1";
         else if (k == "patch") v = g_options.no_patch ? "0" : g_options.patch_all ? "all" : "1";
         else if (k == "executor") v = g_options.use_graph ? "graph" : "streams";
         else if (k == "conv") v = g_options.allow_tc ? "auto" : "direct";
@@ -1235,12 +1237,13 @@ int ios_engine_describe(ios_engine *engine, char *text, int capacity) {
         const EngineImpl &e = engine->impl;
         const Plan &p = e.plan;
         int n_tc = 0, n_direct = 0, n_dw = 0, n_sum = 0, n_pool = 0, n_split = 0, n_persistent = 0, n_half = 0, n_few = 0,
-            n_direct_store = 0, n_patch = 0;
+            n_direct_store = 0, n_patch = 0, n_push = 0;
         for (const Step &s : p.steps) {
             switch (s.kind) {
                 case StepKind::ConvTc:
                     ++n_tc;
                     if (s.tcplan.split_k > 1) ++n_split;
+                    if (s.tcplan.split_k > 1 && s.tcplan.cluster && s.tcplan.push) ++n_push;
                     if (s.tcplan.persistent) ++n_persistent;
                     if (s.tcplan.patch) ++n_patch;
                     if (s.tcplan.half_rows) ++n_half;
@@ -1260,13 +1263,13 @@ int ios_engine_describe(ios_engine *engine, char *text, int capacity) {
         const Op &out = p.model.ops[p.model.output];
         const Op &in = p.model.ops[p.model.placeholders[0]];
         std::snprintf(text, size_t(capacity),
-                      "{\"launches\": %d, \"conv_tc\": %d, \"conv_tc_split_k\": %d, \"conv_tc_persistent\": %d, "
+                      "{\"launches\": %d, \"conv_tc\": %d, \"conv_tc_split_k\": %d, \"conv_tc_cluster_push\": %d, \"conv_tc_persistent\": %d, "
                       "\"conv_tc_half_rows\": %d, \"conv_tc_patch\": %d, \"conv_tc_direct_store\": %d, \"conv_direct\": %d, \"conv_few_channels\": %d, "
                       "\"conv_depthwise\": %d, "
                       "\"sum_act\": %d, \"pool\": %d, \"stages\": %zu, \"arena_bytes\": %zu, \"workspace_bytes\": %zu, "
                       "\"weight_bytes\": %zu, \"conv_flops\": %.0f, \"output_shape\": [%d, %d, %d, %d], \"input_shape\": [%d, %d, %d, %d], \"executor\": \"%s\", "
                       "\"stage_barriers\": %d, \"pdl_edges\": %d, \"pdl_edges_applied\": %d, \"device\": %d, \"precision\": \"%s\"}",
-                      p.launches_per_forward, n_tc, n_split, n_persistent, n_half, n_patch, n_direct_store, n_direct, n_few, n_dw, n_sum,
+                      p.launches_per_forward, n_tc, n_split, n_push, n_persistent, n_half, n_patch, n_direct_store, n_direct, n_few, n_dw, n_sum,
                       n_pool, p.model.stages.size(), e.bytes,
                       p.workspace_bytes, weight_bytes, p.model.conv_flops(), p.model.batch, out.C, out.H, out.W,
                       p.model.batch, in.C, in.H, in.W,
