@@ -129,26 +129,40 @@ struct MmaRing {
 };
 
 template <int MODE, bool kTimeline>
-__device__ __forceinline__ bool mma_loop(int n_it, int stages, uint32_t wait0, uint32_t empty0, MmaRing &ring, uint32_t tmem_d,
-                                         uint32_t idesc, uint32_t idesc_wide, const ConvTcParams &p) {
+__device__ __forceinline__ bool mma_loop(int n_it, int stages, uint32_t wait0, uint32_t landed0, uint32_t empty0, MmaRing &ring,
+                                         uint32_t tmem_d, uint32_t idesc, uint32_t idesc_wide, const ConvTcParams &p) {
 #pragma unroll 1
     for (int i = 0; i < n_it; ++i) {
-        if (!mbar_wait(wait0 + 8u * ring.s, ring.phase, p.error_flag)) return false;
-        if (i == 0) STAMP(3);
-        tc_fence_after();
         const uint64_t da = ring.da, db = ring.db, dal = ring.dal, dbl = ring.dbl;
+        if (MODE == 1 || MODE == 3) {
+            // Three-pass mode: the products of the first activation tile as it landed (its TF32 value) start while
+            // the epilogue warps are still writing the tile's residual; only the residual's product waits for them.
+            // (Later tiles have their residual written while the tensor core is busy with the tile before: one wait.)
+            if (!mbar_wait((i == 0 ? landed0 : wait0) + 8u * ring.s, ring.phase, p.error_flag)) return false;
+            tc_fence_after();
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+                if (MODE == 3) {
+                    // a_hi*[w_hi | w_lo]: one instruction of twice the width
+                    umma_tf32(tmem_d, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc_wide, acc);
+                } else {
+                    umma_tf32(tmem_d, da + uint64_t(k * 2), dbl + uint64_t(k * 2), idesc, acc);
+                    umma_tf32(tmem_d, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, 1u);
+                }
+            }
+        }
+        if (!(MODE == 1 || MODE == 3) || i == 0) {
+            if (!mbar_wait(wait0 + 8u * ring.s, ring.phase, p.error_flag)) return false;
+            tc_fence_after();
+        }
+        if (i == 0) STAMP(3);
 #pragma unroll
         for (int k = 0; k < (MODE == 4 ? 2 : 4); ++k) {   // 32 bytes of K per instruction: 8 TF32 or 16 BF16; 64-byte rows: two
             const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
-            if (MODE == 3) {
-                // a*w ~= a_hi*[w_hi | w_lo] + a_lo*w_hi
-                umma_tf32(tmem_d, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc_wide, acc);
+            if (MODE == 1 || MODE == 3) {
+                // a_lo*w_hi
                 umma_tf32(tmem_d, dal + uint64_t(k * 2), db + uint64_t(k * 2), idesc, 1u);
-            } else if (MODE == 1) {
-                // a*w ~= a_lo*w_hi + a_hi*w_lo + a_hi*w_hi, small terms first
-                umma_tf32(tmem_d, dal + uint64_t(k * 2), db + uint64_t(k * 2), idesc, acc);
-                umma_tf32(tmem_d, da + uint64_t(k * 2), dbl + uint64_t(k * 2), idesc, 1u);
-                umma_tf32(tmem_d, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, 1u);
             } else if (MODE == 2 || MODE == 4) {
                 umma_f16(tmem_d, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, acc);
             } else {
@@ -199,6 +213,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const ConvGeom &g = p.g;
     if (threadIdx.x == 0) STAMP(0);
+    // The next kernel of the stream may start its prologue (on SMs this grid leaves free, or as CTAs leave) as soon
+    // as every CTA of this grid has got here; it reads nothing of ours before its own griddepcontrol.wait.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     {
         // Kernel parameters are new with every launch, so the first read of each of their cache lines misses.
         // One word of every line is asked for here, all at once, instead of one miss at a time where the
@@ -246,24 +263,57 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         push_rows = max(0, min(push_rpr, push_vrows - int(cluster_cta_rank()) * push_rpr));
     }
 
+    // Set-up is spread over three warps so that none of its chains follows another: warp 0 initialises the barriers
+    // and requests the weight tiles, warp 1 fetches the tensor maps and requests the activation tiles, warp 2
+    // allocates tensor memory.  The tiles of the first `stages` K steps are requested here, one lane per step (at
+    // batch 1 a CTA of a split-K cluster has no more steps than that); the rest of the set-up runs while they
+    // are on their way.
+    const int early = min(n_it, t.stages);
     if (warp == 0) {
-        // one lane per pipeline stage initialises its three barriers; lane 31 fetches the tensor maps
-        if (lane < t.stages) {
-            mbar_init(full0 + 8u * lane, 1);
-            mbar_init(empty0 + 8u * lane, 1);
-            mbar_init(ready0 + 8u * lane, 128);
+        // the barriers lie behind one another: full[stages], empty[stages], ready[stages], accumulator, (8 bytes
+        // of other use), receive -- lane i initialises the i-th of them
+        const int n_bars = 3 * t.stages + 3;
+        if (lane < n_bars && lane != 3 * t.stages + 1 && (push || lane != 3 * t.stages + 2))
+            mbar_init(bars + 8u * lane, (lane >= 2 * t.stages && lane < 3 * t.stages) ? 128u : 1u);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("bar.arrive 2, 64;" ::: "memory");         // warp 1 may use the barriers
+        // Weights never depend on the previous kernel: no grid dependency is waited for.  (Their bytes may be
+        // counted before warp 1 has announced them: the barrier's phase cannot end before that arrival.)
+        if (lane < early) {
+            const int it = it_begin + lane;
+            const uint32_t stage = smem_base + uint32_t(lane) * stage_bytes;
+            const uint32_t bar = full0 + 8u * lane;
+            tma_load_2d(stage + b_off, &tmap_b, bar, it * t.chunk, cout0);
+            if (kX3) tma_load_2d(stage + b_lo_off, &tmap_b, bar, it * t.chunk, t.cout_pad + cout0);
         }
-        if (lane == 30) mbar_init(accum_bar, 1);
-        if (lane == 29 && push) mbar_init(recv_bar, 1);
+        // the bytes this CTA will be sent: its rows of the partial tiles of all CTAs of the cluster
+        if (lane == 3 * t.stages + 2 && push) mbar_expect_tx(recv_bar, uint32_t(t.split_k * push_rows * t.bn) * 4u);
+    } else if (warp == 1) {
         if (lane == 31) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
             if (t.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_c) : "memory");
         }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        // the bytes this CTA will be sent: its rows of the partial tiles of all CTAs of the cluster
-        if (lane == 29 && push) mbar_expect_tx(recv_bar, uint32_t(t.split_k * push_rows * t.bn) * 4u);
+        int cc = 0, r = 0, sx = 0;
+        if (lane < early) {
+            const int it = it_begin + lane;
+            const int tap = div_by(it, t.cchunks, t.magic_cc);
+            cc = it - tap * t.cchunks;
+            r = div_by(tap, g.kw, t.magic_kw);
+            sx = tap - r * g.kw;
+        }
+        asm volatile("bar.sync 2, 64;" ::: "memory");           // the barriers exist
+        if (lane < early) {
+            const uint32_t stage = smem_base + uint32_t(lane) * stage_bytes;
+            const uint32_t bar = full0 + 8u * lane;
+            mbar_expect_tx(bar, uint32_t(t.a_bytes + passes * b_bytes));
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            if (t.im2col) tma_load_im2col(stage, &tmap_a, bar, cc * t.chunk, im_w, im_h, n0, uint32_t(sx), uint32_t(r));
+            else if (t.flat) tma_load_4d(stage, &tmap_a, bar, cc * t.chunk, ow0, 0, 0);
+            else tma_load_4d(stage, &tmap_a, bar, cc * t.chunk, ow0 * g.sw - g.pw + sx, oh0 * g.sh - g.ph + r, n0);
+            if (lane == 0) STAMP(2);
+        }
     }
     if (warp == 2) {
         tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), uint32_t(t.tmem_cols));
@@ -277,42 +327,14 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     if (push) cluster_arrive_relaxed();
     const uint32_t tmem_base = *tmem_slot;
     if (threadIdx.x == 0) STAMP(1);
-    // Everything above touches no global memory, so under programmatic dependent launch it overlaps
-    // the tail of the previous kernel; the next kernel may start its own prologue from here on.
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // Warps 0 and 1 work through a few lanes only.  Their other lanes leave now: a lane that spins on a
     // barrier pays about 50 cycles per wait while the rest of its warp is parked at the reconvergence point.
     // (Not in a cluster: there every thread takes part in the cluster barriers below.)
-    // Weights never depend on the previous kernel: the weight tiles of the first `stages` K steps are
-    // requested before the grid dependency is waited for, so that under programmatic dependent launch
-    // their latency hides behind the predecessor's tail -- one lane per stage, all at once.
-    if (warp == 2 && lane < min(n_it, t.stages)) {      // (an epilogue warp, idle at this point: warp 0 goes straight to the activations)
-        const uint32_t stage = smem_base + uint32_t(lane) * stage_bytes;
-        const uint32_t bar = full0 + 8u * lane;
-        mbar_expect_tx(bar, uint32_t(t.a_bytes + passes * b_bytes));
-        tma_load_2d(stage + b_off, &tmap_b, bar, (it_begin + lane) * t.chunk, cout0);
-        if (kX3) tma_load_2d(stage + b_lo_off, &tmap_b, bar, (it_begin + lane) * t.chunk, t.cout_pad + cout0);
-    }
-    if (!kCluster && ((warp == 0 && lane >= max(t.producers, min(n_it, t.stages))) || (warp == 1 && lane != 0))) return;
+    if (!kCluster && ((warp == 0 && lane >= t.producers) || (warp == 1 && lane != 0))) return;
 
     if (warp == 0) {
         // ---------------- TMA producers ----------------
-        // The activation tiles of the first `stages` K steps go out at once, one lane per step (at batch 1
-        // a CTA of a split-K cluster has no more steps than that); their weight tiles are on their way.
-        const int early = min(n_it, t.stages);
-        if (lane < early) {
-            const int it = it_begin + lane;
-            const int tap = div_by(it, t.cchunks, t.magic_cc), cc = it - tap * t.cchunks;
-            const int r = div_by(tap, g.kw, t.magic_kw), sx = tap - r * g.kw;
-            const uint32_t stage = smem_base + uint32_t(lane) * stage_bytes;
-            const uint32_t bar = full0 + 8u * lane;
-            asm volatile("griddepcontrol.wait;" ::: "memory");
-            if (t.im2col) tma_load_im2col(stage, &tmap_a, bar, cc * t.chunk, im_w, im_h, n0, uint32_t(sx), uint32_t(r));
-            else if (t.flat) tma_load_4d(stage, &tmap_a, bar, cc * t.chunk, ow0, 0, 0);
-            else tma_load_4d(stage, &tmap_a, bar, cc * t.chunk, ow0 * g.sw - g.pw + sx, oh0 * g.sh - g.ph + r, n0);
-            if (lane == 0) STAMP(2);
-        }
-        if (!kCluster && lane >= t.producers) return;
+        // (the tiles of the first `stages` K steps were requested during set-up)
         if (lane < t.producers && n_it > t.stages) {
             // One thread gets through wait -> arm -> issue about once per 600-800 cycles, whatever the
             // tiles' size, so `producers` lanes share the remaining K steps: lane l serves steps l + stages,
@@ -373,7 +395,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const uint32_t idesc_wide = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(t.bn >> 2) << 17) | (uint32_t(kTileM >> 4) << 24);
             MmaRing ring;
             ring.start(smem_base, a_lo_off, b_off, b_lo_off, stage_bytes, kRow);
-#define IOS_MMA_LOOP(FORM, WAIT) mma_loop<FORM, kTimeline>(n_it, t.stages, WAIT, empty0, ring, tmem_base, idesc, idesc_wide, p)
+#define IOS_MMA_LOOP(FORM, WAIT) mma_loop<FORM, kTimeline>(n_it, t.stages, WAIT, full0, empty0, ring, tmem_base, idesc, idesc_wide, p)
             const bool ok = kX3 ? (t.wide ? IOS_MMA_LOOP(3, ready0) : IOS_MMA_LOOP(1, ready0))
                                  : (kBf16 ? IOS_MMA_LOOP(MODE, full0) : IOS_MMA_LOOP(0, full0));
 #undef IOS_MMA_LOOP
@@ -1030,7 +1052,7 @@ conv_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             if (!ok) break;
             tc_fence_after();
             const uint32_t tmem_d = tmem_base + a * uint32_t(pg.acc_stride);
-#define IOS_MMA_LOOP(FORM, WAIT) mma_loop<FORM, false>(t.k_iters, t.stages, WAIT, empty0, ring, tmem_d, idesc, idesc_wide, p)
+#define IOS_MMA_LOOP(FORM, WAIT) mma_loop<FORM, false>(t.k_iters, t.stages, WAIT, full0, empty0, ring, tmem_d, idesc, idesc_wide, p)
             ok = kX3 ? (t.wide ? IOS_MMA_LOOP(3, ready0) : IOS_MMA_LOOP(1, ready0))
                       : (kBf16 ? IOS_MMA_LOOP(MODE, full0) : IOS_MMA_LOOP(0, full0));
 #undef IOS_MMA_LOOP
