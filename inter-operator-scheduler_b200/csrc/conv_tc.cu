@@ -72,6 +72,8 @@ struct TileGeom {
     int producers;    // lanes of warp 0 that issue TMA loads; divides `stages`
     int wide;         // 1: (three-pass mode, bn <= 128) one instruction of width 2 bn covers the weight tile and its
                       //    residual; the residual's products accumulate in columns [bn, 2 bn)
+    int dual;         // 1: (three-pass mode, wide) a second thread issues the products with the activation residual into an
+                      //    accumulator of its own, columns [2 bn, 3 bn)
     int split_shift;  // log2(split_k) when it is a power of two, else -1
     unsigned magic_ow, magic_cc, magic_kw;   // division by OW / cchunks / kw as a multiplication (0: divide)
     int push;         // 1: (cluster) partial tiles are pushed into the shared memory of the CTA that finishes their rows
@@ -179,6 +181,28 @@ __device__ __forceinline__ bool mma_loop(int n_it, int stages, uint32_t wait0, u
     return true;
 }
 
+// Three-pass mode with two issuing threads: each runs this loop over its own pair of operand planes and its own
+// accumulator, so neither waits for the other's instructions to be issued (one thread gets a tcgen05.mma out
+// about every 90 cycles, whatever its width).  Both hand a stage back; the producer waits for the two of them.
+template <bool kTimeline>
+__device__ __forceinline__ bool mma_loop_planes(int n_it, int stages, uint32_t wait0, uint32_t empty0, uint64_t da0, uint64_t db0,
+                                                uint64_t dstep, uint32_t tmem_d, uint32_t idesc, const ConvTcParams &p, bool stamp) {
+    uint64_t da = da0, db = db0;
+    uint32_t s = 0, phase = 0;
+#pragma unroll 1
+    for (int i = 0; i < n_it; ++i) {
+        if (!mbar_wait(wait0 + 8u * s, phase, p.error_flag)) return false;
+        if (i == 0 && stamp) STAMP(3);
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 4; ++k) umma_tf32(tmem_d, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+        umma_commit(empty0 + 8u * s);
+        da += dstep; db += dstep;
+        if (++s == uint32_t(stages)) { s = 0; phase ^= 1u; da = da0; db = db0; }
+    }
+    return true;
+}
+
 // ---- the kernel ------------------------------------------------------------------------------
 // One instantiation per operand mode (0: TF32, 1: three-pass TF32, 2: BF16, 4: BF16 with 64-byte operand rows)
 // and per reduction form
@@ -269,12 +293,16 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // batch 1 a CTA of a split-K cluster has no more steps than that); the rest of the set-up runs while they
     // are on their way.
     const int early = min(n_it, t.stages);
+    const bool dual = kX3 && t.dual != 0;
     if (warp == 0) {
         // the barriers lie behind one another: full[stages], empty[stages], ready[stages], accumulator, (8 bytes
         // of other use), receive -- lane i initialises the i-th of them
         const int n_bars = 3 * t.stages + 3;
-        if (lane < n_bars && lane != 3 * t.stages + 1 && (push || lane != 3 * t.stages + 2))
-            mbar_init(bars + 8u * lane, (lane >= 2 * t.stages && lane < 3 * t.stages) ? 128u : 1u);
+        if (lane < n_bars && lane != 3 * t.stages + 1 && (push || lane != 3 * t.stages + 2)) {
+            // arrivals per phase: the split's 128 threads on `ready`; both issuers on `empty` and on the accumulator's
+            const bool both = dual && ((lane >= t.stages && lane < 2 * t.stages) || lane == 3 * t.stages);
+            mbar_init(bars + 8u * lane, (lane >= 2 * t.stages && lane < 3 * t.stages) ? 128u : (both ? 2u : 1u));
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("bar.arrive 2, 64;" ::: "memory");         // warp 1 may use the barriers
@@ -330,7 +358,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // Warps 0 and 1 work through a few lanes only.  Their other lanes leave now: a lane that spins on a
     // barrier pays about 50 cycles per wait while the rest of its warp is parked at the reconvergence point.
     // (Not in a cluster: there every thread takes part in the cluster barriers below.)
-    if (!kCluster && ((warp == 0 && lane >= t.producers) || (warp == 1 && lane != 0))) return;
+    if (!kCluster && ((warp == 0 && lane >= t.producers) || (warp == 1 && lane != 0) || (warp == 6 && (lane != 0 || !dual)))) return;
+    if (!kCluster && !kX3 && warp >= 7) return;
 
     if (warp == 0) {
         // ---------------- TMA producers ----------------
@@ -396,15 +425,64 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             MmaRing ring;
             ring.start(smem_base, a_lo_off, b_off, b_lo_off, stage_bytes, kRow);
 #define IOS_MMA_LOOP(FORM, WAIT) mma_loop<FORM, kTimeline>(n_it, t.stages, WAIT, full0, empty0, ring, tmem_base, idesc, idesc_wide, p)
-            const bool ok = kX3 ? (t.wide ? IOS_MMA_LOOP(3, ready0) : IOS_MMA_LOOP(1, ready0))
-                                 : (kBf16 ? IOS_MMA_LOOP(MODE, full0) : IOS_MMA_LOOP(0, full0));
+            // (two issuers: this one forms a_hi*[w_hi | w_lo] from the tiles as they land)
+            const bool ok = dual ? mma_loop_planes<kTimeline>(n_it, t.stages, full0, empty0, ring.da0, ring.db0, ring.dstep, tmem_base,
+                                                              idesc_wide, p, true)
+                            : kX3 ? (t.wide ? IOS_MMA_LOOP(3, ready0) : IOS_MMA_LOOP(1, ready0))
+                                  : (kBf16 ? IOS_MMA_LOOP(MODE, full0) : IOS_MMA_LOOP(0, full0));
 #undef IOS_MMA_LOOP
             if (ok) umma_commit(accum_bar);
             else atomicExch(p.error_flag, 2);
             STAMP(4);
         }
+    } else if (warp == 6) {
+        if (lane == 0 && dual) {
+            // ---------------- second MMA issuer (three-pass mode): a_lo*w_hi, once the residual of a tile is written ----------------
+            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(t.bn >> 3) << 17) | (uint32_t(kTileM >> 4) << 24);
+            const bool ok = mma_loop_planes<kTimeline>(n_it, t.stages, ready0, empty0, smem_desc_kmajor(smem_base + a_lo_off, kRow),
+                                                       smem_desc_kmajor(smem_base + b_off, kRow), uint64_t(stage_bytes >> 4),
+                                                       tmem_base + 2u * uint32_t(t.bn), idesc, p, false);
+            if (ok) umma_commit(accum_bar);
+            else atomicExch(p.error_flag, 2);
+        }
+    } else if (warp >= 7) {
+        // ---------------- warps 7..10 (three-pass mode): the residual of every landed activation tile ----------------
+        if (kX3) {
+            const int tid = threadIdx.x - 224;          // 0..127
+            // The tensor core reads the 19 leading bits of an fp32 operand (sign, exponent, 10 mantissa
+            // bits), so the landed activation tile serves as the TF32 value as it is.  What the hardware
+            // drops -- x minus x with the low 13 bits cleared, exact in fp32 -- is written to the residual
+            // tile here.  (Weights are split on the host into two planes; deriving their residual here too
+            // was measured 7-15 % slower: this step sits on the latency chain TMA -> split -> MMA.)
+            const int n_vec = t.a_bytes >> 4;
+            int s = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+#pragma unroll 1
+            for (int i = 0; i < n_it && ok; ++i) {
+                ok = mbar_wait(full0 + 8u * s, phase, p.error_flag);
+                if (!ok) break;
+                uint8_t *stage = generic_base + size_t(s) * stage_bytes;
+                const float4 *hi = reinterpret_cast<const float4 *>(stage);
+                float4 *lo = reinterpret_cast<float4 *>(stage + a_lo_off);
+#pragma unroll 2
+                for (int v = tid; v < n_vec; v += 128) {
+                    const float4 x = hi[v];
+                    float4 l;
+                    l.x = x.x - __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u);
+                    l.y = x.y - __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u);
+                    l.z = x.z - __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u);
+                    l.w = x.w - __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u);
+                    lo[v] = l;
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(ready0 + 8u * s) : "memory");
+                if (++s == t.stages) { s = 0; phase ^= 1u; }
+            }
+            if (!ok && lane == 0) atomicExch(p.error_flag, 5);
+        }
     } else {
-        // ---------------- warps 2..5: operand split (3-pass mode), then the epilogue ----------------
+        // ---------------- warps 2..5: the epilogue ----------------
         const int tid = threadIdx.x - 64;           // 0..127
         const int quad = warp & 3;                  // TMEM lane group this warp may read
         const int row = quad * 32 + lane;
@@ -474,37 +552,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (threadIdx.x == 64) STAMP(15);
         };
         bool ok = true;
-        if (kX3) {
-            // The tensor core reads the 19 leading bits of an fp32 operand (sign, exponent, 10 mantissa
-            // bits), so the landed activation tile serves as the TF32 value as it is.  What the hardware
-            // drops -- x minus x with the low 13 bits cleared, exact in fp32 -- is written to the residual
-            // tile here.  (Weights are split on the host into two planes; deriving their residual here too
-            // was measured 7-15 % slower: this step sits on the latency chain TMA -> split -> MMA.)
-            const int n_vec = t.a_bytes >> 4;
-            int s = 0;
-            uint32_t phase = 0;
-#pragma unroll 1
-            for (int i = 0; i < n_it && ok; ++i) {
-                ok = mbar_wait(full0 + 8u * s, phase, p.error_flag);
-                if (!ok) break;
-                uint8_t *stage = generic_base + size_t(s) * stage_bytes;
-                const float4 *hi = reinterpret_cast<const float4 *>(stage);
-                float4 *lo = reinterpret_cast<float4 *>(stage + a_lo_off);
-#pragma unroll 2
-                for (int v = tid; v < n_vec; v += 128) {
-                    const float4 x = hi[v];
-                    float4 l;
-                    l.x = x.x - __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u);
-                    l.y = x.y - __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u);
-                    l.z = x.z - __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u);
-                    l.w = x.w - __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u);
-                    lo[v] = l;
-                }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(ready0 + 8u * s) : "memory");
-                if (++s == t.stages) { s = 0; phase ^= 1u; }
-            }
-        }
         if (kCluster && push) prepare_rows();
         if (ok) ok = mbar_wait(accum_bar, 0, p.error_flag);
         ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
@@ -515,6 +562,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (threadIdx.x == 64) STAMP(9);
         const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16);
         const uint32_t pair = t.wide ? uint32_t(t.bn) : 0u;
+        const uint32_t third = dual ? 2u * uint32_t(t.bn) : 0u;
         const int tile_id = m_tile * gridDim.y + n_tile;
         bool finisher = true;
         if (kCluster && push) {
@@ -527,7 +575,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll 1
                 for (int c = 0; c < t.bn; c += 32) {
                     float v[32];
-                    acc_ld32_pair(taddr + c, pair, v);
+                    acc_ld32_pair(taddr + c, pair, v, third);
                     if (push_mine) {
 #pragma unroll
                         for (int j = 0; j < 32; j += 4)
@@ -629,7 +677,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll 1
                 for (int c = 0; c < t.bn; c += 32) {
                     float v[32];
-                    acc_ld32(taddr + c, pair, v);
+                    acc_ld32(taddr + c, pair, v, third);
 #pragma unroll
                     for (int j = 0; j < 32; j += 4)
                         ws[size_t((c + j) >> 2) * kTileM] = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
@@ -642,7 +690,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll 1
             for (int c = 0; c < t.bn; c += 16) {
                 float v[16];
-                acc_ld16(taddr + c, pair, v);
+                acc_ld16(taddr + c, pair, v, third);
 #pragma unroll
                 for (int j = 0; j < 16; ++j) ws[size_t(c + j) * kTileM + row] = v[j];
             }
@@ -675,7 +723,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll 1
                 for (int c = 0; c < t.bn; c += 32) {
                     float v[32];
-                    acc_ld32(taddr + c, pair, v);
+                    acc_ld32(taddr + c, pair, v, third);
 #pragma unroll
                     for (int j = 0; j < 32; j += 4) {
                         float o[4];
@@ -692,7 +740,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             for (int c = 0; c < t.bn; c += 16) {
                 float v[16];
                 if (t.split_k == 1) {
-                    acc_ld16(taddr + c, pair, v);
+                    acc_ld16(taddr + c, pair, v, third);
                     if (c == 0 && threadIdx.x == 64) STAMP(13);
                 } else {
 #pragma unroll
@@ -768,8 +816,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
     if (kCluster) {
         if (push) {
-            // warps 0 and 1 pair their arrival at the set-up barrier with a wait and leave
-            if (warp < 2) {
+            // the warps of the single-thread roles pair their arrival at the set-up barrier with a wait and leave
+            if (warp < 2 || warp >= 6) {
                 __syncwarp();
                 cluster_wait();
                 return;
@@ -781,7 +829,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             cluster_sync_all();
         }
         if (threadIdx.x == 64) STAMP(10);
-        if (warp >= 2) {
+        if (warp >= 2 && warp < 6) {
             // CTA r of the cluster finishes rows [r*128/S, (r+1)*128/S) of the tile: it adds the S partial
             // tiles in split order (so the result does not depend on timing), applies bias and activation
             // and writes its rows.  A thread puts all its loads in flight before it adds anything.
@@ -863,7 +911,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (threadIdx.x == 64) STAMP(7);
         }
     }
-    if (warp < 2 || kCluster) return;   // the producer lanes and the MMA issuer have nothing left to do
+    if (warp < 2 || warp >= 6 || kCluster) return;   // the producer lanes, the MMA issuers and the residual warps have nothing left to do
     // warps 0 and 1 are gone by now or on their way out; the warps that read the accumulator free it
     asm volatile("bar.sync 1, 128;" ::: "memory");
     if (warp == 2) {
@@ -1643,8 +1691,11 @@ void launch_conv_tc(const ConvTcParams &p, const ConvTcPlan &q, cudaStream_t str
     t.chunk = (q.bf16 && !q.half_rows) ? 64 : 32;
     t.slab = q.bf16 ? 64 : 32;
     t.wide = (q.x3 && q.bn <= 128) ? 1 : 0;
+    // two issuers (three accumulator ranges) when tensor memory has room: this kernel has the SM's to itself
+    // unless a second CTA shares the SM, and then 3 x bn columns of each must fit side by side
+    t.dual = (t.wide && !q.persistent && !q.no_dual && 3 * q.bn <= ((q.split_k > 1 && q.cluster) ? 512 : 256)) ? 1 : 0;
     int cols = 32;
-    while (cols < (t.wide ? 2 : 1) * q.bn) cols *= 2;   // the wide form keeps a second accumulator range
+    while (cols < (t.dual ? 3 : t.wide ? 2 : 1) * q.bn) cols *= 2;   // the wide form keeps a second accumulator range
     t.tmem_cols = cols;
     t.round_tf32 = p.g.round_out;
     t.x3 = q.x3;
@@ -1677,7 +1728,7 @@ void launch_conv_tc(const ConvTcParams &p, const ConvTcPlan &q, cudaStream_t str
         cfg.blockDim = dim3(kPersistThreads);
     } else {
         cfg.gridDim = dim3(q.tiles_w * q.tiles_h * q.tiles_n, q.n_tiles, q.split_k);
-        cfg.blockDim = dim3(kThreads);
+        cfg.blockDim = dim3(q.x3 ? kThreads : 192);     // (warps 6..10 have work in three-pass mode only)
     }
     cfg.dynamicSmemBytes = q.smem_bytes;
     cfg.stream = stream;

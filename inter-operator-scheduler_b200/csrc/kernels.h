@@ -132,6 +132,7 @@ struct ConvTcPlan {
     int pdl;                       // 1: launch with programmatic stream serialization
     int cluster;                   // 1: a K split of up to 8 is reduced inside a thread-block cluster
     int push;                      // 1: (cluster) partial tiles are pushed into the shared memory of the CTA that finishes their rows
+    int no_dual;                   // testing aid: three-pass mode issues all products from one thread
     int no_push;                   // testing aid: the cluster reduction always goes through the workspace in L2
     int recv_off;                  // byte offset of the area the pushes land in
     int bf16;                      // 1: bfloat16 operands and activations (kind::f16), 0: float32 storage (kind::tf32)

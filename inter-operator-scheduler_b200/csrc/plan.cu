@@ -411,6 +411,7 @@ private:
             slot.impl = StepKind::ConvTc;
             slot.tcplan.no_persistent = plan_.options.no_persistent ? 1 : 0;
             slot.tcplan.no_push = plan_.options.no_cluster_push ? 1 : 0;
+            slot.tcplan.no_dual = plan_.options.no_dual_issue ? 1 : 0;
             slot.tcplan.no_half_rows = plan_.options.no_half_rows ? 1 : 0;
             conv_tc_choose(g, sms_, width_, plan_.options.three_pass, &slot.tcplan, plan_.options.force_bn, plan_.options.bf16,
                            !plan_.options.no_im2col);

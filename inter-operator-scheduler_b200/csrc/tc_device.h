@@ -14,7 +14,7 @@ constexpr int kTileM = 128;          // TMEM lanes = pixel rows per CTA
 constexpr int kRowBytes = 128;       // K bytes per pipeline step = one 128-byte swizzle row (32 floats or 64 bf16)
 constexpr int kChunk = 32;           // float32 elements per row
 constexpr int kATileBytes = kTileM * kRowBytes;    // 16 KiB
-constexpr int kThreads = 192;
+constexpr int kThreads = 352;          // producer warp, MMA issuer, four epilogue warps; three-pass mode: second MMA issuer, four residual warps
 constexpr uint64_t kWaitBudgetNs = 2000000000ull;  // 2 s per wait
 
 // ---- PTX wrappers ----------------------------------------------------------------------------
@@ -191,7 +191,9 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float *v) {
 }
 // Accumulator columns [c, c + N) of this thread's lane; in three-pass mode the products with the weight
 // residual accumulate in a second column range `pair` columns further on and are added here.
-__device__ __forceinline__ void acc_ld32(uint32_t taddr, uint32_t pair, float *v) {
+// (`third`: a further range at that offset, where the products with the activation residual have an accumulator
+// of their own because a second thread issues them)
+__device__ __forceinline__ void acc_ld32(uint32_t taddr, uint32_t pair, float *v, uint32_t third = 0) {
     tmem_ld32(taddr, v);
     if (pair) {
         float w[32];
@@ -199,11 +201,38 @@ __device__ __forceinline__ void acc_ld32(uint32_t taddr, uint32_t pair, float *v
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] += w[i];
     }
+    if (third) {
+        float w[32];
+        tmem_ld32(taddr + third, w);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] += w[i];
+    }
 }
 // The same with both column ranges requested before either is waited for.
-__device__ __forceinline__ void acc_ld32_pair(uint32_t taddr, uint32_t pair, float *v) {
+__device__ __forceinline__ void acc_ld32_pair(uint32_t taddr, uint32_t pair, float *v, uint32_t third = 0) {
     if (!pair) {
         tmem_ld32(taddr, v);
+        return;
+    }
+    if (third) {
+        // three ranges: all requested before any is waited for; added in a fixed order
+        uint32_t r[32], w[32], x[32];
+#define IOS_LD32(dst, addr)                                                                                              \
+        asm volatile(                                                                                                    \
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, " \
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"                 \
+            : "=r"(dst[0]), "=r"(dst[1]), "=r"(dst[2]), "=r"(dst[3]), "=r"(dst[4]), "=r"(dst[5]), "=r"(dst[6]), "=r"(dst[7]), \
+              "=r"(dst[8]), "=r"(dst[9]), "=r"(dst[10]), "=r"(dst[11]), "=r"(dst[12]), "=r"(dst[13]), "=r"(dst[14]), "=r"(dst[15]), \
+              "=r"(dst[16]), "=r"(dst[17]), "=r"(dst[18]), "=r"(dst[19]), "=r"(dst[20]), "=r"(dst[21]), "=r"(dst[22]), "=r"(dst[23]), \
+              "=r"(dst[24]), "=r"(dst[25]), "=r"(dst[26]), "=r"(dst[27]), "=r"(dst[28]), "=r"(dst[29]), "=r"(dst[30]), "=r"(dst[31]) \
+            : "r"(addr))
+        IOS_LD32(r, taddr);
+        IOS_LD32(w, taddr + pair);
+        IOS_LD32(x, taddr + third);
+#undef IOS_LD32
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = (__uint_as_float(r[i]) + __uint_as_float(w[i])) + __uint_as_float(x[i]);
         return;
     }
     uint32_t r[32], w[32];
@@ -227,11 +256,17 @@ __device__ __forceinline__ void acc_ld32_pair(uint32_t taddr, uint32_t pair, flo
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) + __uint_as_float(w[i]);
 }
-__device__ __forceinline__ void acc_ld16(uint32_t taddr, uint32_t pair, float *v) {
+__device__ __forceinline__ void acc_ld16(uint32_t taddr, uint32_t pair, float *v, uint32_t third = 0) {
     tmem_ld16(taddr, v);
     if (pair) {
         float w[16];
         tmem_ld16(taddr + pair, w);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] += w[i];
+    }
+    if (third) {
+        float w[16];
+        tmem_ld16(taddr + third, w);
 #pragma unroll
         for (int i = 0; i < 16; ++i) v[i] += w[i];
     }

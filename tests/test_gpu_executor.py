@@ -21,7 +21,7 @@ pytestmark = pytest.mark.gpu
 
 DEFAULTS = (('precision', 'tf32x3'), ('pdl', '1'), ('executor', 'graph'), ('conv', 'auto'), ('split_k', '0'),
             ('im2col', '1'), ('persistent', '1'), ('stem', '1'), ('bulk_store', '1'), ('stage_barriers', '1'),
-            ('pdl_edges', '0'))
+            ('pdl_edges', '0'), ('cluster_push', '1'), ('dual_issue', '1'))
 
 
 @pytest.fixture(autouse=True)
@@ -106,6 +106,40 @@ def test_plain_stores_equal_bulk_tensor_stores(golden):
         b = rng.standard_normal(cout).astype(np.float32) * 0.1
         ref = oracle.conv2d_numpy(xs, wt, b, (1, 1), (1, 1), 1, 'relu')
         assert oracle.max_rel_err(rt.conv2d(xs, wt, b, padding=(1, 1), act='relu', impl='tensor'), ref) <= TOL_FP32
+
+
+@pytest.mark.parametrize('precision,tol', [('tf32x3', TOL_FP32), ('tf32', TOL_TF32), ('bf16', 2e-2)])
+def test_split_k_exchange_and_issue_variants(precision, tol):
+    """Split-K clusters: partial tiles pushed through shared memory (default) or exchanged through the workspace in L2 give
+    the same bits; three-pass products issued by two threads or by one agree with the oracle.  Covers full tiles, a
+    ragged last tile (17 x 17 = 289 pixels), a tile of 64 valid rows (8 x 8), wide tiles and every cluster size."""
+    rt.set_option('precision', precision)
+    rng = np.random.default_rng(11)
+    shapes = [(1, 768, 17, 17, 192, 1, 0), (1, 2048, 8, 8, 320, 1, 0), (1, 448, 8, 8, 384, 3, 1), (1, 288, 35, 35, 64, 1, 0),
+              (2, 160, 17, 17, 192, 3, 1), (1, 1280, 8, 8, 448, 1, 0), (1, 96, 9, 9, 40, 3, 1)]
+    for n, cin, h, w, cout, k, pad in shapes:
+        xs = rng.standard_normal((n, cin, h, w)).astype(np.float32)
+        wt = (rng.standard_normal((cout, cin, k, k)) / np.sqrt(k * k * cin)).astype(np.float32)
+        b = rng.standard_normal(cout).astype(np.float32) * 0.1
+        ref = oracle.conv2d_numpy(xs, wt, b, (1, 1), (pad, pad), 1, 'relu')
+        for split in ('0', '2', '4', '8', '3'):
+            rt.set_option('split_k', split)
+            outs = {}
+            for push in ('1', '0'):
+                for dual in ('1', '0'):
+                    rt.set_option('cluster_push', push)
+                    rt.set_option('dual_issue', dual)
+                    y = rt.conv2d(xs, wt, b, padding=(pad, pad), act='relu', impl='tensor')
+                    bound = 2 * tol if (precision == 'tf32x3' and k * k * cin > 2000) else tol    # long sums in fp32
+                    assert oracle.max_rel_err(y, ref) <= bound, (precision, (n, cin, h, w, cout, k), split, push, dual)
+                    outs[(push, dual)] = y
+            for dual in ('1', '0'):
+                assert np.array_equal(outs[('1', dual)], outs[('0', dual)]), ('exchange changes bits', (n, cin, h, w, cout, k), split, dual)
+            # the same call again: the result does not depend on timing
+            rt.set_option('cluster_push', '1')
+            rt.set_option('dual_issue', '1')
+            again = rt.conv2d(xs, wt, b, padding=(pad, pad), act='relu', impl='tensor')
+            assert np.array_equal(again, outs[('1', '1')])
 
 
 @pytest.mark.parametrize('precision,tol', [('tf32x3', TOL_FP32), ('bf16', 2e-2), ('fp32', TOL_FP32)])
