@@ -1358,7 +1358,7 @@ void conv_tc_choose(const ConvGeom &g, int sm_count, int concurrency_hint, bool 
     }
     // cycles; fitted to a sweep of tile width x split over the 43 distinct Inception-v3 layers at batch 1 and 64
     const double kFixed = 3000.0, kIssue = 450.0, kIssueThreePass = 700.0, kFillBytesPerCycle = 60.0, kEpiloguePerColumn = 36.0,
-                 kClusterOverhead = 3000.0, kTensorPerColumn = 2.1 * 1.15;
+                 kClusterOverhead = 2000.0, kTensorPerColumn = 2.1 * 1.15;
     const int planes = q.x3 ? 2 : 1;
     const int share = std::max(1, concurrency_hint);
     double best_cost = 1e30;

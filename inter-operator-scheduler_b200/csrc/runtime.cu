@@ -359,10 +359,12 @@ void check_error_flag(const Plan &plan, char *base) {
     if (plan.options.timeline) {
         long long stamps[16];
         CUDA_OK(cudaMemcpy(stamps, base + plan.error_flag_offset + 64, sizeof stamps, cudaMemcpyDeviceToHost));
-        std::fprintf(stderr, "conv_tc timeline (SM cycles since entry): setup %lld, first load issued %lld, first tile landed %lld, "
-                     "last mma issued %lld, accumulator ready %lld, bias ready %lld, partial published %lld, tile staged %lld, "
-                     "staging fenced %lld, stores issued %lld, epilogue done %lld, tmem freed %lld; first chunk: loaded %lld, "
-                     "finished %lld, staged %lld\n",
+        // (slots 10-12 mean "staged / fenced / stores issued" in the bulk-store epilogue and "partials received / loaded /
+        //  first rows stored" in the cluster reduction; 8 and 13-15 are the cluster epilogue's preparation steps)
+        std::fprintf(stderr, "conv_tc timeline (SM cycles since entry): setup %lld, first load issued %lld, first tile usable %lld, "
+                     "last mma issued %lld, accumulator ready %lld, bias ready %lld, partial handed over %lld, staged|received %lld, "
+                     "fenced|loaded %lld, stores issued|first rows stored %lld, epilogue done %lld, tmem freed|preparation begins %lld; "
+                     "first chunk loaded|barriers seen %lld, finished|pushes prepared %lld, staged|rows prepared %lld\n",
                      stamps[1] - stamps[0], stamps[2] - stamps[0], stamps[3] - stamps[0], stamps[4] - stamps[0],
                      stamps[5] - stamps[0], stamps[9] - stamps[0], stamps[6] - stamps[0], stamps[10] - stamps[0],
                      stamps[11] - stamps[0], stamps[12] - stamps[0], stamps[7] - stamps[0], stamps[8] - stamps[0],
