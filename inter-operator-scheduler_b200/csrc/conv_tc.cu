@@ -287,6 +287,56 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         push_rows = max(0, min(push_rpr, push_vrows - int(cluster_cta_rank()) * push_rpr));
     }
 
+    // Push form: one "item" is four output channels of one of the rows this CTA finishes.  Its position in the
+    // receive area, its place in the output and its bias are worked out ahead of time (prepare_item); once the
+    // rows have been received, finish_item adds the cluster's partial sums in split order and stores.
+    auto prepare_item = [&](int item, int &src, long &at, int &count, float4 &bias) {
+        src = -1;
+        at = -1;
+        count = 0;
+        bias = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (item >= push_rows * (t.bn >> 2)) return;
+        const int r0 = int(cluster_cta_rank()) * push_rpr;
+        const int valid = min(t.bn, g.Cout - cout0);
+        const int q4 = div_pow2_likely(item, push_rows), lr = item - q4 * push_rows, c = q4 << 2;
+        src = q4 * push_rpr + lr;
+        const long pix = long(ow0) + r0 + lr;
+        const long pix_off = t.flat ? ((r0 + lr < t.box_w && pix < long(g.N) * g.OH * g.OW) ? pix * p.out.pitch : -1)
+                                    : boxed_pixel_offset(r0 + lr, t.box_w, t.box_h, t.box_n, ow0, oh0, n0, g.N, g.OH, g.OW, p.out.pitch);
+        if (pix_off >= 0 && c < valid) {
+            at = pix_off + cout0 + c;
+            count = valid - c;
+            // (straight from global memory: the loads are in flight until the sums need them)
+            float b[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) b[j] = (p.bias && c + j < valid) ? __ldg(p.bias + cout0 + c + j) : 0.0f;
+            bias = make_float4(b[0], b[1], b[2], b[3]);
+        }
+    };
+    auto finish_item = [&](auto split_tag, int src, long at, int count, const float4 &bias) {
+        constexpr int S = decltype(split_tag)::value;
+        const float4 *recv = reinterpret_cast<const float4 *>(generic_base + t.recv_off);
+        const int plane = (t.bn >> 2) * push_rpr;           // float4 from one partial tile to the next
+        float4 part[S];
+#pragma unroll
+        for (int sp = 0; sp < S; ++sp) part[sp] = recv[max(src, 0) + sp * plane];
+        float4 acc = part[0];
+#pragma unroll
+        for (int sp = 1; sp < S; ++sp) {
+            acc.x += part[sp].x; acc.y += part[sp].y; acc.z += part[sp].z; acc.w += part[sp].w;
+        }
+        float o[4] = {acc.x + bias.x, acc.y + bias.y, acc.z + bias.z, acc.w + bias.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            o[j] = act_apply(o[j], g.act);
+            if (t.round_tf32) o[j] = round_tf32(o[j]);
+        }
+        if (at >= 0) store4_direct(p.out.ptr, kBf16, at, make_float4(o[0], o[1], o[2], o[3]), count);
+    };
+    // Splits of 2, 4 and 8 have an unrolled form; three-pass mode has four more warps (those of the residual) that
+    // take the second 128 items, so that a thread of either group has one item.
+    const bool fast_split = t.split_k == 8 || t.split_k == 4 || t.split_k == 2;
+
     // Set-up is spread over three warps so that none of its chains follows another: warp 0 initialises the barriers
     // and requests the weight tiles, warp 1 fetches the tensor maps and requests the activation tiles, warp 2
     // allocates tensor memory.  The tiles of the first `stages` K steps are requested here, one lane per step (at
@@ -479,7 +529,31 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(ready0 + 8u * s) : "memory");
                 if (++s == t.stages) { s = 0; phase ^= 1u; }
             }
+            ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
             if (!ok && lane == 0) atomicExch(p.error_flag, 5);
+            if (kCluster && push) {
+                // These warps are free now: each thread finishes one of the second 128 items of this CTA's rows.
+                cluster_wait();                                 // (pairs with the arrival at set-up)
+                int src, count;
+                long at;
+                float4 bias;
+                prepare_item(128 + tid, src, at, count, bias);
+                bool good = ok;
+                if (good && fast_split && push_rows > 0)
+                    good = __all_sync(0xffffffffu, mbar_wait_cluster(recv_bar, 0, p.error_flag) ? 1 : 0) != 0;
+                if (good && fast_split && push_rows > 0) {
+                    if (t.split_k == 8) finish_item(std::integral_constant<int, 8>(), src, at, count, bias);
+                    else if (t.split_k == 4) finish_item(std::integral_constant<int, 4>(), src, at, count, bias);
+                    else finish_item(std::integral_constant<int, 2>(), src, at, count, bias);
+                }
+                if (!good) {
+                    // (as in the epilogue: a warp that gave up waits for the rest of the cluster to leave or give up)
+                    if (lane == 0) atomicExch(p.error_flag, 4);
+                    cluster_arrive();
+                    cluster_wait();
+                }
+                return;
+            }
         }
     } else {
         // ---------------- warps 2..5: the epilogue ----------------
@@ -498,7 +572,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         // now, while the first tiles are on their way.  After the accumulator there are four warps, one per
         // scheduler, each instruction waiting for the one before it: what is left on that path is the accumulator
         // load, the pushes, and for the rows this CTA finishes the loads, adds and stores.
-        constexpr int kFast = 2;                    // items per thread with everything precomputed (covers 64 columns x 16 rows)
+        constexpr int kFast = kX3 ? 1 : 2;          // items per thread with everything precomputed (256 in all: 64 columns x 16 rows)
         uint32_t push_dst = 0, push_bar = 0, push_stride = 0;
         bool push_mine = false;
         int fast_src[kFast];                        // float4 index of partial tile 0 of the item in the receive area
@@ -522,33 +596,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (tid + u * 128 < t.bn) bias_s[tid + u * 128] = bias_early[u];
         // (the second half of the preparation: called once the operand work of the K loop is behind these warps)
         auto prepare_rows = [&]() {
-            const int r0 = int(cluster_cta_rank()) * push_rpr;
-            const int valid = min(t.bn, g.Cout - cout0);
-            const int n_items = push_rows * (t.bn >> 2);
 #pragma unroll
-            for (int k = 0; k < kFast; ++k) {
-                const int item = tid + k * 128;
-                fast_src[k] = -1;
-                fast_at[k] = -1;
-                fast_count[k] = 0;
-                fast_bias[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (item < n_items) {
-                    const int q4 = div_pow2_likely(item, push_rows), lr = item - q4 * push_rows, c = q4 << 2;
-                    fast_src[k] = q4 * push_rpr + lr;
-                    const long pix = long(ow0) + r0 + lr;
-                    const long pix_off = t.flat ? ((r0 + lr < t.box_w && pix < long(g.N) * g.OH * g.OW) ? pix * p.out.pitch : -1)
-                                                : boxed_pixel_offset(r0 + lr, t.box_w, t.box_h, t.box_n, ow0, oh0, n0, g.N, g.OH, g.OW, p.out.pitch);
-                    if (pix_off >= 0 && c < valid) {
-                        fast_at[k] = pix_off + cout0 + c;
-                        fast_count[k] = valid - c;
-                        // (straight from global memory: the loads are in flight until the sums need them)
-                        float b[4];
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) b[j] = (p.bias && c + j < valid) ? __ldg(p.bias + cout0 + c + j) : 0.0f;
-                        fast_bias[k] = make_float4(b[0], b[1], b[2], b[3]);
-                    }
-                }
-            }
+            for (int k = 0; k < kFast; ++k) prepare_item(tid + k * 128, fast_src[k], fast_at[k], fast_count[k], fast_bias[k]);
             if (threadIdx.x == 64) STAMP(15);
         };
         bool ok = true;
@@ -593,42 +642,20 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 // partial tiles are added in split order, so the result does not depend on timing
                 const float4 *recv = reinterpret_cast<const float4 *>(generic_base + t.recv_off);
                 const int plane = (t.bn >> 2) * push_rpr;           // float4 from one partial tile to the next
-                auto finish_fast = [&](auto split_tag) {
-                    constexpr int S = decltype(split_tag)::value;
-                    float4 part[kFast][S];
 #pragma unroll
-                    for (int k = 0; k < kFast; ++k)
-#pragma unroll
-                        for (int sp = 0; sp < S; ++sp) part[k][sp] = recv[max(fast_src[k], 0) + sp * plane];
-                    if (threadIdx.x == 64) STAMP(11);
-#pragma unroll
-                    for (int k = 0; k < kFast; ++k) {
-                        float4 acc = part[k][0];
-#pragma unroll
-                        for (int sp = 1; sp < S; ++sp) {
-                            acc.x += part[k][sp].x; acc.y += part[k][sp].y; acc.z += part[k][sp].z; acc.w += part[k][sp].w;
-                        }
-                        float o[4] = {acc.x + fast_bias[k].x, acc.y + fast_bias[k].y, acc.z + fast_bias[k].z, acc.w + fast_bias[k].w};
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            o[j] = act_apply(o[j], g.act);
-                            if (t.round_tf32) o[j] = round_tf32(o[j]);
-                        }
-                        if (fast_at[k] >= 0) store4_direct(p.out.ptr, kBf16, fast_at[k], make_float4(o[0], o[1], o[2], o[3]), fast_count[k]);
-                        if (k == 0 && threadIdx.x == 64) STAMP(12);
-                    }
-                };
-                if (t.split_k == 8) finish_fast(std::integral_constant<int, 8>());
-                else if (t.split_k == 4) finish_fast(std::integral_constant<int, 4>());
-                else if (t.split_k == 2) finish_fast(std::integral_constant<int, 2>());
+                for (int k = 0; k < kFast; ++k) {
+                    if (t.split_k == 8) finish_item(std::integral_constant<int, 8>(), fast_src[k], fast_at[k], fast_count[k], fast_bias[k]);
+                    else if (t.split_k == 4) finish_item(std::integral_constant<int, 4>(), fast_src[k], fast_at[k], fast_count[k], fast_bias[k]);
+                    else if (t.split_k == 2) finish_item(std::integral_constant<int, 2>(), fast_src[k], fast_at[k], fast_count[k], fast_bias[k]);
+                    if (k == 0 && threadIdx.x == 64) STAMP(12);
+                }
                 // items beyond the precomputed ones (wide tiles), and splits without a form of their own
                 const int quads = t.bn >> 2;
                 const int n_items = push_rows * quads;
                 const int r0 = int(cluster_cta_rank()) * push_rpr;
                 const int valid = min(t.bn, g.Cout - cout0);
-                const bool fast_done = t.split_k == 8 || t.split_k == 4 || t.split_k == 2;
 #pragma unroll 1
-                for (int item = tid + (fast_done ? kFast * 128 : 0); item < n_items; item += 128) {
+                for (int item = tid + (fast_split ? 256 : 0); item < n_items; item += 128) {
                     const int q4 = item / push_rows, lr = item - q4 * push_rows, c = q4 << 2;
                     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 1
