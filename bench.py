@@ -233,8 +233,23 @@ def run_ours(args):
     graph = build_graph(args.model)
     weights = seeded_weights(graph, 0)
     base_config = graph.export_config()
-    exec_graph, search_s = schedule_graph(graph, args.schedule, args.batch)
+    cost_model = ios.cost_model.IOSCostModel() if args.schedule == 'dp' else None
+    exec_graph, search_s = schedule_graph(graph, args.schedule, args.batch, cost_model=cost_model)
     schedule_note = args.schedule
+    additivity = None
+    if args.schedule == 'dp':
+        # what the search minimised: the sum of the latencies of the chosen stages, each measured alone
+        # (answered from the cost model's memo); reported beside the latency of the whole schedule
+        try:
+            isolated = 0.0
+            for block in exec_graph.blocks:
+                nodes = {n.name: n for n in block.inner_nodes + [block.exit_node]}
+                for stage in block.stages:
+                    isolated += float(np.mean(cost_model.get_stage_latency(
+                        [[nodes[name] for name in group] for group in stage], args.batch, 2, 6, 3)))
+            additivity = {'sum_of_isolated_stage_ms': round(isolated, 4), 'stages_measured_by_search': cost_model.measured}
+        except Exception as exc:      # (reporting only)
+            additivity = {'error': repr(exc)}
     if args.schedule == 'dp':
         # the search adds up stage latencies measured one by one; the whole schedules are timed too and the
         # heuristic one is kept if it is faster (both numbers are reported)
@@ -242,6 +257,11 @@ def run_ours(args):
         exec_graph, whole = rt.pick_faster([exec_graph, graph], args.batch, warmup=3, number=10, repeat=5)
         schedule_note = (f'dp ({whole[0]:.4f} ms whole) vs greedy ({whole[1]:.4f} ms whole): '
                          f'{"dp" if whole[0] <= whole[1] else "greedy"} kept')
+        if additivity and 'sum_of_isolated_stage_ms' in additivity:
+            additivity['dp_whole_ms'] = round(whole[0], 4)
+            additivity['greedy_whole_ms'] = round(whole[1], 4)
+            additivity['whole_minus_sum_over_sum'] = round((whole[0] - additivity['sum_of_isolated_stage_ms']) /
+                                                            additivity['sum_of_isolated_stage_ms'], 4)
     log(f'[rank {ranks.rank}] schedule "{schedule_note}": {sum(len(b.stages) for b in exec_graph.blocks)} stages, '
         f'search took {search_s:.1f} s')
 
@@ -373,6 +393,7 @@ def run_ours(args):
                 'h2d_bytes_per_step': int(x.nbytes), 'd2h_bytes_per_step': int(y.nbytes)},
         'gpu_launches': info['launches'] * args.steps + (info['launches'] + 2) * args.steps * 2 +
                         info['launches'] * max(10, args.steps),
+        'schedule_additivity': additivity,
         'warm_l2_ms_per_step': round(warm_ms, 5),
         'ms_per_step_spread': {'median': round(statistics.median(step_ms), 5), 'p10': round(float(np.percentile(step_ms, 10)), 5),
                                'p90': round(float(np.percentile(step_ms, 90)), 5), 'note': 'rank 0, device time per step'},
