@@ -94,7 +94,8 @@ IOS_API const char *ios_last_error(void);
  * warps that issue tcgen05.mma in the patch convolution),
  * "cluster_push" "1"/"0" (the CTAs of a split-K cluster push their partial tiles into each other's shared memory / exchange
  * them through a workspace in L2; same bits), "dual_issue" "1"/"0" (three-pass products issued by two threads into
- * accumulators of their own / by one thread),
+ * accumulators of their own / by one thread), "weight_prefetch" "1"/"0" (a tensor-core convolution asks the packed
+ * weights of the next one into L2 while it runs / does not),
  * "persistent" "1"/"0" (grids of several waves run as resident CTAs that walk the tiles / one CTA per tile),
  * "bulk_store" "1"/"0" (results leave through a bulk tensor store / straight from registers),
  * "split_k", "bn", "stages", "producers" (a positive number overrides the K split, the output-channel tile

@@ -499,6 +499,17 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         // ---------------- warps 7..10 (three-pass mode): the residual of every landed activation tile ----------------
         if (kX3) {
             const int tid = threadIdx.x - 224;          // 0..127
+            // Nothing to do until the first tile lands: the CTAs of the grid share out the next convolution's
+            // weights, one 128-byte line per request, and ask them into L2 (they are read once per forward and the
+            // networks' weights do not fit the L2 together, so they would otherwise be met in DRAM).
+            if (p.next_weights) {
+                const unsigned ctas = gridDim.x * gridDim.y * gridDim.z;
+                const unsigned cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+                const char *w = static_cast<const char *>(p.next_weights);
+#pragma unroll 1
+                for (unsigned off = (cta * 128u + unsigned(tid)) * 128u; off < p.next_weight_bytes; off += ctas * 128u * 128u)
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(w + off) : "memory");
+            }
             // The tensor core reads the 19 leading bits of an fp32 operand (sign, exponent, 10 mantissa
             // bits), so the landed activation tile serves as the TF32 value as it is.  What the hardware
             // drops -- x minus x with the low 13 bits cleared, exact in fp32 -- is written to the residual

@@ -167,6 +167,8 @@ struct ConvTcParams {
     unsigned int *counters;
     int *error_flag;               // device word set to non-zero when a bounded wait ran out
     long long *timeline;           // optional diagnostics: 16 SM-clock stamps written by CTA (0,0,0), or null
+    const void *next_weights;      // packed weights of the tensor-core convolution launched after this one (or null) ...
+    unsigned next_weight_bytes;    // ... and how many of their bytes to ask into L2 while this kernel runs
     ConvGeom g;
 };
 // Returns false when the shape / view cannot use the tensor-core kernel.

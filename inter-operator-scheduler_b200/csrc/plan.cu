@@ -83,6 +83,24 @@ public:
             }
         }
         plan_.launches_per_forward = int(plan_.steps.size());
+        // Weights are read once per forward and do not fit the L2 together, so every convolution would meet its own
+        // in DRAM: each tensor-core convolution asks the weights of the next one (in launch order) into L2 instead.
+        {
+            Step *previous = nullptr;
+            for (Step &s : plan_.steps) {
+                if (s.kind != StepKind::ConvTc) continue;
+                s.tc.next_weights = nullptr;
+                s.tc.next_weight_bytes = 0;
+                if (previous && !plan_.options.no_weight_prefetch) {
+                    size_t bytes = 0;
+                    for (const ConvSlot &c : plan_.convs)
+                        if (c.op == s.op) bytes = c.weight_bytes;
+                    previous->tc.next_weights = s.tc.weight_packed;
+                    previous->tc.next_weight_bytes = unsigned(std::min<size_t>(bytes, size_t(16) << 20) & ~size_t(127));
+                }
+                previous = &s;
+            }
+        }
         if (dry_) {
             plan_.zero_bytes = counter_total_;
             plan_.group_workspace_bytes = ws_need_;
@@ -450,6 +468,8 @@ private:
             s.tc.error_flag = reinterpret_cast<int *>(at(plan_.error_flag_offset));
             s.tc.workspace = nullptr;
             s.tc.counters = nullptr;
+            s.tc.next_weights = nullptr;
+            s.tc.next_weight_bytes = 0;
             s.tc.timeline = plan_.options.timeline ? reinterpret_cast<long long *>(at(plan_.error_flag_offset) + 16) : nullptr;
             if (slot.tcplan.split_k > 1) {
                 if (dry_) {

@@ -40,6 +40,7 @@ struct Options {
     bool patch_bulk_store = false; // testing aid: patch convolutions store finished tiles with bulk tensor stores
     bool patch_all = false;     // testing aid: patch convolutions also for layers that stream their weights
     bool no_patch = false;      // testing aid: stride-1 windows load an activation tile per tap instead of one patch per tile
+    bool no_weight_prefetch = false; // testing aid: a convolution does not ask the next one's weights into L2
     bool no_dual_issue = false; // testing aid: three-pass convolutions issue all their products from one thread
     bool no_cluster_push = false; // testing aid: split-K clusters exchange partial tiles through L2 instead of shared memory
     bool no_persistent = false; // testing aid: grids of several waves launch one CTA per tile instead of resident CTAs

@@ -862,6 +862,7 @@ int ios_set_option(const char *key, const char *value) {
         else if (k == "persistent" && (v == "0" || v == "1")) g_options.no_persistent = v == "0";
         else if (k == "cluster_push" && (v == "0" || v == "1")) g_options.no_cluster_push = v == "0";
         else if (k == "dual_issue" && (v == "0" || v == "1")) g_options.no_dual_issue = v == "0";
+        else if (k == "weight_prefetch" && (v == "0" || v == "1")) g_options.no_weight_prefetch = v == "0";
         else if (k == "patch" && (v == "0" || v == "1" || v == "all")) {
             g_options.no_patch = v == "0";
             g_options.patch_all = v == "all";
@@ -889,6 +890,7 @@ int ios_get_option(const char *key, char *value, int capacity) {
         else if (k == "persistent") v = g_options.no_persistent ? "0" : "1";
         else if (k == "cluster_push") v = g_options.no_cluster_push ? "0" : "1";
         else if (k == "dual_issue") v = g_options.no_dual_issue ? "0" : "1";
+        else if (k == "weight_prefetch") v = g_options.no_weight_prefetch ? "0" : "1";
         else if (k == "patch") v = g_options.no_patch ? "0" : g_options.patch_all ? "all" : "1";
         else if (k == "executor") v = g_options.use_graph ? "graph" : "streams";
         else if (k == "conv") v = g_options.allow_tc ? "auto" : "direct";

@@ -21,7 +21,7 @@ pytestmark = pytest.mark.gpu
 
 DEFAULTS = (('precision', 'tf32x3'), ('pdl', '1'), ('executor', 'graph'), ('conv', 'auto'), ('split_k', '0'),
             ('im2col', '1'), ('persistent', '1'), ('stem', '1'), ('bulk_store', '1'), ('stage_barriers', '1'),
-            ('pdl_edges', '0'), ('cluster_push', '1'), ('dual_issue', '1'))
+            ('pdl_edges', '0'), ('cluster_push', '1'), ('dual_issue', '1'), ('weight_prefetch', '1'))
 
 
 @pytest.fixture(autouse=True)
@@ -51,6 +51,7 @@ def test_executor_variants_reproduce_the_reference_outputs(golden, model, option
     base = rt.graph_inference(opt, 1, x)
     golden.expect(f'{model}_dp_parallel_merge_seed7', base, TOL_TF32)
     rt.set_option(option, '0' if option == 'stage_barriers' else '1')
+    rt.set_option('weight_prefetch', '0' if option == 'pdl_edges' else '1')     # (no effect on results either way)
     for executor in ('graph', 'streams'):
         rt.set_option('executor', executor)
         y = rt.graph_inference(opt, 1, x)
