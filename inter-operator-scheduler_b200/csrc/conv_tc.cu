@@ -237,9 +237,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const ConvGeom &g = p.g;
     if (threadIdx.x == 0) STAMP(0);
-    // The next kernel of the stream may start its prologue (on SMs this grid leaves free, or as CTAs leave) as soon
-    // as every CTA of this grid has got here; it reads nothing of ours before its own griddepcontrol.wait.
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     {
         // Kernel parameters are new with every launch, so the first read of each of their cache lines misses.
         // One word of every line is asked for here, all at once, instead of one miss at a time where the
@@ -403,6 +400,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // Nothing may be pushed into a CTA before its barrier exists: every thread of the cluster arrives here and
     // waits only where it needs the others (the epilogue before its first push, everyone else before leaving).
     if (push) cluster_arrive_relaxed();
+    // The next kernel of the stream may start its prologue (on SMs this grid leaves free, or as CTAs leave) once
+    // every CTA of this grid has got here; it reads nothing of ours before its own griddepcontrol.wait.  (At kernel
+    // entry instead: the same for one stream, 2 % slower for schedules with concurrent groups, whose waiting
+    // dependents then hold SMs that a sibling group's kernel could use.)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
     if (threadIdx.x == 0) STAMP(1);
     // Warps 0 and 1 work through a few lanes only.  Their other lanes leave now: a lane that spins on a
