@@ -74,6 +74,8 @@ struct TileGeom {
                       //    residual; the residual's products accumulate in columns [bn, 2 bn)
     int dual;         // 1: (three-pass mode, wide) a second thread issues the products with the activation residual into an
                       //    accumulator of its own, columns [2 bn, 3 bn)
+                      // 2: (single-pass modes) a second thread issues the second half of every K step's instructions into an
+                      //    accumulator of its own, columns [bn, 2 bn)
     int split_shift;  // log2(split_k) when it is a power of two, else -1
     unsigned magic_ow, magic_cc, magic_kw;   // division by OW / cchunks / kw as a multiplication (0: divide)
     int push;         // 1: (cluster) partial tiles are pushed into the shared memory of the CTA that finishes their rows
@@ -184,9 +186,11 @@ __device__ __forceinline__ bool mma_loop(int n_it, int stages, uint32_t wait0, u
 // Three-pass mode with two issuing threads: each runs this loop over its own pair of operand planes and its own
 // accumulator, so neither waits for the other's instructions to be issued (one thread gets a tcgen05.mma out
 // about every 90 cycles, whatever its width).  Both hand a stage back; the producer waits for the two of them.
-template <bool kTimeline>
+// (Single-pass modes use it too: there the two threads share the instructions of a K step, k in [k0, k1) each.)
+template <bool kTimeline, bool kF16 = false>
 __device__ __forceinline__ bool mma_loop_planes(int n_it, int stages, uint32_t wait0, uint32_t empty0, uint64_t da0, uint64_t db0,
-                                                uint64_t dstep, uint32_t tmem_d, uint32_t idesc, const ConvTcParams &p, bool stamp) {
+                                                uint64_t dstep, uint32_t tmem_d, uint32_t idesc, const ConvTcParams &p, bool stamp,
+                                                int k0 = 0, int k1 = 4) {
     uint64_t da = da0, db = db0;
     uint32_t s = 0, phase = 0;
 #pragma unroll 1
@@ -195,7 +199,12 @@ __device__ __forceinline__ bool mma_loop_planes(int n_it, int stages, uint32_t w
         if (i == 0 && stamp) STAMP(3);
         tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < 4; ++k) umma_tf32(tmem_d, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+        for (int k = 0; k < 4; ++k) {
+            if (k < k0 || k >= k1) continue;
+            const uint32_t acc = (i > 0 || k > k0) ? 1u : 0u;
+            if (kF16) umma_f16(tmem_d, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, acc);
+            else umma_tf32(tmem_d, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, acc);
+        }
         umma_commit(empty0 + 8u * s);
         da += dstep; db += dstep;
         if (++s == uint32_t(stages)) { s = 0; phase ^= 1u; da = da0; db = db0; }
@@ -340,14 +349,16 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // batch 1 a CTA of a split-K cluster has no more steps than that); the rest of the set-up runs while they
     // are on their way.
     const int early = min(n_it, t.stages);
-    const bool dual = kX3 && t.dual != 0;
+    const bool dual = kX3 && t.dual == 1;
+    const bool halves = !kX3 && t.dual == 2;        // single-pass modes: the K step's instructions shared by two threads
+    constexpr int kSteps = MODE == 4 ? 2 : 4;       // instructions per K step (32 bytes of K each)
     if (warp == 0) {
         // the barriers lie behind one another: full[stages], empty[stages], ready[stages], accumulator, (8 bytes
         // of other use), receive -- lane i initialises the i-th of them
         const int n_bars = 3 * t.stages + 3;
         if (lane < n_bars && lane != 3 * t.stages + 1 && (push || lane != 3 * t.stages + 2)) {
             // arrivals per phase: the split's 128 threads on `ready`; both issuers on `empty` and on the accumulator's
-            const bool both = dual && ((lane >= t.stages && lane < 2 * t.stages) || lane == 3 * t.stages);
+            const bool both = (dual || halves) && ((lane >= t.stages && lane < 2 * t.stages) || lane == 3 * t.stages);
             mbar_init(bars + 8u * lane, (lane >= 2 * t.stages && lane < 3 * t.stages) ? 128u : (both ? 2u : 1u));
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -410,7 +421,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // Warps 0 and 1 work through a few lanes only.  Their other lanes leave now: a lane that spins on a
     // barrier pays about 50 cycles per wait while the rest of its warp is parked at the reconvergence point.
     // (Not in a cluster: there every thread takes part in the cluster barriers below.)
-    if (!kCluster && ((warp == 0 && lane >= t.producers) || (warp == 1 && lane != 0) || (warp == 6 && (lane != 0 || !dual)))) return;
+    if (!kCluster && ((warp == 0 && lane >= t.producers) || (warp == 1 && lane != 0) || (warp == 6 && (lane != 0 || !(dual || halves))))) return;
     if (!kCluster && !kX3 && warp >= 7) return;
 
     if (warp == 0) {
@@ -480,6 +491,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             // (two issuers: this one forms a_hi*[w_hi | w_lo] from the tiles as they land)
             const bool ok = dual ? mma_loop_planes<kTimeline>(n_it, t.stages, full0, empty0, ring.da0, ring.db0, ring.dstep, tmem_base,
                                                               idesc_wide, p, true)
+                            : halves ? mma_loop_planes<kTimeline, kBf16>(n_it, t.stages, full0, empty0, ring.da0, ring.db0, ring.dstep,
+                                                                         tmem_base, idesc, p, true, 0, kSteps / 2)
                             : kX3 ? (t.wide ? IOS_MMA_LOOP(3, ready0) : IOS_MMA_LOOP(1, ready0))
                                   : (kBf16 ? IOS_MMA_LOOP(MODE, full0) : IOS_MMA_LOOP(0, full0));
 #undef IOS_MMA_LOOP
@@ -494,6 +507,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const bool ok = mma_loop_planes<kTimeline>(n_it, t.stages, ready0, empty0, smem_desc_kmajor(smem_base + a_lo_off, kRow),
                                                        smem_desc_kmajor(smem_base + b_off, kRow), uint64_t(stage_bytes >> 4),
                                                        tmem_base + 2u * uint32_t(t.bn), idesc, p, false);
+            if (ok) umma_commit(accum_bar);
+            else atomicExch(p.error_flag, 2);
+        } else if (lane == 0 && halves) {
+            // ---------------- second MMA issuer (single-pass modes): the second half of every K step ----------------
+            const uint32_t fmt = kBf16 ? 1u : 2u;
+            const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(t.bn >> 3) << 17) | (uint32_t(kTileM >> 4) << 24);
+            const bool ok = mma_loop_planes<kTimeline, kBf16>(n_it, t.stages, full0, empty0, smem_desc_kmajor(smem_base, kRow),
+                                                              smem_desc_kmajor(smem_base + b_off, kRow), uint64_t(stage_bytes >> 4),
+                                                              tmem_base + uint32_t(t.bn), idesc, p, false, kSteps / 2, kSteps);
             if (ok) umma_commit(accum_bar);
             else atomicExch(p.error_flag, 2);
         }
@@ -623,7 +645,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (!(kCluster && push)) asm volatile("bar.sync 1, 128;" ::: "memory");          // bias_s is complete
         if (threadIdx.x == 64) STAMP(9);
         const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16);
-        const uint32_t pair = t.wide ? uint32_t(t.bn) : 0u;
+        const uint32_t pair = (t.wide || halves) ? uint32_t(t.bn) : 0u;
         const uint32_t third = dual ? 2u * uint32_t(t.bn) : 0u;
         const int tile_id = m_tile * gridDim.y + n_tile;
         bool finisher = true;
@@ -1734,8 +1756,9 @@ void launch_conv_tc(const ConvTcParams &p, const ConvTcPlan &q, cudaStream_t str
     // two issuers (three accumulator ranges) when tensor memory has room: this kernel has the SM's to itself
     // unless a second CTA shares the SM, and then 3 x bn columns of each must fit side by side
     t.dual = (t.wide && !q.persistent && !q.no_dual && 3 * q.bn <= ((q.split_k > 1 && q.cluster) ? 512 : 256)) ? 1 : 0;
+    if (!q.x3 && !q.persistent && !q.no_dual && 2 * q.bn <= ((q.split_k > 1 && q.cluster) ? 512 : 256)) t.dual = 2;
     int cols = 32;
-    while (cols < (t.dual ? 3 : t.wide ? 2 : 1) * q.bn) cols *= 2;   // the wide form keeps a second accumulator range
+    while (cols < (t.dual == 1 ? 3 : (t.wide || t.dual == 2) ? 2 : 1) * q.bn) cols *= 2;   // further accumulator ranges
     t.tmem_cols = cols;
     t.round_tf32 = p.g.round_out;
     t.x3 = q.x3;
@@ -1768,7 +1791,7 @@ void launch_conv_tc(const ConvTcParams &p, const ConvTcPlan &q, cudaStream_t str
         cfg.blockDim = dim3(kPersistThreads);
     } else {
         cfg.gridDim = dim3(q.tiles_w * q.tiles_h * q.tiles_n, q.n_tiles, q.split_k);
-        cfg.blockDim = dim3(q.x3 ? kThreads : 192);     // (warps 6..10 have work in three-pass mode only)
+        cfg.blockDim = dim3(q.x3 ? kThreads : t.dual == 2 ? 224 : 192);     // (warp 6: second issuer; warps 7..10: three-pass mode only)
     }
     cfg.dynamicSmemBytes = q.smem_bytes;
     cfg.stream = stream;
