@@ -14,25 +14,36 @@
 //   tcgen05.mma.kind::tf32 of K = 8; 64 bfloat16, four kind::f16 of K = 16; bfloat16 layers of at most 32
 //   input channels use 64-byte rows, two instructions per step).  Three-pass TF32: the weight tile and its
 //   residual lie behind one another, one instruction of width 2 bn forms a_hi*w_hi | a_hi*w_lo, a second
-//   adds a_lo*w_hi; the activation residual is computed from the landed tile by the epilogue warps.
+//   adds a_lo*w_hi; the activation residual is computed from the landed tile by warps of their own.
+//   Two threads issue: in three-pass mode one the wide instructions (as soon as a tile has landed), the
+//   other a_lo*w_hi (once the residual is written) into an accumulator of its own; in the single-pass
+//   modes each takes half of a K step's instructions.  The epilogue adds the accumulator ranges in a fixed order.
 // * split_k CTAs share an output tile when the layer is too small to fill 148 SMs (batch 1).  Up to 8
-//   of them form a thread-block cluster: each writes its fp32 partial tile to a workspace (it stays in
-//   L2), and after ONE cluster barrier CTA r adds rows [r*128/S, (r+1)*128/S) of all S tiles in split
-//   order, applies bias and activation and stores them.  Larger splits (a testing aid, and the
-//   allocation-free entry point) elect the last CTA to arrive by one atomic ticket per tile.  Either way
-//   the result does not depend on timing.
+//   of them form a thread-block cluster and exchange their fp32 partial tiles through distributed shared
+//   memory: the tile's valid rows are dealt to the CTAs, every epilogue thread pushes its row (st.async, 16
+//   bytes at a time) into the receive area of the CTA that finishes it, the bytes are counted on that CTA's
+//   mbarrier, and the finishing CTA adds the S slices in split order, applies bias and activation and
+//   stores.  When the receive area does not fit, partial tiles go to a workspace (it stays in L2) and one
+//   cluster barrier precedes the same row-wise reduction.  Larger splits (a testing aid, and the
+//   allocation-free entry point) elect the last CTA to arrive by one atomic ticket per tile.  In every
+//   form the result does not depend on timing.
 // * Epilogue: tcgen05.ld (one thread per pixel row), + bias, activation, optional rounding to TF32 for a
 //   consumer convolution, then the tile is staged in shared memory (128-byte swizzle) and leaves through
 //   bulk tensor stores into a channel window of the destination (NHWC, pitch) -- which is how
 //   concat-by-placement and merged convolutions are written without a copy; windows that are not 16-byte
-//   aligned are stored from registers.
+//   aligned, and the rows of a cluster reduction, are stored from registers.
+// * While a three-pass convolution waits for its first tile it asks the packed weights of the next
+//   convolution into L2 (they are read once per forward and the networks' weights do not fit the L2 together).
 //
-// Warp roles of conv_tc_kernel (192 threads): warp 0 = TMA producer lanes, warp 1 = MMA issuer, warps
-// 2..5 = operand split (three-pass mode) and epilogue; warp 2 allocates and frees tensor memory.
-// conv_tc_persistent_kernel (320 threads): the same with eight epilogue warps and two accumulators in
-// tensor memory, for grids of several waves.  Every wait on an mbarrier is bounded: when the bound is hit
-// the kernel records a code in *error_flag, drains its own loads, frees its tensor memory and returns.
-// Stride-1 windows whose weights fit in shared memory take conv_tc_patch.cu instead.
+// Warp roles of conv_tc_kernel: warp 0 = TMA producer lanes (and barrier set-up, first weight tiles),
+// warp 1 = MMA issuer (and tensor-map prefetch, first activation tiles), warps 2..5 = epilogue (warp 2
+// allocates and frees tensor memory), warp 6 = second MMA issuer; three-pass mode: warps 7..10 = residual
+// of the landed activation tiles, then half of the rows of a cluster reduction (192 / 224 / 352 threads).
+// conv_tc_persistent_kernel (320 threads): one issuer, eight epilogue warps (three-pass mode: four, and four
+// for the residual) and two accumulators in tensor memory, for grids of several waves.  Every wait on an
+// mbarrier is bounded: when the bound is hit the kernel records a code in *error_flag, drains its own loads,
+// frees its tensor memory and returns.  Stride-1 windows whose weights fit in shared memory take
+// conv_tc_patch.cu instead.
 //
 // Replaces cudnnConvolutionBiasActivationForward / cudnnConvolutionForward + cudnnAddTensor
 // (reference src/ios/ios_runtime.cu:313-331) and the algorithm search of :150-205.
