@@ -263,10 +263,11 @@ __global__ void __launch_bounds__(kThreads) pool3x3_kernel(const PoolParams p, i
     float r1[V], r2[V];
 #pragma unroll
     for (int j = 0; j < V; ++j) r1[j] = r2[j] = identity;
-    for (int hb = h_first; hb <= h_last; hb += kRows) {
-        Raw raw[kRows][3];
+    // Two rows per request, two requests in flight: while one pair of rows is reduced, the next pair is on its way.
+    constexpr int kPair = kRows / 2;
+    auto fetch = [&](Raw (&raw)[kPair][3], int hb) {
 #pragma unroll
-        for (int r = 0; r < kRows; ++r) {
+        for (int r = 0; r < kPair; ++r) {
             const int h = hb + r;
             const bool row_ok = h >= 0 && h < p.in.H && h <= h_last;
             const T *src = image + size_t(max(h, 0)) * row_pitch;
@@ -274,8 +275,10 @@ __global__ void __launch_bounds__(kThreads) pool3x3_kernel(const PoolParams p, i
             for (int s = 0; s < 3; ++s)
                 if (row_ok && w_ok[s]) raw[r][s] = *reinterpret_cast<const Raw *>(src + (s - first) * p.in.pitch);
         }
+    };
+    auto reduce = [&](const Raw (&raw)[kPair][3], int hb) {
 #pragma unroll
-        for (int r = 0; r < kRows; ++r) {
+        for (int r = 0; r < kPair; ++r) {
             const int h = hb + r;
             if (h > h_last) break;
             const bool row_ok = h >= 0 && h < p.in.H;
@@ -310,6 +313,14 @@ __global__ void __launch_bounds__(kThreads) pool3x3_kernel(const PoolParams p, i
 #pragma unroll
             for (int j = 0; j < V; ++j) { r1[j] = r2[j]; r2[j] = acc[j]; }
         }
+    };
+    Raw even[kPair][3], odd[kPair][3];
+    fetch(even, h_first);
+    for (int hb = h_first; hb <= h_last; hb += kRows) {
+        fetch(odd, hb + kPair);
+        reduce(even, hb);
+        fetch(even, hb + kRows);
+        reduce(odd, hb + kPair);
     }
 }
 
