@@ -231,8 +231,9 @@ template <> struct VecIo<__nv_bfloat16, 8> {
 // neighbours in the warp read at the same moment, so two of three come from L1) are reduced to one
 // value per row, the last three rows' values sit in registers, and an output row is emitted whenever
 // the window is complete -- 3 loads per output for a stride-1 window instead of 9, 6 for stride 2.
-// Rows are fetched four at a time (12 independent 16-byte loads in flight per thread): a thread's rows
-// depend on one another only through registers, so the memory latency is paid once per four rows.
+// Rows are fetched two at a time, and the next pair is requested before the current one is reduced (6 to 12
+// independent 16-byte loads in flight per thread at any time): a thread's rows depend on one another only
+// through registers, and with two blocks of 256 threads per SM it is the bytes in flight that feed the memory.
 // Average pooling divides by 9 whatever the padding (CUDNN_POOLING_AVERAGE_COUNT_INCLUDE_PADDING,
 // the reference's mode, src/ios/ios_runtime.cu:546-553).
 template <typename T, int V, bool kMax>
