@@ -151,7 +151,7 @@ __device__ __forceinline__ bool mma_loop(int n_it, int stages, uint32_t wait0, u
         const uint64_t da = ring.da, db = ring.db, dal = ring.dal, dbl = ring.dbl;
         if (MODE == 1 || MODE == 3) {
             // Three-pass mode: the products of the first activation tile as it landed (its TF32 value) start while
-            // the epilogue warps are still writing the tile's residual; only the residual's product waits for them.
+            // the residual warps are still writing the tile's residual; only the residual's product waits for them.
             // (Later tiles have their residual written while the tensor core is busy with the tile before: one wait.)
             if (!mbar_wait((i == 0 ? landed0 : wait0) + 8u * ring.s, ring.phase, p.error_flag)) return false;
             tc_fence_after();
