@@ -151,6 +151,10 @@ IOS_API int ios_engine_time(ios_engine *engine, int iters, float *ms_per_iter);
 /* Describe the plan: writes a JSON text (kernel launches per forward, arena bytes, workspace bytes,
  * algorithmic FLOPs, output shape) into text[capacity]. */
 IOS_API int ios_engine_describe(ios_engine *engine, char *text, int capacity);
+/* The plan of a scheduled graph without a device: arena size, launches, and for every convolution the kernel
+ * and tiling the current options choose for a GPU of `sm_count` SMs (0: 148) -- JSON into `text`.  Nothing is
+ * allocated or launched; a machine without a GPU can call it. */
+IOS_API int ios_plan_describe(const char *graph_json, int batch_size, int sm_count, char *text, int capacity);
 /* Device time of the launches of one forward by kind: all launches of a kind run one after another
  * on a single stream (captured into one CUDA graph of their own), and every launch is credited with
  * its kind's mean, averaged over `iters` passes.  step_kind: 0 sum/copy, 1 pool,

@@ -1237,6 +1237,47 @@ int ios_engine_profile(ios_engine *engine, int iters, int capacity, int *count, 
     });
 }
 
+int ios_plan_describe(const char *graph_json, int batch_size, int sm_count, char *text, int capacity) {
+    return guarded([&]() {
+        if (!graph_json || !text || capacity <= 0 || batch_size <= 0) throw ArgumentError("graph_json and text must not be NULL, batch_size > 0");
+        Plan plan;
+        plan.model = model_from_graph(Json::parse(graph_json), batch_size);
+        {
+            std::lock_guard<std::mutex> lock(g_mutex);
+            plan.options = g_options;
+        }
+        plan_layout(&plan, sm_count > 0 ? sm_count : 148);        // sizes and tilings only: no device is touched
+        std::string out = "{\"arena_bytes\": " + std::to_string(plan.arena_bytes) + ", \"launches\": " +
+                          std::to_string(plan.launches_per_forward) + ", \"convolutions\": [";
+        bool first = true;
+        for (const Step &s : plan.steps) {
+            if (s.kind != StepKind::ConvTc && s.kind != StepKind::ConvDirect && s.kind != StepKind::ConvDepthwise) continue;
+            const ConvGeom &g = s.kind == StepKind::ConvTc ? s.tc.g : s.direct.g;
+            char line[640];
+            if (s.kind == StepKind::ConvTc) {
+                const ConvTcPlan &q = s.tcplan;
+                std::snprintf(line, sizeof line,
+                              "{\"op\": \"%s\", \"kind\": \"tensor\", \"cin\": %d, \"cout\": %d, \"kh\": %d, \"kw\": %d, \"oh\": %d, \"ow\": %d, "
+                              "\"bn\": %d, \"n_tiles\": %d, \"k_iters\": %d, \"split_k\": %d, \"cluster\": %d, \"push\": %d, \"recv_off\": %d, "
+                              "\"stages\": %d, \"smem_bytes\": %zu, \"workspace_bytes\": %zu, \"persistent\": %d, \"patch\": %d, \"grid_ctas\": %d, "
+                              "\"x3\": %d, \"bf16\": %d, \"half_rows\": %d}",
+                              plan.model.ops[s.op].name.c_str(), g.Cin, g.Cout, g.kh, g.kw, g.OH, g.OW, q.bn, q.n_tiles, q.k_iters, q.split_k,
+                              q.cluster, q.push, q.recv_off, q.stages, q.smem_bytes, q.workspace_bytes, q.persistent, q.patch, q.grid_ctas,
+                              q.x3, q.bf16, q.half_rows);
+            } else {
+                std::snprintf(line, sizeof line, "{\"op\": \"%s\", \"kind\": \"%s\", \"cin\": %d, \"cout\": %d, \"kh\": %d, \"kw\": %d}",
+                              plan.model.ops[s.op].name.c_str(), s.kind == StepKind::ConvDirect ? "cuda_core" : "depthwise", g.Cin, g.Cout,
+                              g.kh, g.kw);
+            }
+            out += (first ? "" : ", ") + std::string(line);
+            first = false;
+        }
+        out += "]}";
+        if (int(out.size()) + 1 > capacity) throw ArgumentError("capacity is too small for the description (" + std::to_string(out.size() + 1) + " bytes)");
+        std::memcpy(text, out.c_str(), out.size() + 1);
+    });
+}
+
 int ios_engine_describe(ios_engine *engine, char *text, int capacity) {
     return guarded([&]() {
         if (!engine || !text || capacity <= 0) throw ArgumentError("engine and text must not be NULL");

@@ -64,6 +64,8 @@ def load_ios_library():
         handle.ios_engine_run_pipelined.argtypes = [ctypes.c_void_p, _INT, _VOIDPP, _VOIDPP]
         handle.ios_engine_time.argtypes = [ctypes.c_void_p, _INT, _FLOATP]
         handle.ios_engine_describe.argtypes = [ctypes.c_void_p, ctypes.c_char_p, _INT]
+        handle.ios_plan_describe.argtypes = [ctypes.c_char_p, _INT, _INT, ctypes.c_char_p, _INT]
+        handle.ios_plan_describe.restype = _INT
         handle.ios_engine_profile.argtypes = [ctypes.c_void_p, _INT, _INT, ctypes.POINTER(_INT), _FLOATP,
                                               ctypes.POINTER(_INT), ctypes.POINTER(ctypes.c_double)]
         handle.ios_engine_set_input.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
@@ -95,6 +97,18 @@ def _check(status):
 def set_option(key: str, value: str):
     """Run-time switches: precision tf32x3|tf32|bf16|fp32, executor graph|streams, conv auto|direct, pdl 0|1."""
     _check(_library().ios_set_option(key.encode(), str(value).encode()))
+
+
+def plan_describe(graph: Graph, batch_size: int, sm_count: int = 0) -> dict:
+    """
+    The plan the current options would build for `graph`: arena size, launches per forward, and for every convolution
+    its kernel and tiling.  Touches no device (works on a machine without a GPU).
+    """
+    text = json.dumps(graph.export_config()).encode()
+    capacity = 1 << 20
+    buf = ctypes.create_string_buffer(capacity)
+    _check(_library().ios_plan_describe(text, batch_size, sm_count, buf, capacity))
+    return json.loads(buf.value.decode())
 
 
 def get_option(key: str) -> str:
